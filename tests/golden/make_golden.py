@@ -1,0 +1,187 @@
+"""Generate the golden fixtures in this directory by EXECUTING the reference's own
+test code (run once, where the reference checkout is available):
+
+    python tests/golden/make_golden.py /path/to/reference
+
+The reference test modules (tests/test_flash_attn_npu_v2.py, ..._v3.py) import
+``torch_npu`` and the NPU package, so they are loaded with stub modules: the
+public attention functions are replaced by recorders that capture the inputs
+the test built, ``Tensor.npu()`` is the identity, and
+``torch.testing.assert_close`` records the *expected* tensors -- i.e. the golden
+output and LSE computed by the reference's ``ref_flash_attention`` plus its
+in-test mask construction and dead-row patch-up.  Each fixture therefore holds
+(inputs, reference golden) pairs produced by the reference's code, at shapes
+small enough to commit.  Inputs come from ``torch.manual_seed(seed)`` followed by
+the test's own ``torch.rand`` calls.
+"""
+from __future__ import annotations
+
+import importlib.util
+import json
+import os
+import sys
+import types
+
+import numpy as np
+import torch
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+
+
+def to_np(t: torch.Tensor):
+    t = t.detach().cpu().contiguous()
+    if t.dtype == torch.bfloat16:
+        return t.view(torch.int16).numpy(), "bf16"
+    if t.dtype == torch.float16:
+        return t.numpy(), "fp16"
+    if t.dtype == torch.float32:
+        return t.numpy(), "fp32"
+    if t.dtype == torch.int32:
+        return t.numpy(), "i32"
+    raise TypeError(t.dtype)
+
+
+class Recorder:
+    def __init__(self):
+        self.call = None
+        self.expected = []
+
+    def api(self, name, n_ret):
+        def fn(*args, **kwargs):
+            self.call = (name, args, kwargs)
+            q = args[0]
+            out = torch.zeros_like(q)
+            lse = torch.zeros(1)
+            if name == "flash_attn_func":
+                return (out, lse, None) if kwargs.get("return_attn_probs", False) else out
+            if name == "flash_attn_varlen_func":
+                return out, lse, None
+            rest = tuple(None for _ in range(n_ret - 2))
+            return (out, lse) + rest
+        return fn
+
+    def assert_close(self, actual, expected, **kw):
+        self.expected.append(expected.detach().clone())
+
+
+def load_reference_tests(ref_root: str, which: str, rec: Recorder):
+    npu = types.ModuleType("torch_npu")
+    npu.npu = types.SimpleNamespace(get_device_name=lambda: "Ascend910B", device_count=lambda: 1)
+    sys.modules["torch_npu"] = npu
+    pkg = types.ModuleType("flash_attn_npu_" + which)
+    n_ret = 2 if which == "v2" else 4
+    for name in ("flash_attn_with_kvcache", "flash_attn_func", "flash_attn_varlen_func"):
+        setattr(pkg, name, rec.api(name, n_ret))
+    sys.modules["flash_attn_npu_" + which] = pkg
+    torch.Tensor.npu = lambda self, *a, **k: self
+    path = os.path.join(ref_root, "tests", f"test_flash_attn_npu_{which}.py")
+    spec = importlib.util.spec_from_file_location(f"ref_tests_{which}", path)
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    return mod
+
+
+def dump(name, rec: Recorder, meta: dict, used_blocks=None):
+    fn, args, kwargs = rec.call
+    arrays, dtypes = {}, {}
+    names = {
+        "flash_attn_with_kvcache": ["q", "k_cache", "v_cache", "k", "v"],
+        "flash_attn_func": ["q", "k", "v", "dropout_p"],
+        "flash_attn_varlen_func": ["q", "k", "v", "cu_seqlens_q", "cu_seqlens_k", "max_seqlen_q", "max_seqlen_k"],
+    }[fn]
+    scalars = {}
+    items = list(zip(names, args)) + list(kwargs.items())
+    for key, val in items:
+        if isinstance(val, torch.Tensor):
+            if used_blocks is not None and key in ("k_cache", "v_cache"):
+                scalars[key + "_num_blocks"] = int(val.shape[0])
+                val = val[:used_blocks]
+            arrays["in_" + key], dtypes["in_" + key] = to_np(val)
+        elif val is None:
+            scalars[key] = None
+        elif isinstance(val, (list, tuple)):
+            scalars[key] = list(val)
+        else:
+            scalars[key] = val
+    arrays["exp_out"], dtypes["exp_out"] = to_np(rec.expected[0])
+    if len(rec.expected) > 1:
+        arrays["exp_lse"], dtypes["exp_lse"] = to_np(rec.expected[1])
+    meta = dict(meta, fn=fn, scalars=scalars, dtypes=dtypes)
+    np.savez_compressed(os.path.join(HERE, name + ".npz"), meta=json.dumps(meta), **arrays)
+    print("wrote", name, {k: v.shape for k, v in arrays.items()})
+
+
+BF, FP = torch.bfloat16, torch.float16
+
+# (name, seed, args of the reference's test_fa_custom_ops)
+KVCACHE_CASES = [
+    # dtype, batch, heads, kv_heads, s_q, s_kv, d, cache_mode, block, causal, wl, wr, softcap
+    ("v2_kvcache_gqa_causal", 11, (BF, 2, 4, 2, 3, 200, 64, 0, 128, True, -1, -1, 0.0)),
+    ("v2_kvcache_paged_decode_mqa", 12, (BF, 2, 4, 1, 1, 256, 128, 1, 128, False, -1, -1, 0.0)),
+    ("v2_kvcache_local_literal", 13, (FP, 1, 2, 2, 64, 192, 64, 0, 128, False, 32, 64, 0.0)),
+    ("v2_kvcache_band_dead_rows", 14, (FP, 2, 1, 1, 128, 128, 64, 0, 128, False, 124, -64, 0.0)),
+    ("v2_kvcache_paged_swa", 15, (BF, 1, 4, 2, 5, 300, 128, 1, 128, True, 100, 0, 0.0)),
+    ("v2_kvcache_softcap", 16, (BF, 1, 8, 2, 6, 256, 64, 0, 128, False, -1, -1, 30.0)),
+]
+FWD_CASES = [
+    # dtype, batch, heads, kv_heads, s_q, s_kv, d, return_attn_probs, causal, softcap
+    ("v2_fwd_causal_fp16", 21, (FP, 2, 4, 4, 128, 128, 64, True, True, 0.0)),
+    ("v2_fwd_gqa_bf16", 22, (BF, 1, 2, 1, 130, 130, 128, True, False, 0.0)),
+    ("v2_fwd_d256_softcap", 23, (BF, 1, 2, 2, 96, 96, 256, True, True, 50.0)),
+]
+VARLEN_CASES = [
+    # dtype, batch, heads, kv_heads, s_q, s_kv, d, causal, wl, wr, softcap
+    ("v2_varlen_causal", 31, (BF, 2, 2, 1, 50, 100, 128, True, -1, -1, 0.0)),
+    ("v2_varlen_d192", 32, (FP, 3, 5, 1, 77, 88, 192, False, -1, -1, 0.0)),
+    ("v2_varlen_d111", 33, (BF, 1, 2, 1, 40, 120, 111, True, -1, -1, 0.0)),
+    ("v2_varlen_swa", 34, (BF, 2, 6, 2, 2, 256, 128, True, 64, 0, 0.0)),
+]
+
+
+def main(ref_root: str):
+    rec = Recorder()
+    torch.testing.assert_close = rec.assert_close
+    mod = load_reference_tests(ref_root, "v2", rec)
+
+    for name, seed, case in KVCACHE_CASES:
+        rec.call, rec.expected = None, []
+        torch.manual_seed(seed)
+        mod.test_fa_custom_ops(*case)
+        used = None
+        if case[7] == 1:
+            used = case[1] * ((case[5] + 127) // 128)
+        dump(name, rec, {"seed": seed, "case": [str(case[0])] + list(case[1:])}, used_blocks=used)
+    for name, seed, case in FWD_CASES:
+        rec.call, rec.expected = None, []
+        torch.manual_seed(seed)
+        mod.test_fa_fwd_custom_ops(*case)
+        dump(name, rec, {"seed": seed, "case": [str(case[0])] + list(case[1:])})
+    for name, seed, case in VARLEN_CASES:
+        rec.call, rec.expected = None, []
+        torch.manual_seed(seed)
+        mod.test_fa_varlen_ops(*case)
+        dump(name, rec, {"seed": seed, "case": [str(case[0])] + list(case[1:])})
+
+    # The first benchmark configuration: fp16, batch 2, s 128, heads 4, d 64, causal,
+    # q, k, v ~ N(0,1) drawn in that order from seed 0, scale 1/8; golden applied per batch
+    # element with the bottom-right causal mask as the reference tests do (:342-346, :350-403).
+    g = torch.Generator().manual_seed(0)
+    q = torch.randn(2, 128, 4, 64, generator=g).to(FP)
+    k = torch.randn(2, 128, 4, 64, generator=g).to(FP)
+    v = torch.randn(2, 128, 4, 64, generator=g).to(FP)
+    mask = torch.triu(torch.ones(128, 128), diagonal=1).bool()
+    outs, lses = [], []
+    for i in range(2):
+        o, l = mod.ref_flash_attention(q[i], k[i], v[i], 1.0 / 8.0, mask, FP, 0.0)
+        outs.append(o.reshape(128, 4, 64))
+        lses.append(l.reshape(4, 128))
+    arrays = {"in_q": q.numpy(), "in_k": k.numpy(), "in_v": v.numpy(),
+              "exp_out": torch.stack(outs).numpy(), "exp_lse": torch.stack(lses).numpy()}
+    meta = {"fn": "flash_attn_func", "seed": 0, "scalars": {"causal": True, "softmax_scale": 0.125},
+            "dtypes": {k_: ("fp32" if k_ == "exp_lse" else "fp16") for k_ in arrays}}
+    np.savez_compressed(os.path.join(HERE, "config1_causal_fp16.npz"), meta=json.dumps(meta), **arrays)
+    print("wrote config1_causal_fp16")
+
+
+if __name__ == "__main__":
+    main(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
