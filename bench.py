@@ -1,0 +1,463 @@
+#!/usr/bin/env python
+"""Benchmark of the attention-forward hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload c2|c3|c4|c5] [--impl reference]
+
+Prints ONE JSON line (rank 0).  Default workload: the causal-prefill configuration the headline
+metric is quoted on (bf16, batch 4, seqlen 4096, 32 heads, head dim 128).  A "step" is one forward
+over one batch of seeded synthetic inputs.
+
+* value        whole-job throughput with inputs resident in HBM, timed with CUDA events on the
+               launching stream (barrier + synchronize on both sides, max over ranks).
+* e2e          the same metric through the public API with HOST (pinned) buffers: host->device copy
+               of q, k, v and device->host copy of O and LSE inside the timed region.
+* roofline     achieved = algorithmic FLOPs (prefill) or bytes (decode) per launch / average kernel
+               time; peak from MEASURED_PEAKS.json (driver-measured on this pool) or the fallback.
+* cpu_baseline the CPU oracle (a port of the reference's PyTorch golden) timed on the host cores on
+               a bounded sample of the same workload.
+With N > 1 (torchrun) every rank runs the same per-GPU workload on its own independent
+(batch x head) units -- no collective on the data path -- so scaling is "weak"; c5 is the one
+workload with an exchange step (sequence-sharded KV, all-gather of the partials + merge).
+"""
+import argparse
+import json
+import math
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, os.path.join(ROOT, "flash-attention-npu_b200"))
+sys.path.insert(0, ROOT)
+
+import torch  # noqa: E402
+
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
+
+
+def load_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            d = json.load(f)
+        d["_source"] = "measured"
+        return d
+    d = dict(FALLBACK_PEAKS)
+    d["_source"] = "fallback"
+    return d
+
+
+class ClockSampler:
+    """Samples nvidia-smi clocks / throttle reasons of one GPU while the timed region runs."""
+    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.index, self.samples, self.proc = index, [], None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", "-i", str(self.index), f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
+                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.samples.append(line.strip())
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        mhz, mx, reasons = [], None, set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for s in self.samples:
+            parts = [x.strip() for x in s.split(",")]
+            if len(parts) < 6:
+                continue
+            try:
+                mhz.append(float(parts[0]))
+                mx = float(parts[1])
+            except ValueError:
+                continue
+            for n, v in zip(names, parts[2:6]):
+                if v.lower().startswith("active"):
+                    reasons.add(n)
+        mhz.sort()
+        # the busiest half of the samples is "under load"
+        load = mhz[len(mhz) // 2:] if mhz else []
+        med = load[len(load) // 2] if load else None
+        return {"sm_mhz": med, "sm_max_mhz": mx, "reasons": sorted(reasons), "samples": len(mhz)}
+
+
+# ------------------------------------------------------------------------------------------------
+# workloads
+# ------------------------------------------------------------------------------------------------
+BF = torch.bfloat16
+
+
+def _pin(t):
+    return t.cpu().pin_memory()
+
+
+class Prefill:
+    """c2: causal prefill, bf16, batch 4, seqlen 4096, 32 heads (MHA), head dim 128."""
+    name, metric, unit, bound = "c2_causal_prefill_b4_s4096_h32_d128", "attn_fwd_causal_prefill_tflops", "TFLOP/s", "tensor"
+    b, s, h, d = 4, 4096, 32, 128
+    scale = 1e-12
+
+    def setup(self, dev, rank, world):
+        g = torch.Generator(device=dev).manual_seed(2 + 1000 * rank)
+        shape = (self.b, self.s, self.h, self.d)
+        self.q, self.k, self.v = [(torch.randn(shape, generator=g, device=dev) / math.sqrt(2)).to(BF) for _ in range(3)]
+        self.units = 4.0 * self.b * self.h * self.s * self.s * self.d / 2  # FLOPs per step (causal convention)
+
+    def setup_e2e(self):
+        self.hq, self.hk, self.hv = _pin(self.q), _pin(self.k), _pin(self.v)
+        self.ho = torch.empty(self.q.shape, dtype=BF).pin_memory()
+        self.hl = torch.empty((self.b, self.h, self.s), dtype=torch.float32).pin_memory()
+        self.h2d = sum(t.numel() * t.element_size() for t in (self.hq, self.hk, self.hv))
+        self.d2h = self.ho.numel() * 2 + self.hl.numel() * 4
+
+    def step(self):
+        import flash_attn_npu_v2 as fa2
+        return fa2.flash_attn_func(self.q, self.k, self.v, causal=True, return_attn_probs=True)
+
+    def step_e2e(self):
+        import flash_attn_npu_v2 as fa2
+        q, k, v = [t.to("cuda", non_blocking=True) for t in (self.hq, self.hk, self.hv)]
+        out, lse, _ = fa2.flash_attn_func(q, k, v, causal=True, return_attn_probs=True)
+        self.ho.copy_(out, non_blocking=True)
+        self.hl.copy_(lse, non_blocking=True)
+
+    launches_per_step = 1
+
+    def cpu_sample(self, budget_s):
+        """Oracle on (1 batch, 4 heads) slices until the time budget is used; returns (units, seconds, text)."""
+        from oracle import api as OA
+        g = torch.Generator().manual_seed(2)
+        done, t_total, n = 0.0, 0.0, 0
+        while t_total < budget_s and n < 32:
+            q, k, v = [(torch.randn((1, self.s, 4, self.d), generator=g) / math.sqrt(2)).to(BF) for _ in range(3)]
+            t0 = time.perf_counter()
+            OA.flash_attn_func(q, k, v, causal=True)
+            t_total += time.perf_counter() - t0
+            done += 4.0 * 1 * 4 * self.s * self.s * self.d / 2
+            n += 1
+        return done, t_total, f"{n} slices of (batch 1, 4 heads, seqlen {self.s}, d {self.d}) causal, bf16"
+
+
+class DecodeBase:
+    metric, unit, bound = "kv_decode_hbm_gbs", "GB/s", "hbm"
+    scale = 1e-9
+
+    def setup_e2e(self):
+        self.hq = _pin(self.q)
+        self.ho = torch.empty(self.q.shape, dtype=BF).pin_memory()
+        self.hl = torch.empty((self.q.shape[0], self.q.shape[2], self.q.shape[1]), dtype=torch.float32).pin_memory()
+        self.h2d = self.hq.numel() * 2
+        self.d2h = self.ho.numel() * 2 + self.hl.numel() * 4
+
+    def step_e2e(self):
+        q = self.hq.to("cuda", non_blocking=True)
+        out, lse = self.run(q)
+        self.ho.copy_(out, non_blocking=True)
+        self.hl.copy_(lse, non_blocking=True)
+
+    def step(self):
+        return self.run(self.q)
+
+
+class DecodeContiguous(DecodeBase):
+    """c3: contiguous KV-cache decode with in-place append + rotary, bf16, batch 64, GQA 32/8, d 128."""
+    name = "c3_contiguous_decode_b64_h32_hk8_d128_cache8192_append_rotary"
+    b, s_cache, h, hk, d = 64, 8192, 32, 8, 128
+
+    def setup(self, dev, rank, world):
+        g = torch.Generator(device=dev).manual_seed(3 + 1000 * rank)
+        self.kc = torch.randn((self.b, self.s_cache, self.hk, self.d), generator=g, device=dev).to(BF)
+        self.vc = torch.randn((self.b, self.s_cache, self.hk, self.d), generator=g, device=dev).to(BF)
+        self.q = torch.randn((self.b, 1, self.h, self.d), generator=g, device=dev).to(BF)
+        self.kn = torch.randn((self.b, 1, self.hk, self.d), generator=g, device=dev).to(BF)
+        self.vn = torch.randn((self.b, 1, self.hk, self.d), generator=g, device=dev).to(BF)
+        self.lens = torch.randint(1024, 8192, (self.b,), generator=g, device=dev, dtype=torch.int32)
+        inv = 10000.0 ** (-torch.arange(0, 128, 2, dtype=torch.float32) / 128)
+        ang = torch.arange(8192, dtype=torch.float32).view(-1, 1) * inv.view(1, -1)
+        self.cos, self.sin = torch.cos(ang).to(BF).to(dev), torch.sin(ang).to(BF).to(dev)
+        row = self.hk * self.d * 2 * 2
+        self.units = float((self.lens.long() + 1).sum()) * row + 2 * self.b * self.h * self.d * 2 \
+            + 2 * self.b * row + self.b * self.h * 4 + self.b * 4 + 2 * self.b * 64 * 2
+        self.launches_per_step = 2
+
+    def setup_e2e(self):
+        super().setup_e2e()
+        self.hkn, self.hvn = _pin(self.kn), _pin(self.vn)
+        self.h2d += self.hkn.numel() * 2 * 2
+
+    def run(self, q, kn=None, vn=None):
+        import flash_attn_npu_v2 as fa2
+        return fa2.flash_attn_with_kvcache(q, self.kc, self.vc, self.kn if kn is None else kn,
+                                           self.vn if vn is None else vn, rotary_cos=self.cos, rotary_sin=self.sin,
+                                           cache_seqlens=self.lens, causal=True, rotary_interleaved=False,
+                                           return_softmax_lse=True)
+
+    def step_e2e(self):
+        q, kn, vn = [t.to("cuda", non_blocking=True) for t in (self.hq, self.hkn, self.hvn)]
+        out, lse = self.run(q, kn, vn)
+        self.ho.copy_(out, non_blocking=True)
+        self.hl.copy_(lse, non_blocking=True)
+
+    def cpu_sample(self, budget_s):
+        from oracle import api as OA
+        done, t_total, n = 0.0, 0.0, 0
+        lens = self.lens.cpu()
+        cos, sin = self.cos.cpu(), self.sin.cpu()
+        while t_total < budget_s and n < self.b:
+            kc, vc = self.kc[n:n + 1].cpu(), self.vc[n:n + 1].cpu()
+            q, kn, vn = self.q[n:n + 1].cpu(), self.kn[n:n + 1].cpu(), self.vn[n:n + 1].cpu()
+            t0 = time.perf_counter()
+            OA.flash_attn_with_kvcache(q, kc, vc, kn, vn, rotary_cos=cos, rotary_sin=sin, cache_seqlens=lens[n:n + 1],
+                                       causal=True, rotary_interleaved=False)
+            t_total += time.perf_counter() - t0
+            done += (int(lens[n]) + 1) * self.hk * self.d * 4
+            n += 1
+        return done, t_total, f"first {n} of {self.b} sequences (K/V bytes attended)"
+
+
+class DecodePaged(DecodeBase):
+    """c4: paged speculative decode, bf16, batch 32, s_q 4, GQA 64/8, d 128, page 256, window (4096, 0)."""
+    name = "c4_paged_decode_b32_sq4_h64_hk8_d128_page256_window4096"
+    b, s_q, h, hk, d, page, nblk = 32, 4, 64, 8, 128, 256, 4096
+
+    def setup(self, dev, rank, world):
+        g = torch.Generator(device=dev).manual_seed(4 + 1000 * rank)
+        self.kp = torch.randn((self.nblk, self.page, self.hk, self.d), generator=g, device=dev).to(BF)
+        self.vp = torch.randn((self.nblk, self.page, self.hk, self.d), generator=g, device=dev).to(BF)
+        self.bt = torch.randperm(self.nblk, generator=g, device=dev).view(self.b, 128).to(torch.int32)
+        self.lens = torch.randint(512, 32769, (self.b,), generator=g, device=dev, dtype=torch.int32)
+        self.q = torch.randn((self.b, self.s_q, self.h, self.d), generator=g, device=dev).to(BF)
+        n_b = torch.clamp(self.lens.long(), max=4096 + self.s_q)
+        self.units = float(n_b.sum()) * self.hk * self.d * 4 + 2 * self.q.numel() * 2 + self.b * self.h * self.s_q * 4
+        self.launches_per_step = 2
+
+    def run(self, q):
+        import flash_attn_npu_v2 as fa2
+        return fa2.flash_attn_with_kvcache(q, self.kp, self.vp, cache_seqlens=self.lens, block_table=self.bt,
+                                           causal=True, window_size=(4096, 0), return_softmax_lse=True)
+
+    def cpu_sample(self, budget_s):
+        from oracle import api as OA
+        done, t_total, n = 0.0, 0.0, 0
+        kp, vp, bt, lens = self.kp.cpu(), self.vp.cpu(), self.bt.cpu(), self.lens.cpu()
+        while t_total < budget_s and n < self.b:
+            q = self.q[n:n + 1].cpu()
+            t0 = time.perf_counter()
+            OA.flash_attn_with_kvcache(q, kp, vp, cache_seqlens=lens[n:n + 1], block_table=bt[n:n + 1], causal=True,
+                                       window_size=(4096, 0))
+            t_total += time.perf_counter() - t0
+            done += min(int(lens[n]), 4096 + self.s_q) * self.hk * self.d * 4
+            n += 1
+        return done, t_total, f"first {n} of {self.b} sequences (in-window K/V bytes; the golden reads whole sequences)"
+
+
+class DecodeLongSharded(DecodeBase):
+    """c5: long-context decode, bf16, batch 8, s_q 1, GQA 64/8, d 128, 131072 keys per sequence split
+    evenly over the ranks; partial (O, LSE) all-gathered and merged on every rank."""
+    name = "c5_long_decode_b8_h64_hk8_d128_L131072_seqsharded"
+    b, L, h, hk, d = 8, 131072, 64, 8, 128
+    strong = True
+
+    def setup(self, dev, rank, world):
+        from flash_b200 import dist as D
+        self.world = world
+        self.lo, self.hi = D.kv_shard_range(self.L, world, rank)
+        g = torch.Generator(device=dev).manual_seed(5)
+        self.q = torch.randn((self.b, 1, self.h, self.d), generator=g, device=dev).to(BF)
+        g2 = torch.Generator(device=dev).manual_seed(50 + rank)
+        n = self.hi - self.lo
+        self.kc = torch.randn((self.b, n, self.hk, self.d), generator=g2, device=dev).to(BF)
+        self.vc = torch.randn((self.b, n, self.hk, self.d), generator=g2, device=dev).to(BF)
+        self.units = float(self.b) * n * self.hk * self.d * 4 + 264192
+        self.launches_per_step = 3
+
+    def run(self, q):
+        from flash_b200 import dist as D
+        return D.sharded_decode(q, self.kc, self.vc, kv_pos_offset=self.lo, kv_total=self.L, causal=True)
+
+    def cpu_sample(self, budget_s):
+        from oracle import api as OA
+        n_tok = 16384
+        kc, vc, q = self.kc[:1, :n_tok].cpu(), self.vc[:1, :n_tok].cpu(), self.q[:1].cpu()
+        done, t_total, n = 0.0, 0.0, 0
+        while t_total < budget_s and n < 8:
+            t0 = time.perf_counter()
+            OA.flash_attn_with_kvcache(q, kc, vc, cache_seqlens=n_tok, causal=True)
+            t_total += time.perf_counter() - t0
+            done += n_tok * self.hk * self.d * 4
+            n += 1
+        return done, t_total, f"{n} passes over the first {n_tok} keys of sequence 0"
+
+
+WORKLOADS = {"c2": Prefill, "c3": DecodeContiguous, "c4": DecodePaged, "c5": DecodeLongSharded}
+
+
+# ------------------------------------------------------------------------------------------------
+# driver
+# ------------------------------------------------------------------------------------------------
+def run_reference(args, rank, world):
+    """--impl reference: the reference's CPU implementation of the path (its PyTorch golden, here the
+    oracle port -- the reference's native code needs the Ascend toolchain) on the host cores."""
+    if rank != 0:
+        return
+    torch.set_num_threads(os.cpu_count() or 1)
+    # The CPU arm always times the prefill configuration (the headline metric); the decode workloads
+    # build multi-GiB caches on the device and have their own cpu_baseline leg in the default arm.
+    target = Prefill()
+    budget = 2.0
+    if args.warmup > 0:
+        target.cpu_sample(0.5)
+    done, secs, sample = 0.0, 0.0, ""
+    for _ in range(args.steps):
+        d, s, sample = target.cpu_sample(budget)
+        done += d
+        secs += s
+    val = done / secs * target.scale
+    line = {"impl": "reference", "metric": target.metric, "value": val, "unit": target.unit, "n_gpus": args.gpus,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": secs / args.steps * 1e3,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": target.name, "note": "CPU golden (oracle port) on host cores; each step a bounded sample"},
+            "cpu_baseline": {"value": val, "unit": target.unit, "cores": torch.get_num_threads(), "kind": "port",
+                             "sample": sample + f", x{args.steps} steps"},
+            "e2e": {"value": val, "unit": target.unit, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+            "gpu_launches": 0}
+    print(json.dumps(line))
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS))
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--cpu-budget", type=float, default=12.0)
+    args = ap.parse_args()
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.impl == "reference":
+        run_reference(args, rank, world)
+        return
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device (there is no CPU implementation of the product path)")
+    args.warmup = max(args.warmup, 3)
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    import torch.distributed as dist
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    wl = WORKLOADS[args.workload]()
+    wl.setup(dev, rank, world)
+    peaks = load_peaks()
+
+    # ---- device-resident timing ----
+    for _ in range(args.warmup):
+        wl.step()
+    barrier()
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    stream = torch.cuda.current_stream()
+    ev = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps + 1)]
+    barrier()
+    ev[0].record(stream)
+    for i in range(args.steps):
+        wl.step()
+        ev[i + 1].record(stream)
+    barrier()
+    total_ms = ev[0].elapsed_time(ev[-1])
+    per = sorted(ev[i].elapsed_time(ev[i + 1]) for i in range(args.steps))
+    # keep the GPU busy a little longer so the clock sampler sees load even for short runs
+    t_end = time.time() + 0.6
+    while rank == 0 and time.time() < t_end:
+        wl.step()
+    torch.cuda.synchronize()
+    clocks = sampler.stop() if rank == 0 else None
+
+    # ---- end-to-end timing (host buffers) ----
+    wl.setup_e2e()
+    for _ in range(3):
+        wl.step_e2e()
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record(stream)
+    for _ in range(args.steps):
+        wl.step_e2e()
+    e1.record(stream)
+    barrier()
+    e2e_ms = e0.elapsed_time(e1)
+
+    t = torch.tensor([total_ms, e2e_ms, wl.units], dtype=torch.float64, device=dev)
+    if world > 1:
+        tmax = t.clone()
+        dist.all_reduce(tmax, op=dist.ReduceOp.MAX)
+        tsum = t.clone()
+        dist.all_reduce(tsum, op=dist.ReduceOp.SUM)
+        total_ms, e2e_ms, units_all = float(tmax[0]), float(tmax[1]), float(tsum[2])
+    else:
+        units_all = wl.units
+    if rank == 0:
+        value = units_all * args.steps / (total_ms * 1e-3) * wl.scale
+        e2e = units_all * args.steps / (e2e_ms * 1e-3) * wl.scale
+        med_ms = per[len(per) // 2]
+        achieved = wl.units / (total_ms / args.steps * 1e-3) * wl.scale
+        if wl.bound == "tensor":
+            peak = peaks["bf16_tflops"] if total_ms < 1000 else peaks.get("bf16_tflops_sustained", peaks["bf16_tflops"])
+            runit = "TFLOP/s"
+        else:
+            peak, runit = peaks["hbm_gbs"], "GB/s"
+        strong = getattr(wl, "strong", False)
+        line = {
+            "metric": wl.metric, "value": value, "unit": wl.unit, "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": total_ms / args.steps, "higher_is_better": True,
+            "scaling": "strong" if strong else "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": wl.name, "l2": "inputs larger than L2 (no flush needed)" if args.workload != "c2"
+                       else "q+k+v+o = 537 MB per step, larger than the 126 MB L2", "median_ms_per_step": med_ms,
+                       "per_gpu_units": wl.units},
+            "roofline": {"bound": wl.bound, "achieved": achieved, "peak": peak, "unit": runit,
+                         "frac": achieved / peak, "traffic": None, "peak_source": peaks["_source"],
+                         "per_launch": "one attention launch per step" + (" (+ merge)" if wl.launches_per_step > 1 else "")},
+            "e2e": {"value": e2e, "unit": wl.unit, "h2d_bytes_per_step": wl.h2d, "d2h_bytes_per_step": wl.d2h},
+            "gpu_launches": wl.launches_per_step * args.steps,
+            "clocks": clocks,
+        }
+        if not args.no_cpu_baseline and world == 1:
+            torch.set_num_threads(os.cpu_count() or 1)
+            done, secs, sample = wl.cpu_sample(args.cpu_budget)
+            line["cpu_baseline"] = {"value": done / secs * wl.scale, "unit": wl.unit, "cores": torch.get_num_threads(),
+                                    "kind": "port", "sample": sample, "seconds": secs}
+        print(json.dumps(line))
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,317 @@
+// Host side of the C ABI: validation, window normalisation, tile / split planning and the
+// kernel launches.  Replaces the host functions mha_fwd / mha_varlen_fwd / mha_fwd_kvcache of
+// the reference (csrc/arch22/flash_attn_npu_v2/flash_api.cpp:356-1060) -- without their
+// per-call device-to-host copy of the sequence lengths (:459), mask upload (:575-579) or
+// tiling upload (:580): lengths are read on the device and masks are computed from indices.
+#include <cuda_runtime.h>
+
+#include <algorithm>
+#include <cstdio>
+#include <cstring>
+#include <string>
+
+#include "combine.cuh"
+#include "mma_configs.cuh"
+#include "tc5_api.cuh"
+
+namespace fa {
+
+static thread_local std::string g_err;
+
+static int fail(int code, const std::string& msg) {
+  g_err = msg;
+  return code;
+}
+
+static int device_sm_count() {
+  static int cached[64] = {0};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return 0;
+  if (dev < 0 || dev >= 64) return 0;
+  if (cached[dev] == 0) {
+    int n = 0;
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) return 0;
+    cached[dev] = n;
+  }
+  return cached[dev];
+}
+
+static void normalize_window(int seqlen_q, int max_k, bool causal, int& wl, int& wr, bool& is_causal, bool& is_local) {
+  // csrc/arch22/flash_attn_npu_v2/flash_api.cpp:483-494
+  if (max_k > 0 && wl >= max_k - 1) wl = -1;
+  if (seqlen_q > 0 && wr >= seqlen_q - 1) wr = -1;
+  if (causal) wr = 0;
+  is_causal = (wl < 0 && wr == 0);
+  is_local = (wl >= 0 || wr >= 0) && !is_causal;
+}
+
+struct Planned {
+  fa_fwd_plan pl;
+  KParams kp;
+  int hd_pad;
+};
+
+static int make_plan(const fa_fwd_params& a, Planned* out) {
+  std::memset(out, 0, sizeof(*out));
+  if (a.b <= 0) return fail(FA_ERR_INVALID, "batch size must be positive");
+  if (a.dtype != FA_FP16 && a.dtype != FA_BF16) return fail(FA_ERR_INVALID, "FlashAttention only supports FP16 and BF16 data types");
+  if (a.d <= 0 || a.d > 256) return fail(FA_ERR_INVALID, "FlashAttention only supports head dimension at most 256");
+  if (a.d % 8 != 0) return fail(FA_ERR_INVALID, "head dimension must be a multiple of 8 (pad it on the caller side)");
+  if (a.h <= 0 || a.h_k <= 0 || a.h % a.h_k != 0)
+    return fail(FA_ERR_INVALID, "Number of heads in key/value must divide number of heads in query");
+  if (a.seqlen_q < 0 || a.seqlen_k < 0) return fail(FA_ERR_INVALID, "negative sequence length");
+  if (a.softcap < 0.f) return fail(FA_ERR_INVALID, "softcap must be non-negative (0.0 disables softcap)");
+  if (a.num_splits < 0) return fail(FA_ERR_INVALID, "num_splits must be >= 0");
+  if (a.block_table && a.page_size <= 0) return fail(FA_ERR_INVALID, "paged KV cache needs page_size > 0");
+  if (a.block_table && a.cu_seqlens_k) return fail(FA_ERR_INVALID, "block_table cannot be combined with cu_seqlens_k");
+  if (a.block_table && !a.seqused_k) return fail(FA_ERR_INVALID, "paged KV cache needs the per-sequence key lengths");
+  if ((a.k_new != nullptr) != (a.v_new != nullptr)) return fail(FA_ERR_INVALID, "k and v must be passed together");
+  if (a.k_new && a.seqlen_new <= 0) return fail(FA_ERR_INVALID, "seqlen_new must be positive when k, v are given");
+  if (!a.k_new && a.seqlen_new != 0) return fail(FA_ERR_INVALID, "seqlen_new given without k, v");
+  if (a.k_new && !a.seqused_k) return fail(FA_ERR_INVALID, "appending k, v needs cache_seqlens");
+  if ((a.rotary_cos != nullptr) != (a.rotary_sin != nullptr)) return fail(FA_ERR_INVALID, "rotary_cos and rotary_sin must be passed together");
+  if (a.rotary_cos) {
+    if (!a.k_new) return fail(FA_ERR_INVALID, "rotary embedding is only applied together with new k, v");
+    if (a.rotary_dim <= 0 || a.rotary_dim % 16 != 0 || a.rotary_dim > a.d)
+      return fail(FA_ERR_INVALID, "rotary_dim must be divisible by 16 and at most the head dimension");
+  }
+  if (a.kv_total < 0 || a.kv_pos_offset < 0) return fail(FA_ERR_INVALID, "negative kv shard position");
+
+  const int s_new = a.seqlen_new;
+  const int max_k_bound = a.seqlen_k + s_new;
+  const int group = a.h / a.h_k;
+  const int hd_pad = a.d <= 64 ? 64 : (a.d <= 128 ? 128 : 256);
+  out->hd_pad = hd_pad;
+
+  // ---- window normalisation ----
+  int wl = a.window_left, wr = a.window_right;
+  bool is_causal = false, is_local = false;
+  int wl_on_device = 0;
+  {
+    int max_k = -1;
+    if (!a.seqused_k) max_k = max_k_bound;  // dense: s_k; varlen: max_seqlen_k
+    else if (a.max_seqlen_k_known >= 0) max_k = a.max_seqlen_k_known + s_new;
+    if (a.kv_total > 0) max_k = a.kv_total;
+    if (max_k < 0) {
+      // Unknown on the host.  If the window already covers the largest possible length the rule
+      // fires for certain; otherwise the kernel applies it from the device-side maximum.
+      if (wl >= 0 && wl >= max_k_bound - 1) max_k = max_k_bound;
+      else if (wl >= 0) wl_on_device = 1;
+      if (max_k < 0) max_k = 0;  // leaves wl untouched below
+    }
+    normalize_window(a.seqlen_q, max_k, a.causal != 0, wl, wr, is_causal, is_local);
+  }
+
+  // ---- tile shape ----
+  const bool pack = group > 1 && a.seqlen_q < 64;
+  const int gp = pack ? group : 1;
+  const int rows_max = a.seqlen_q * gp;
+  int cfg = rows_max <= 16 ? 0 : (rows_max <= 32 ? 1 : (pack ? 2 : 3));
+  MmaConfigInfo ci;
+  if (!mma_config_info(hd_pad, cfg, &ci)) return fail(FA_ERR_UNSUPPORTED, "no tile configuration");
+  const int m_blocks = std::max(1, ceil_div(rows_max, ci.block_m));
+  const int heads_eff = a.h / gp;
+
+  // ---- KV range bound and splits ----
+  int range = max_k_bound;
+  if (is_local && wl >= 0) {
+    const int i_span = ceil_div(ci.block_m, gp);
+    const long long r = (long long)wl + std::max(wr, 0) + i_span + 1;
+    if (r < range) range = (int)r;
+  }
+  int max_blocks = std::min(ceil_div(range, ci.block_n) + 1, std::max(1, ceil_div(max_k_bound, ci.block_n)));
+  if (max_blocks < 1) max_blocks = 1;
+  int num_sm = a.num_sm > 0 ? a.num_sm : device_sm_count();
+  if (num_sm <= 0) return fail(FA_ERR_CUDA, "cannot query the SM count of the current device");
+  const long long base = (long long)m_blocks * heads_eff * a.b;
+  int ns = 1;
+  if (a.num_splits >= 1) {
+    ns = std::min(a.num_splits, max_blocks);
+  } else if (base < 8LL * num_sm && max_blocks >= 16) {
+    long long want = (16LL * num_sm + base - 1) / base;
+    ns = (int)std::max(1LL, std::min<long long>(want, max_blocks / 8));
+  }
+  int bps = ceil_div(max_blocks, ns);
+  ns = ceil_div(max_blocks, bps);
+
+  const bool varlen_q = a.cu_seqlens_q != nullptr;
+  const int64_t lse_elems = varlen_q ? (int64_t)a.h * a.total_q : (int64_t)a.b * a.h * a.seqlen_q;
+  if (ns > 1) {
+    const bool canonical = varlen_q ? (a.lse_head_stride == a.total_q)
+                                    : (a.lse_batch_stride == (int64_t)a.h * a.seqlen_q && a.lse_head_stride == a.seqlen_q);
+    if (!canonical) { ns = 1; bps = max_blocks; }
+  }
+
+  fa_fwd_plan& pl = out->pl;
+  pl.kernel = FA_KERNEL_MMA;
+  pl.config = cfg;
+  pl.pack_gqa = pack;
+  pl.block_m = ci.block_m;
+  pl.block_n = ci.block_n;
+  pl.m_blocks = m_blocks;
+  pl.num_splits = ns;
+  pl.blocks_per_split = bps;
+  pl.grid = (int)(base * ns);
+  pl.threads = ci.threads;
+  pl.smem_bytes = ci.smem_bytes;
+  pl.is_causal = is_causal;
+  pl.is_local = is_local;
+  pl.window_left = wl;
+  pl.window_right = wr;
+  pl.launches = ns > 1 ? 2 : 1;
+  pl.workspace_bytes = ns > 1 ? (((size_t)ns * lse_elems * sizeof(float) + 15) & ~(size_t)15) + (size_t)ns * lse_elems * a.d * sizeof(float) : 0;
+  if (base * ns > 0x7fffffffLL) return fail(FA_ERR_UNSUPPORTED, "grid too large");
+
+  KParams& kp = out->kp;
+  kp.a = a;
+  kp.causal_in = a.causal;
+  kp.wl = wl;
+  kp.wr = wr;
+  kp.wl_on_device = wl_on_device;
+  kp.group = group;
+  kp.gp = gp;
+  kp.heads_eff = heads_eff;
+  kp.m_blocks = m_blocks;
+  kp.num_splits = ns;
+  kp.blocks_per_split = bps;
+  kp.scale_log2 = a.softmax_scale * kLog2e;
+  kp.lse_elems = lse_elems;
+
+  // ---- tcgen05 prefill kernel eligibility ----
+  if (a.kernel != FA_KERNEL_MMA && tc5_eligible(a, is_causal, is_local, wl_on_device)) {
+    tc5_fill_plan(a, &pl);
+  } else if (a.kernel == FA_KERNEL_TCGEN05) {
+    return fail(FA_ERR_UNSUPPORTED, "the tcgen05 kernel does not cover this problem");
+  }
+  return FA_OK;
+}
+
+static int launch_combine(const fa_combine_params& c, cudaStream_t st) {
+  const int64_t rows = (int64_t)c.b * c.s * c.h;
+  if (rows == 0) return FA_OK;
+  const int grid = (int)((rows + kCombineWarps - 1) / kCombineWarps);
+  if (c.out_dtype == FA_BF16) combine_kernel<__nv_bfloat16><<<grid, kCombineWarps * 32, 0, st>>>(c);
+  else if (c.out_dtype == FA_FP16) combine_kernel<__half><<<grid, kCombineWarps * 32, 0, st>>>(c);
+  else if (c.out_dtype == 2) combine_kernel<float><<<grid, kCombineWarps * 32, 0, st>>>(c);
+  else return fail(FA_ERR_INVALID, "bad out_dtype");
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return fail(FA_ERR_CUDA, std::string("combine launch: ") + cudaGetErrorString(e));
+  return FA_OK;
+}
+
+static int run_fwd(const fa_fwd_params& a, void* workspace, size_t workspace_bytes, cudaStream_t st) {
+  if (!a.q || !a.k || !a.v || !a.o || !a.lse) return fail(FA_ERR_INVALID, "q, k, v, o and lse must be non-null");
+  Planned P;
+  int rc = make_plan(a, &P);
+  if (rc != FA_OK) return rc;
+  if (a.total_q == 0 || a.seqlen_q == 0) return FA_OK;
+  if (P.pl.kernel == FA_KERNEL_TCGEN05) return tc5_launch(a, P.pl, st, &g_err);
+
+  KParams& kp = P.kp;
+  if (P.pl.num_splits > 1) {
+    if (!workspace || workspace_bytes < P.pl.workspace_bytes) return fail(FA_ERR_WORKSPACE, "workspace missing or too small");
+    if ((reinterpret_cast<uintptr_t>(workspace) & 15) != 0) return fail(FA_ERR_WORKSPACE, "workspace must be 16-byte aligned");
+    kp.lse_partial = reinterpret_cast<float*>(workspace);
+    // O partials start at a 16-byte boundary after the LSE partials
+    const size_t lse_bytes = ((size_t)P.pl.num_splits * kp.lse_elems * sizeof(float) + 15) & ~(size_t)15;
+    kp.o_partial = reinterpret_cast<float*>(reinterpret_cast<char*>(workspace) + lse_bytes);
+  }
+  cudaError_t e = cudaErrorInvalidValue;
+  const bool bf = a.dtype == FA_BF16;
+  switch (P.hd_pad) {
+    case 64: e = bf ? launch_mma_64_bf16(P.pl.config, kp, P.pl.grid, st) : launch_mma_64_fp16(P.pl.config, kp, P.pl.grid, st); break;
+    case 128: e = bf ? launch_mma_128_bf16(P.pl.config, kp, P.pl.grid, st) : launch_mma_128_fp16(P.pl.config, kp, P.pl.grid, st); break;
+    case 256: e = bf ? launch_mma_256_bf16(P.pl.config, kp, P.pl.grid, st) : launch_mma_256_fp16(P.pl.config, kp, P.pl.grid, st); break;
+  }
+  if (e != cudaSuccess) return fail(FA_ERR_CUDA, std::string("attention kernel launch: ") + cudaGetErrorString(e));
+
+  if (P.pl.num_splits > 1) {
+    fa_combine_params c;
+    std::memset(&c, 0, sizeof(c));
+    const bool varlen_q = a.cu_seqlens_q != nullptr;
+    c.o_partial = kp.o_partial;
+    c.lse_partial = kp.lse_partial;
+    c.o = a.o;
+    c.lse = a.lse;
+    c.num_splits = P.pl.num_splits;
+    c.b = varlen_q ? 1 : a.b;
+    c.s = varlen_q ? a.total_q : a.seqlen_q;
+    c.h = a.h;
+    c.d = a.d;
+    c.lp_split_stride = kp.lse_elems;
+    c.lp_batch_stride = a.lse_batch_stride;
+    c.lp_row_stride = 1;
+    c.lp_head_stride = a.lse_head_stride;
+    c.op_split_stride = kp.lse_elems * a.d;
+    c.op_batch_stride = a.lse_batch_stride * a.d;
+    c.op_row_stride = a.d;
+    c.op_head_stride = a.lse_head_stride * a.d;
+    c.o_batch_stride = varlen_q ? 0 : a.o_batch_stride;
+    c.o_row_stride = a.o_row_stride;
+    c.o_head_stride = a.o_head_stride;
+    c.lse_batch_stride = a.lse_batch_stride;
+    c.lse_row_stride = 1;
+    c.lse_head_stride = a.lse_head_stride;
+    c.out_dtype = a.partial_out ? 2 : a.dtype;
+    c.partial_out = a.partial_out;
+    return launch_combine(c, st);
+  }
+  return FA_OK;
+}
+
+}  // namespace fa
+
+extern "C" {
+
+int fa_b200_fwd(const fa_fwd_params* p, void* workspace, size_t workspace_bytes, void* stream) {
+  if (!p) return fa::fail(FA_ERR_INVALID, "null params");
+  fa::g_err.clear();
+  return fa::run_fwd(*p, workspace, workspace_bytes, reinterpret_cast<cudaStream_t>(stream));
+}
+
+int fa_b200_fwd_plan(const fa_fwd_params* p, fa_fwd_plan* plan) {
+  if (!p || !plan) return fa::fail(FA_ERR_INVALID, "null argument");
+  fa::g_err.clear();
+  fa::Planned P;
+  int rc = fa::make_plan(*p, &P);
+  if (rc == FA_OK) *plan = P.pl;
+  return rc;
+}
+
+int fa_b200_combine(const fa_combine_params* p, void* stream) {
+  if (!p) return fa::fail(FA_ERR_INVALID, "null params");
+  fa::g_err.clear();
+  if (!p->o_partial || !p->lse_partial || !p->o) return fa::fail(FA_ERR_INVALID, "o_partial, lse_partial and o must be non-null");
+  if (p->num_splits <= 0 || p->d <= 0 || p->d % 4 != 0) return fa::fail(FA_ERR_INVALID, "bad num_splits or head dimension");
+  return fa::launch_combine(*p, reinterpret_cast<cudaStream_t>(stream));
+}
+
+int fa_b200_normalize_window(int32_t seqlen_q, int32_t max_seqlen_k, int32_t causal, int32_t* window_left,
+                             int32_t* window_right, int32_t* is_causal, int32_t* is_local) {
+  if (!window_left || !window_right || !is_causal || !is_local) return fa::fail(FA_ERR_INVALID, "null argument");
+  int wl = *window_left, wr = *window_right;
+  bool c = false, l = false;
+  fa::normalize_window(seqlen_q, max_seqlen_k, causal != 0, wl, wr, c, l);
+  *window_left = wl;
+  *window_right = wr;
+  *is_causal = c;
+  *is_local = l;
+  return FA_OK;
+}
+
+const char* fa_b200_last_error(void) { return fa::g_err.c_str(); }
+
+const char* fa_b200_status_string(int status) {
+  switch (status) {
+    case FA_OK: return "ok";
+    case FA_ERR_INVALID: return "invalid argument";
+    case FA_ERR_UNSUPPORTED: return "unsupported";
+    case FA_ERR_CUDA: return "CUDA error";
+    case FA_ERR_WORKSPACE: return "workspace missing or too small";
+  }
+  return "unknown status";
+}
+
+int fa_b200_abi_version(void) { return FA_B200_ABI_VERSION; }
+
+}  // extern "C"

@@ -1,0 +1,120 @@
+"""ctypes binding of libfa_b200.so (the C ABI declared in include/fa_b200.h).
+
+The library is loaded from the package directory; there is no fallback of any kind:
+if the shared object is missing the import raises, so a GPU box can never silently
+run something else.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+
+_PKG = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+LIB_PATH = os.path.join(_PKG, "libfa_b200.so")
+
+FA_OK = 0
+FA_FP16, FA_BF16, FA_FP32_OUT = 0, 1, 2
+KERNEL_AUTO, KERNEL_MMA, KERNEL_TCGEN05 = 0, 1, 2
+
+_p = C.c_void_p
+_i64 = C.c_int64
+_i32 = C.c_int32
+
+
+class FwdParams(C.Structure):
+    """Mirror of ``fa_fwd_params`` (include/fa_b200.h); field order is the ABI."""
+    _fields_ = (
+        [(n, _p) for n in (
+            "q", "k", "v", "o", "lse", "k_new", "v_new", "cu_seqlens_q", "cu_seqlens_k", "seqused_k",
+            "cache_batch_idx", "block_table", "rotary_cos", "rotary_sin", "alibi_slopes")]
+        + [(n, _i64) for n in (
+            "q_batch_stride", "q_row_stride", "q_head_stride",
+            "k_batch_stride", "k_row_stride", "k_head_stride",
+            "v_batch_stride", "v_row_stride", "v_head_stride",
+            "o_batch_stride", "o_row_stride", "o_head_stride",
+            "knew_batch_stride", "knew_row_stride", "knew_head_stride",
+            "vnew_batch_stride", "vnew_row_stride", "vnew_head_stride",
+            "lse_batch_stride", "lse_head_stride",
+            "block_table_batch_stride", "alibi_batch_stride")]
+        + [(n, _i32) for n in (
+            "b", "seqlen_q", "seqlen_k", "h", "h_k", "d", "total_q", "seqlen_new", "page_size",
+            "rotary_dim", "rotary_seqlen", "rotary_interleaved", "dtype",
+            "causal", "window_left", "window_right", "max_seqlen_k_known",
+            "kv_pos_offset", "kv_total", "partial_out",
+            "num_splits", "kernel", "num_sm")]
+        + [("softmax_scale", C.c_float), ("softcap", C.c_float)]
+    )
+
+
+class FwdPlan(C.Structure):
+    """Mirror of ``fa_fwd_plan``."""
+    _fields_ = [(n, _i32) for n in (
+        "kernel", "config", "pack_gqa", "block_m", "block_n", "m_blocks", "num_splits", "blocks_per_split",
+        "grid", "threads", "smem_bytes", "is_causal", "is_local", "window_left", "window_right", "launches")] + [
+        ("workspace_bytes", C.c_size_t)]
+
+
+class CombineParams(C.Structure):
+    """Mirror of ``fa_combine_params``."""
+    _fields_ = (
+        [(n, _p) for n in ("o_partial", "lse_partial", "o", "lse")]
+        + [(n, _i64) for n in (
+            "op_split_stride", "op_batch_stride", "op_row_stride", "op_head_stride",
+            "lp_split_stride", "lp_batch_stride", "lp_row_stride", "lp_head_stride",
+            "o_batch_stride", "o_row_stride", "o_head_stride",
+            "lse_batch_stride", "lse_row_stride", "lse_head_stride")]
+        + [(n, _i32) for n in ("num_splits", "b", "s", "h", "d", "out_dtype", "partial_out")]
+    )
+
+
+# every symbol include/fa_b200.h declares
+EXPORTS = (
+    "fa_b200_fwd", "fa_b200_fwd_plan", "fa_b200_combine", "fa_b200_normalize_window",
+    "fa_b200_last_error", "fa_b200_status_string", "fa_b200_abi_version",
+)
+
+_lib = None
+
+
+def load() -> C.CDLL:
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not os.path.exists(LIB_PATH):
+        raise ImportError(
+            f"{LIB_PATH} is missing: build it with `python flash-attention-npu_b200/build.py` "
+            "(there is no fallback implementation)")
+    lib = C.CDLL(LIB_PATH)
+    lib.fa_b200_fwd.argtypes = [C.POINTER(FwdParams), _p, C.c_size_t, _p]
+    lib.fa_b200_fwd.restype = C.c_int
+    lib.fa_b200_fwd_plan.argtypes = [C.POINTER(FwdParams), C.POINTER(FwdPlan)]
+    lib.fa_b200_fwd_plan.restype = C.c_int
+    lib.fa_b200_combine.argtypes = [C.POINTER(CombineParams), _p]
+    lib.fa_b200_combine.restype = C.c_int
+    lib.fa_b200_normalize_window.argtypes = [_i32, _i32, _i32] + [C.POINTER(_i32)] * 4
+    lib.fa_b200_normalize_window.restype = C.c_int
+    lib.fa_b200_last_error.restype = C.c_char_p
+    lib.fa_b200_status_string.argtypes = [C.c_int]
+    lib.fa_b200_status_string.restype = C.c_char_p
+    lib.fa_b200_abi_version.restype = C.c_int
+    if lib.fa_b200_abi_version() != 1:
+        raise ImportError("libfa_b200.so ABI version mismatch")
+    _lib = lib
+    return lib
+
+
+def check(status: int) -> None:
+    """Non-zero status -> RuntimeError, the error convention of the reference's TORCH_CHECK."""
+    if status != FA_OK:
+        lib = load()
+        msg = lib.fa_b200_last_error().decode() or lib.fa_b200_status_string(status).decode()
+        raise RuntimeError(msg)
+
+
+def normalize_window(seqlen_q: int, max_seqlen_k: int, causal: bool, wl: int, wr: int):
+    """Host-only; returns (is_causal, is_local, wl, wr)."""
+    lib = load()
+    a, b, c, d = _i32(wl), _i32(wr), _i32(0), _i32(0)
+    check(lib.fa_b200_normalize_window(seqlen_q, max_seqlen_k, int(bool(causal)), C.byref(a), C.byref(b),
+                                       C.byref(c), C.byref(d)))
+    return bool(c.value), bool(d.value), a.value, b.value

@@ -1,0 +1,199 @@
+"""Torch-facing launcher: turns tensors into the POD parameter block of the C ABI.
+
+PyTorch is plumbing here (device memory, the current stream); all compute happens in
+libfa_b200.so.  Every function raises if the tensors are not CUDA tensors -- there is no
+CPU path.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from typing import Optional, Tuple
+
+import torch
+
+from . import lib as L
+
+_sm_count = {}
+
+
+def _num_sm(device: torch.device) -> int:
+    idx = device.index if device.index is not None else torch.cuda.current_device()
+    if idx not in _sm_count:
+        _sm_count[idx] = torch.cuda.get_device_properties(idx).multi_processor_count
+    return _sm_count[idx]
+
+
+def _ptr(t: Optional[torch.Tensor]):
+    return None if t is None else t.data_ptr()
+
+
+def _dtype_code(t: torch.Tensor) -> int:
+    if t.dtype == torch.float16:
+        return L.FA_FP16
+    if t.dtype == torch.bfloat16:
+        return L.FA_BF16
+    raise RuntimeError("FlashAttention only supports FP16 and BF16 data types")
+
+
+def _check_i32(t, name):
+    if t is not None:
+        if t.dtype != torch.int32:
+            raise RuntimeError(f"{name} must have dtype int32")
+        if not t.is_cuda:
+            raise RuntimeError(f"{name} must be a CUDA tensor")
+        if t.dim() > 0 and t.stride(-1) != 1:
+            raise RuntimeError(f"{name} must have contiguous last dimension")
+
+
+def build_params(q, k, v, out, lse, *, k_new=None, v_new=None, cu_seqlens_q=None, cu_seqlens_k=None,
+                 max_seqlen_q=None, max_seqlen_k=None, seqused_k=None, cache_batch_idx=None, block_table=None,
+                 rotary_cos=None, rotary_sin=None, rotary_interleaved=True, alibi_slopes=None,
+                 softmax_scale=1.0, causal=False, window_left=-1, window_right=-1, softcap=0.0, num_splits=0,
+                 max_seqlen_k_known=-1, kv_pos_offset=0, kv_total=0, partial_out=False, kernel=L.KERNEL_AUTO,
+                 num_sm=0) -> L.FwdParams:
+    p = L.FwdParams()
+    varlen_q = cu_seqlens_q is not None
+    paged = block_table is not None
+    p.q, p.k, p.v, p.o, p.lse = _ptr(q), _ptr(k), _ptr(v), _ptr(out), _ptr(lse)
+    p.dtype = _dtype_code(q)
+    if varlen_q:
+        total_q, h, d = q.shape
+        b = cu_seqlens_q.numel() - 1
+        if max_seqlen_q is None:
+            raise RuntimeError("max_seqlen_q is required with cu_seqlens_q")
+        p.q_batch_stride, p.q_row_stride, p.q_head_stride = 0, q.stride(0), q.stride(1)
+        p.o_batch_stride, p.o_row_stride, p.o_head_stride = 0, out.stride(0), out.stride(1)
+        p.seqlen_q, p.total_q = int(max_seqlen_q), total_q
+        p.lse_batch_stride, p.lse_head_stride = 0, lse.stride(0)
+    else:
+        b, s_q, h, d = q.shape
+        p.q_batch_stride, p.q_row_stride, p.q_head_stride = q.stride(0), q.stride(1), q.stride(2)
+        p.o_batch_stride, p.o_row_stride, p.o_head_stride = out.stride(0), out.stride(1), out.stride(2)
+        p.seqlen_q, p.total_q = s_q, b * s_q
+        p.lse_batch_stride, p.lse_head_stride = lse.stride(0), lse.stride(1)
+    if cu_seqlens_k is not None:
+        if k.dim() != 3:
+            raise RuntimeError("k must be (total_k, h_k, d) with cu_seqlens_k")
+        h_k = k.shape[1]
+        if max_seqlen_k is None:
+            raise RuntimeError("max_seqlen_k is required with cu_seqlens_k")
+        p.k_batch_stride, p.k_row_stride, p.k_head_stride = 0, k.stride(0), k.stride(1)
+        p.v_batch_stride, p.v_row_stride, p.v_head_stride = 0, v.stride(0), v.stride(1)
+        p.seqlen_k = int(max_seqlen_k)
+    else:
+        if k.dim() != 4:
+            raise RuntimeError("k must be 4-dimensional")
+        h_k = k.shape[2]
+        p.k_batch_stride, p.k_row_stride, p.k_head_stride = k.stride(0), k.stride(1), k.stride(2)
+        p.v_batch_stride, p.v_row_stride, p.v_head_stride = v.stride(0), v.stride(1), v.stride(2)
+        if paged:
+            p.page_size = k.shape[1]
+            p.seqlen_k = block_table.shape[1] * k.shape[1]
+            p.block_table_batch_stride = block_table.stride(0)
+        else:
+            p.seqlen_k = k.shape[1]
+    p.b, p.h, p.h_k, p.d = b, h, h_k, d
+    if k_new is not None:
+        p.k_new, p.v_new = _ptr(k_new), _ptr(v_new)
+        p.seqlen_new = k_new.shape[1]
+        p.knew_batch_stride, p.knew_row_stride, p.knew_head_stride = k_new.stride(0), k_new.stride(1), k_new.stride(2)
+        p.vnew_batch_stride, p.vnew_row_stride, p.vnew_head_stride = v_new.stride(0), v_new.stride(1), v_new.stride(2)
+    p.cu_seqlens_q, p.cu_seqlens_k = _ptr(cu_seqlens_q), _ptr(cu_seqlens_k)
+    p.seqused_k, p.cache_batch_idx, p.block_table = _ptr(seqused_k), _ptr(cache_batch_idx), _ptr(block_table)
+    if rotary_cos is not None:
+        p.rotary_cos, p.rotary_sin = _ptr(rotary_cos), _ptr(rotary_sin)
+        p.rotary_seqlen, p.rotary_dim = rotary_cos.shape[0], rotary_cos.shape[1] * 2
+        p.rotary_interleaved = int(bool(rotary_interleaved))
+    if alibi_slopes is not None:
+        p.alibi_slopes = _ptr(alibi_slopes)
+        p.alibi_batch_stride = alibi_slopes.stride(0) if alibi_slopes.dim() == 2 else 0
+    p.causal, p.window_left, p.window_right = int(bool(causal)), int(window_left), int(window_right)
+    p.max_seqlen_k_known = int(max_seqlen_k_known)
+    p.kv_pos_offset, p.kv_total, p.partial_out = int(kv_pos_offset), int(kv_total), int(bool(partial_out))
+    p.num_splits, p.kernel, p.num_sm = int(num_splits), int(kernel), int(num_sm)
+    p.softmax_scale, p.softcap = float(softmax_scale), float(softcap)
+    return p
+
+
+def attention_forward(q, k, v, *, out=None, return_plan=False, **kw) -> Tuple[torch.Tensor, torch.Tensor]:
+    """Runs the forward on the current CUDA stream.  Returns (out, lse[, plan]).
+
+    out has q's shape (dtype of q, fp32 when partial_out); lse is fp32 (b, h, s_q), or
+    (h, total_q) for varlen q.  k / v caches are mutated in place when k_new, v_new are given.
+    """
+    lib = L.load()
+    if not (q.is_cuda and k.is_cuda and v.is_cuda):
+        raise RuntimeError("flash_b200 runs on CUDA tensors only (there is no CPU implementation)")
+    if k.dtype != q.dtype or v.dtype != q.dtype:
+        raise RuntimeError("query and key/value must have the same dtype")
+    for name, t in (("q", q), ("k", k), ("v", v), ("k_new", kw.get("k_new")), ("v_new", kw.get("v_new"))):
+        if t is not None and t.stride(-1) != 1:
+            raise RuntimeError(f"Input tensor {name} must have contiguous last dimension")
+    for name in ("cu_seqlens_q", "cu_seqlens_k", "seqused_k", "cache_batch_idx", "block_table"):
+        _check_i32(kw.get(name), name)
+    if kw.get("alibi_slopes") is not None:
+        a = kw["alibi_slopes"]
+        if a.dtype != torch.float32 or not a.is_cuda or a.stride(-1) != 1:
+            raise RuntimeError("alibi_slopes must be a contiguous fp32 CUDA tensor")
+    for name in ("rotary_cos", "rotary_sin"):
+        r = kw.get(name)
+        if r is not None and (r.dtype != q.dtype or not r.is_contiguous()):
+            raise RuntimeError(f"{name} must be contiguous and have the dtype of q")
+    partial = bool(kw.get("partial_out", False))
+    varlen_q = kw.get("cu_seqlens_q") is not None
+    if out is None:
+        out = torch.empty(q.shape, dtype=torch.float32 if partial else q.dtype, device=q.device)
+    else:
+        if out.shape != q.shape or out.stride(-1) != 1 or out.device != q.device:
+            raise RuntimeError("out must have the shape and device of q and a contiguous last dimension")
+        if out.dtype != (torch.float32 if partial else q.dtype):
+            raise RuntimeError("out has the wrong dtype")
+    if varlen_q:
+        lse = torch.empty((q.shape[1], q.shape[0]), dtype=torch.float32, device=q.device)
+    else:
+        lse = torch.empty((q.shape[0], q.shape[2], q.shape[1]), dtype=torch.float32, device=q.device)
+    with torch.cuda.device(q.device):
+        p = build_params(q, k, v, out, lse, num_sm=_num_sm(q.device), **kw)
+        plan = L.FwdPlan()
+        L.check(lib.fa_b200_fwd_plan(C.byref(p), C.byref(plan)))
+        ws = None
+        if plan.workspace_bytes:
+            ws = torch.empty(plan.workspace_bytes, dtype=torch.uint8, device=q.device)
+        stream = torch.cuda.current_stream(q.device).cuda_stream
+        L.check(lib.fa_b200_fwd(C.byref(p), _ptr(ws), plan.workspace_bytes, stream))
+    if return_plan:
+        return out, lse, plan
+    return out, lse
+
+
+def combine(o_partial: torch.Tensor, lse_partial: torch.Tensor, out: Optional[torch.Tensor] = None,
+            out_dtype: Optional[torch.dtype] = None, partial_out: bool = False):
+    """Merge of split partials.  o_partial (n, b, s, h, d) fp32, lse_partial (n, b, s, h) fp32
+    (natural log, -inf = empty partial) -> out (b, s, h, d), lse (b, s, h)."""
+    lib = L.load()
+    if not o_partial.is_cuda:
+        raise RuntimeError("flash_b200 runs on CUDA tensors only (there is no CPU implementation)")
+    if o_partial.dtype != torch.float32 or lse_partial.dtype != torch.float32:
+        raise RuntimeError("partials must be fp32")
+    n, b, s, h, d = o_partial.shape
+    if tuple(lse_partial.shape) != (n, b, s, h):
+        raise RuntimeError("lse_partial must be (num_splits, batch, seqlen, nheads)")
+    if o_partial.stride(-1) != 1 or d % 4 != 0:
+        raise RuntimeError("o_partial needs a contiguous last dimension that is a multiple of 4")
+    if out_dtype is None:
+        out_dtype = out.dtype if out is not None else torch.float32
+    code = {torch.float16: L.FA_FP16, torch.bfloat16: L.FA_BF16, torch.float32: L.FA_FP32_OUT}[out_dtype]
+    if out is None:
+        out = torch.empty((b, s, h, d), dtype=out_dtype, device=o_partial.device)
+    lse = torch.empty((b, s, h), dtype=torch.float32, device=o_partial.device)
+    c = L.CombineParams()
+    c.o_partial, c.lse_partial, c.o, c.lse = _ptr(o_partial), _ptr(lse_partial), _ptr(out), _ptr(lse)
+    c.op_split_stride, c.op_batch_stride, c.op_row_stride, c.op_head_stride = o_partial.stride()[:4]
+    c.lp_split_stride, c.lp_batch_stride, c.lp_row_stride, c.lp_head_stride = lse_partial.stride()
+    c.o_batch_stride, c.o_row_stride, c.o_head_stride = out.stride()[:3]
+    c.lse_batch_stride, c.lse_row_stride, c.lse_head_stride = lse.stride()
+    c.num_splits, c.b, c.s, c.h, c.d = n, b, s, h, d
+    c.out_dtype, c.partial_out = code, int(bool(partial_out))
+    with torch.cuda.device(o_partial.device):
+        L.check(lib.fa_b200_combine(C.byref(c), torch.cuda.current_stream(o_partial.device).cuda_stream))
+    return out, lse

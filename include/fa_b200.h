@@ -1,0 +1,163 @@
+/*
+ * fa_b200.h -- C ABI of the B200 (sm_100a) attention-forward library, libfa_b200.so.
+ *
+ * Every entry point is extern "C", takes plain pointers / sizes / POD structs and a
+ * CUDA stream passed as void* (cudaStream_t).  No torch types cross this boundary.
+ * All tensor pointers are DEVICE pointers; strides are in ELEMENTS; the last
+ * dimension of every tensor is contiguous.  Calls are asynchronous on `stream`.
+ *
+ * Which reference interface each entry point replaces (paths inside the reference
+ * project Minghuas/flash-attention-npu):
+ *
+ *   fa_b200_fwd                 mha_fwd            csrc/arch22/flash_attn_npu_v2/flash_api.cpp:628-826
+ *                               mha_varlen_fwd     csrc/arch22/flash_attn_npu_v2/flash_api.cpp:828-1060
+ *                               mha_fwd_kvcache    csrc/arch22/flash_attn_npu_v2/flash_api.cpp:356-626
+ *                               mha_fwd (unified)  csrc/arch22/flash_attn_npu_v3/flash_api.cpp:60-491
+ *                               mha_fwd (arch35)   csrc/arch35/flash_attn_npu_v3/mha_fwd.cpp:38-358
+ *                               (pybind names: fwd / varlen_fwd / fwd_kvcache,
+ *                                csrc/arch22/flash_attn_npu_v2/flash_api.cpp:1301-1309,
+ *                                csrc/arch22/flash_attn_npu_v3/flash_api.cpp:816-822)
+ *   fa_b200_fwd_plan            the host tiling / flash-decode decision of the same functions
+ *                               (flash_api.cpp:514-556) and the split planner
+ *                               csrc/arch22/flash_attn_npu_v3/fa_split.h:483-510
+ *   fa_b200_combine             CombineScale, csrc/arch22/flash_attn_npu_v2/CombineScale.hpp:76-357
+ *                               (and the Python-level flash_attn_combine,
+ *                                flash_attn_npu_v3/interface_arch22.py:930-931)
+ *   fa_b200_normalize_window    the window normalisation block, flash_api.cpp:483-494
+ */
+#ifndef FA_B200_H
+#define FA_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define FA_B200_ABI_VERSION 1
+
+enum fa_status {
+  FA_OK = 0,
+  FA_ERR_INVALID = -1,     /* bad argument (the reference raises through TORCH_CHECK) */
+  FA_ERR_UNSUPPORTED = -2, /* valid but not implemented */
+  FA_ERR_CUDA = -3,        /* a CUDA runtime call failed */
+  FA_ERR_WORKSPACE = -4    /* workspace missing or too small */
+};
+
+enum fa_dtype { FA_FP16 = 0, FA_BF16 = 1 };
+
+enum fa_kernel_id {
+  FA_KERNEL_AUTO = 0,
+  FA_KERNEL_MMA = 1,    /* register-accumulator kernel (decode, paged, ragged shapes) */
+  FA_KERNEL_TCGEN05 = 2 /* tcgen05 / TMEM / TMA prefill kernel */
+};
+
+typedef struct fa_fwd_params {
+  /* ---- device pointers ---- */
+  const void* q;      /* (b, s_q, h, d), or (total_q, h, d) when cu_seqlens_q is set */
+  const void* k;      /* dense (b, s_k, h_k, d) | varlen (total_k, h_k, d) | cache (b_c, s_cache, h_k, d)
+                         | pages (n_blocks, page, h_k, d) when block_table is set */
+  const void* v;
+  void* o;            /* same layout as q; fp32 when partial_out != 0 */
+  float* lse;         /* (b, h, s_q) or (h, total_q); natural log; required */
+  const void* k_new;  /* (b, s_new, h_k, d) appended in place at [L_b, L_b + s_new); may be NULL */
+  const void* v_new;
+  const int32_t* cu_seqlens_q;    /* (b + 1) or NULL */
+  const int32_t* cu_seqlens_k;    /* (b + 1) or NULL */
+  const int32_t* seqused_k;       /* (b) keys already in the cache (cache_seqlens) or NULL */
+  const int32_t* cache_batch_idx; /* (b) row of the cache used by sequence i, or NULL */
+  const int32_t* block_table;     /* (b, max_blocks) physical page of logical page, or NULL */
+  const void* rotary_cos;         /* (rotary_seqlen, rotary_dim / 2), dtype of q, or NULL */
+  const void* rotary_sin;
+  const float* alibi_slopes;      /* (h) or (b, h) fp32, or NULL */
+  /* ---- element strides ---- */
+  int64_t q_batch_stride, q_row_stride, q_head_stride;
+  int64_t k_batch_stride, k_row_stride, k_head_stride; /* batch stride = page stride when paged */
+  int64_t v_batch_stride, v_row_stride, v_head_stride;
+  int64_t o_batch_stride, o_row_stride, o_head_stride;
+  int64_t knew_batch_stride, knew_row_stride, knew_head_stride;
+  int64_t vnew_batch_stride, vnew_row_stride, vnew_head_stride;
+  int64_t lse_batch_stride, lse_head_stride; /* query index has stride 1 */
+  int64_t block_table_batch_stride;
+  int64_t alibi_batch_stride; /* 0 for (h) */
+  /* ---- sizes ---- */
+  int32_t b;
+  int32_t seqlen_q;   /* s_q, or max_seqlen_q for varlen */
+  int32_t seqlen_k;   /* s_k / max_seqlen_k / s_cache / max_blocks * page: an upper bound of every key length */
+  int32_t h, h_k, d;
+  int32_t total_q;    /* rows of q when cu_seqlens_q is set, else b * s_q */
+  int32_t seqlen_new; /* s_new, 0 without append */
+  int32_t page_size;  /* rows per page when block_table is set */
+  int32_t rotary_dim, rotary_seqlen, rotary_interleaved;
+  int32_t dtype;      /* enum fa_dtype */
+  /* ---- masking (raw user values; normalised inside exactly like flash_api.cpp:483-494) ---- */
+  int32_t causal, window_left, window_right;
+  /* max over the batch of the key length, if the host knows it; -1 = take the maximum of
+     seqused_k + seqlen_new on the device (only read when a window is requested) */
+  int32_t max_seqlen_k_known;
+  /* ---- sequence-sharded decode: this call sees keys [kv_pos_offset, kv_pos_offset + s_k) of a
+     sequence of kv_total keys (0 = not sharded); only the mask / alibi positions change ---- */
+  int32_t kv_pos_offset, kv_total;
+  int32_t partial_out; /* 1: o is fp32 (normalised partial), lse = -inf for rows without keys */
+  /* ---- tuning ---- */
+  int32_t num_splits; /* 0 heuristic, 1 never split, > 1 requested number of KV splits */
+  int32_t kernel;     /* enum fa_kernel_id */
+  int32_t num_sm;     /* 0 = query the current device */
+  float softmax_scale;
+  float softcap; /* 0 = off */
+} fa_fwd_params;
+
+typedef struct fa_fwd_plan {
+  int32_t kernel;       /* enum fa_kernel_id actually chosen */
+  int32_t config;       /* tile configuration index inside that kernel family */
+  int32_t pack_gqa;     /* 1: the query heads of one kv head share a tile */
+  int32_t block_m, block_n;
+  int32_t m_blocks;
+  int32_t num_splits;   /* KV splits launched (1 = none) */
+  int32_t blocks_per_split;
+  int32_t grid, threads, smem_bytes;
+  int32_t is_causal, is_local, window_left, window_right; /* after host normalisation */
+  int32_t launches;     /* kernel launches fa_b200_fwd will make */
+  size_t workspace_bytes;
+} fa_fwd_plan;
+
+typedef struct fa_combine_params {
+  const float* o_partial;   /* fp32 normalised partial outputs */
+  const float* lse_partial; /* fp32 natural-log LSE; -inf marks an empty partial */
+  void* o;                  /* out_dtype */
+  float* lse;               /* may be NULL */
+  int64_t op_split_stride, op_batch_stride, op_row_stride, op_head_stride;
+  int64_t lp_split_stride, lp_batch_stride, lp_row_stride, lp_head_stride;
+  int64_t o_batch_stride, o_row_stride, o_head_stride;
+  int64_t lse_batch_stride, lse_row_stride, lse_head_stride;
+  int32_t num_splits, b, s, h, d;
+  int32_t out_dtype;   /* enum fa_dtype, or 2 = fp32 */
+  int32_t partial_out; /* 1: rows without keys give lse = -inf (result is itself a partial) */
+} fa_combine_params;
+
+/* Attention forward: dense, varlen, KV-cache (contiguous / paged) with optional fused
+ * in-place append + rotary, split-KV with its merge.  `workspace` (device memory, 256-byte
+ * aligned) must hold fa_fwd_plan.workspace_bytes; it may be NULL when that is 0. */
+int fa_b200_fwd(const fa_fwd_params* p, void* workspace, size_t workspace_bytes, void* stream);
+
+/* Host-only: validates `p` and reports what fa_b200_fwd would launch.  Needs no GPU when
+ * p->num_sm > 0. */
+int fa_b200_fwd_plan(const fa_fwd_params* p, fa_fwd_plan* plan);
+
+/* Merge of split partials (also used across GPUs). */
+int fa_b200_combine(const fa_combine_params* p, void* stream);
+
+/* Host-only window normalisation; writes the normalised window and the two mode flags. */
+int fa_b200_normalize_window(int32_t seqlen_q, int32_t max_seqlen_k, int32_t causal, int32_t* window_left,
+                             int32_t* window_right, int32_t* is_causal, int32_t* is_local);
+
+/* Message of the last error on the calling thread ("" if none). */
+const char* fa_b200_last_error(void);
+const char* fa_b200_status_string(int status);
+int fa_b200_abi_version(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* FA_B200_H */

@@ -1,0 +1,53 @@
+"""Shared helpers of the GPU parity tests: seeded inputs, oracle calls, rule checks."""
+import math
+
+import torch
+
+import precision as P
+from oracle import api as OA
+from oracle import golden as OG
+
+DEV = "cuda"
+
+
+def uniform(shape, dtype, gen, lo=-5.0, hi=5.0):
+    """U(lo, hi) like the reference tests (tests/test_flash_attn_npu_v2.py:259-265), but seeded."""
+    return (lo + (hi - lo) * torch.rand(shape, generator=gen)).to(dtype)
+
+
+def normal(shape, dtype, gen, std=1.0):
+    return (torch.randn(shape, generator=gen) * std).to(dtype)
+
+
+def rotary_tables(seqlen_ro, rotary_dim, dtype, base=10000.0):
+    inv = base ** (-torch.arange(0, rotary_dim, 2, dtype=torch.float32) / rotary_dim)
+    ang = torch.arange(seqlen_ro, dtype=torch.float32).view(-1, 1) * inv.view(1, -1)
+    return torch.cos(ang).to(dtype), torch.sin(ang).to(dtype)
+
+
+def check_rules(out, lse, gold_out, gold_lse, *, plain_out=None, strict_data_compare=True, tag=""):
+    """Rule 1 always; rule 2 when strict_data_compare; rule 3 when a plain-dtype output is given."""
+    P.assert_close_rule(out, gold_out, lse, gold_lse)
+    res, pct, mx = P.data_compare(out, gold_out)
+    if strict_data_compare:
+        assert res == "success", f"{tag} data_compare failed: pct={pct:.4f} max_rel={mx:.4f}"
+    if plain_out is not None:
+        ok, err, bound = P.two_x_rule(out, gold_out, plain_out)
+        assert ok, f"{tag} 2x rule: err {err} > bound {bound}"
+    if lse is not None:
+        a, b = lse.float().cpu(), gold_lse.float().cpu()
+        fin = ~torch.isinf(b)
+        if fin.any():
+            assert float((a[fin] - b[fin]).abs().max()) <= 1e-3 + 1e-4 * float(b[fin].abs().max()), f"{tag} LSE"
+
+
+def plain_dtype_attention(q, k, v, scale, causal=False, window=(-1, -1), max_k=None):
+    """Plain PyTorch attention evaluated in the input dtype, one sequence at a time (rule 3)."""
+    outs = []
+    for i in range(q.shape[0]):
+        s_q, s_k = q.shape[1], k[i].shape[0]
+        ic, il, wl, wr = OG.normalize_window(s_q, max_k if max_k is not None else s_k, causal, window[0], window[1])
+        mask = OG.build_mask(s_q, s_k, ic, il, wl, wr)
+        o, _ = OG.dense_softmax_attention(q[i], k[i], v[i], scale, mask, compute_dtype=q.dtype)
+        outs.append(o)
+    return torch.stack(outs)

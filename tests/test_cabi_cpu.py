@@ -1,0 +1,129 @@
+"""CPU: the C-ABI library loads, exports every symbol include/fa_b200.h declares, and its
+host-only entry points (window normalisation, planning, argument validation) behave like the
+reference's host code.  No kernel is launched here."""
+import ctypes as C
+import os
+import re
+
+import pytest
+
+from flash_b200 import lib as L
+from oracle import golden as OG
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def test_library_exports_every_declared_symbol():
+    lib = L.load()
+    header = open(os.path.join(ROOT, "include", "fa_b200.h")).read()
+    declared = set(re.findall(r"\b(fa_b200_\w+)\s*\(", header))
+    assert declared == set(L.EXPORTS)
+    for name in declared:
+        assert hasattr(lib, name), name
+    assert lib.fa_b200_abi_version() == 1
+    assert lib.fa_b200_status_string(-4).decode().startswith("workspace")
+
+
+def test_struct_layout_matches_header():
+    # sizes produced by gcc for include/fa_b200.h (x86-64 LP64)
+    assert C.sizeof(L.FwdParams) == 400
+    assert C.sizeof(L.FwdPlan) == 72
+    assert C.sizeof(L.CombineParams) == 176
+
+
+@pytest.mark.parametrize("sq,mk,causal,wl,wr", [
+    (64, 192, False, 32, 64), (1024, 1024, True, 512, 256), (1024, 1024, True, -128, 864),
+    (512, 512, False, 508, -256), (128, 512, True, 511, 0), (4, 100, False, -1, -1), (1, 1024, True, 512, 0),
+    (4, 32768, True, 4096, 0), (2, 1024, True, 256, 0), (128, 256, True, 127, 0)])
+def test_window_normalisation_matches_oracle(sq, mk, causal, wl, wr):
+    assert L.normalize_window(sq, mk, causal, wl, wr) == OG.normalize_window(sq, mk, causal, wl, wr)
+
+
+def _params(**kw):
+    p = L.FwdParams()
+    p.q = p.k = p.v = p.o = p.lse = 256
+    p.b, p.seqlen_q, p.seqlen_k, p.h, p.h_k, p.d = 2, 1, 4096, 32, 8, 128
+    p.total_q = 2
+    p.lse_batch_stride, p.lse_head_stride = 32, 1
+    p.dtype, p.num_sm, p.softmax_scale = L.FA_BF16, 148, 0.088
+    p.max_seqlen_k_known = -1
+    p.window_left = p.window_right = -1
+    for k, v in kw.items():
+        setattr(p, k, v)
+    return p
+
+
+def _plan(p):
+    pl = L.FwdPlan()
+    rc = L.load().fa_b200_fwd_plan(C.byref(p), C.byref(pl))
+    return rc, pl
+
+
+def test_plan_decode_packs_gqa_and_splits():
+    rc, pl = _plan(_params(seqused_k=256))
+    assert rc == 0
+    assert pl.pack_gqa == 1 and pl.block_m == 16 and pl.block_n == 128 and pl.m_blocks == 1
+    assert pl.num_splits > 1 and pl.launches == 2
+    assert pl.blocks_per_split * pl.num_splits >= 32
+    assert pl.grid == 2 * 8 * pl.num_splits
+    assert pl.workspace_bytes >= pl.num_splits * 2 * 32 * (128 + 1) * 4
+    rc, pl1 = _plan(_params(seqused_k=256, num_splits=1))
+    assert rc == 0 and pl1.num_splits == 1 and pl1.workspace_bytes == 0 and pl1.launches == 1
+
+
+def test_plan_window_bounds_the_kv_range():
+    p = _params(seqused_k=256, block_table=256, page_size=256, seqlen_k=32768, seqlen_q=4, total_q=8,
+                lse_head_stride=4, lse_batch_stride=128, causal=1, window_left=4096, window_right=0, h=64)
+    rc, pl = _plan(p)
+    assert rc == 0 and pl.is_local == 1 and pl.window_left == 4096 and pl.window_right == 0
+    assert pl.block_m == 32  # 4 query tokens x 8 packed heads
+    assert pl.num_splits * pl.blocks_per_split * pl.block_n <= 4096 + 4 + 3 * 128
+
+
+@pytest.mark.parametrize("kw,msg", [
+    (dict(h=30), "Number of heads"), (dict(d=264), "at most 256"), (dict(d=100), "multiple of 8"),
+    (dict(dtype=7), "FP16 and BF16"), (dict(b=0), "batch size"), (dict(softcap=-1.0), "softcap"),
+    (dict(k_new=256), "together"), (dict(k_new=256, v_new=256, seqlen_new=1), "cache_seqlens"),
+    (dict(block_table=256, page_size=16), "key lengths"),
+    (dict(rotary_cos=256, rotary_sin=256, rotary_dim=64), "together with new k"),
+    (dict(kernel=L.KERNEL_TCGEN05, seqused_k=256), "tcgen05"),
+])
+def test_plan_rejects_bad_arguments(kw, msg):
+    rc, _ = _plan(_params(**kw))
+    assert rc != 0
+    assert msg in L.load().fa_b200_last_error().decode()
+    with pytest.raises(RuntimeError, match=msg):
+        L.check(rc)
+
+
+def test_python_modules_expose_reference_signatures():
+    import inspect
+
+    import flash_attn_npu_v2 as v2
+    import flash_attn_npu_v3 as v3
+    assert v2.__version__ == "0.1.1" and v3.__version__ == "0.1.1"
+    sig = inspect.signature(v2.flash_attn_with_kvcache)
+    assert list(sig.parameters) == ["q", "k_cache", "v_cache", "k", "v", "rotary_cos", "rotary_sin", "cache_seqlens",
+                                    "cache_batch_idx", "cache_leftpad", "block_table", "softmax_scale", "causal",
+                                    "window_size", "softcap", "rotary_interleaved", "alibi_slopes", "num_splits",
+                                    "return_softmax_lse"]
+    assert sig.parameters["rotary_interleaved"].default is True and sig.parameters["num_splits"].default == 0
+    sig = inspect.signature(v2.flash_attn_func)
+    assert list(sig.parameters) == ["q", "k", "v", "dropout_p", "softmax_scale", "causal", "window_size", "softcap",
+                                    "alibi_slopes", "deterministic", "return_attn_probs"]
+    sig = inspect.signature(v3.flash_attn_with_kvcache)
+    assert list(sig.parameters)[:12] == ["q", "k_cache", "v_cache", "k", "v", "qv", "rotary_cos", "rotary_sin",
+                                         "cache_seqlens", "cache_batch_idx", "cache_leftpad", "page_table"]
+    sig = inspect.signature(v3.flash_attn_func)
+    assert sig.parameters["num_splits"].default == 1
+    for name in ("flash_attn_func", "flash_attn_varlen_func", "flash_attn_with_kvcache", "get_scheduler_metadata"):
+        assert hasattr(v3, name)
+
+
+def test_cpu_tensors_are_refused():
+    import torch
+
+    import flash_attn_npu_v2 as v2
+    q = torch.zeros(1, 1, 2, 64, dtype=torch.bfloat16)
+    with pytest.raises(RuntimeError, match="CUDA"):
+        v2.flash_attn_func(q, q, q)
