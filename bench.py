@@ -352,6 +352,9 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--cpu-budget", type=float, default=12.0)
+    ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (profiling runs)")
+    ap.add_argument("--shrink", type=int, default=1,
+                    help="divide the batch (c2-c4) or the key length (c5) by this factor: small cases for ncu captures")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -374,6 +377,14 @@ def main():
         torch.cuda.synchronize()
 
     wl = WORKLOADS[args.workload]()
+    if args.shrink > 1:
+        if args.workload == "c5":
+            wl.L //= args.shrink
+        else:
+            wl.b = max(1, wl.b // args.shrink)
+        if args.workload == "c4":
+            wl.nblk = wl.b * 128
+        wl.name += f"_shrunk{args.shrink}"
     wl.setup(dev, rank, world)
     peaks = load_peaks()
 
@@ -395,24 +406,27 @@ def main():
     total_ms = ev[0].elapsed_time(ev[-1])
     per = sorted(ev[i].elapsed_time(ev[i + 1]) for i in range(args.steps))
     # keep the GPU busy a little longer so the clock sampler sees load even for short runs
-    t_end = time.time() + 0.6
+    t_end = time.time() + (0.6 if args.steps > 2 else 0.0)
     while rank == 0 and time.time() < t_end:
         wl.step()
     torch.cuda.synchronize()
     clocks = sampler.stop() if rank == 0 else None
 
     # ---- end-to-end timing (host buffers) ----
-    wl.setup_e2e()
-    for _ in range(3):
-        wl.step_e2e()
-    barrier()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record(stream)
-    for _ in range(args.steps):
-        wl.step_e2e()
-    e1.record(stream)
-    barrier()
-    e2e_ms = e0.elapsed_time(e1)
+    e2e_ms = float("nan")
+    wl.h2d = wl.d2h = 0
+    if not args.no_e2e:
+        wl.setup_e2e()
+        for _ in range(3):
+            wl.step_e2e()
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        for _ in range(args.steps):
+            wl.step_e2e()
+        e1.record(stream)
+        barrier()
+        e2e_ms = e0.elapsed_time(e1)
 
     t = torch.tensor([total_ms, e2e_ms, wl.units], dtype=torch.float64, device=dev)
     if world > 1:

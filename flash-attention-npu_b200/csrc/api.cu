@@ -7,6 +7,7 @@
 
 #include <algorithm>
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <string>
 
@@ -107,6 +108,11 @@ static int make_plan(const fa_fwd_params& a, Planned* out) {
   const int gp = pack ? group : 1;
   const int rows_max = a.seqlen_q * gp;
   int cfg = rows_max <= 16 ? 0 : (rows_max <= 32 ? 1 : (pack ? 2 : 3));
+  if (const char* e = std::getenv("FA_B200_MMA_CONFIG")) {  // tuning override: tile configuration index
+    const int forced = std::atoi(e);
+    MmaConfigInfo t;
+    if (mma_config_info(hd_pad, forced, &t) && t.block_m >= std::min(rows_max, 16)) cfg = forced;
+  }
   MmaConfigInfo ci;
   if (!mma_config_info(hd_pad, cfg, &ci)) return fail(FA_ERR_UNSUPPORTED, "no tile configuration");
   const int m_blocks = std::max(1, ceil_div(rows_max, ci.block_m));
@@ -128,7 +134,9 @@ static int make_plan(const fa_fwd_params& a, Planned* out) {
   if (a.num_splits >= 1) {
     ns = std::min(a.num_splits, max_blocks);
   } else if (base < 8LL * num_sm && max_blocks >= 16) {
-    long long want = (16LL * num_sm + base - 1) / base;
+    long long per_sm = 16;
+    if (const char* e = std::getenv("FA_B200_CTAS_PER_SM")) per_sm = std::max(1, std::atoi(e));  // tuning override
+    long long want = (per_sm * num_sm + base - 1) / base;
     ns = (int)std::max(1LL, std::min<long long>(want, max_blocks / 8));
   }
   int bps = ceil_div(max_blocks, ns);

@@ -18,11 +18,13 @@ __global__ void __launch_bounds__(Tr::NTHREADS) fwd_mma_kernel(const __grid_cons
   const int g8 = lane >> 2, t4 = lane & 3;
 
   // ---- which tile ----
+  // Heads vary fastest: the CTAs that run together read the same token rows of the (.., h_k, d)
+  // cache, i.e. neighbouring 2 * d-byte pieces of the same DRAM pages.
   int idx = blockIdx.x;
-  const int split = idx % p.num_splits;
-  idx /= p.num_splits;
   const int hh = idx % p.heads_eff;
   idx /= p.heads_eff;
+  const int split = idx % p.num_splits;
+  idx /= p.num_splits;
   const int bi = idx % p.a.b;
   const int mb = p.m_blocks - 1 - idx / p.a.b;  // heavy (late) causal tiles first
   const int hk = (hh * p.gp) / p.group;

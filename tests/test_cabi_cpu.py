@@ -62,9 +62,9 @@ def _plan(p):
 def test_plan_decode_packs_gqa_and_splits():
     rc, pl = _plan(_params(seqused_k=256))
     assert rc == 0
-    assert pl.pack_gqa == 1 and pl.block_m == 16 and pl.block_n == 128 and pl.m_blocks == 1
+    assert pl.pack_gqa == 1 and pl.block_m == 16 and pl.block_n == 64 and pl.m_blocks == 1
     assert pl.num_splits > 1 and pl.launches == 2
-    assert pl.blocks_per_split * pl.num_splits >= 32
+    assert pl.blocks_per_split * pl.num_splits >= 64
     assert pl.grid == 2 * 8 * pl.num_splits
     assert pl.workspace_bytes >= pl.num_splits * 2 * 32 * (128 + 1) * 4
     rc, pl1 = _plan(_params(seqused_k=256, num_splits=1))
