@@ -307,6 +307,14 @@ int fa_b200_normalize_window(int32_t seqlen_q, int32_t max_seqlen_k, int32_t cau
   return FA_OK;
 }
 
+int fa_b200_check_status(void* stream) {
+  const int v = fa::tc5_read_status(reinterpret_cast<cudaStream_t>(stream));
+  if (v == 0) return FA_OK;
+  if (v < 0) return fa::fail(FA_ERR_CUDA, "cannot read the device status word");
+  return fa::fail(FA_ERR_CUDA, "a bounded device-side wait gave up in CTA " + std::to_string(v - 1) +
+                                   " of the tcgen05 kernel (results of that launch are invalid)");
+}
+
 const char* fa_b200_last_error(void) { return fa::g_err.c_str(); }
 
 const char* fa_b200_status_string(int status) {

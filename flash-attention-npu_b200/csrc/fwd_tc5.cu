@@ -1,13 +1,241 @@
-// tcgen05 prefill kernel (placeholder translation unit until the kernel lands).
+// tcgen05 / TMEM / TMA prefill kernel: entry point, TMA descriptors, launch.
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+#include <algorithm>
+#include <cstdio>
+#include <cstring>
+#include <mutex>
+#include <string>
+
+#include "fwd_tc5_roles.cuh"
+#include "fwd_tc5_softmax.cuh"
 #include "tc5_api.cuh"
 
 namespace fa {
+namespace tc5 {
 
-bool tc5_eligible(const fa_fwd_params&, bool, bool, int) { return false; }
-void tc5_fill_plan(const fa_fwd_params&, fa_fwd_plan*) {}
-int tc5_launch(const fa_fwd_params&, const fa_fwd_plan&, cudaStream_t, std::string* err) {
-  *err = "tcgen05 kernel not built";
-  return FA_ERR_UNSUPPORTED;
+template <typename T, uint32_t AB_FMT>
+__global__ void __launch_bounds__(kThreads, 1)
+fwd_tc5_kernel(const __grid_constant__ Tc5Params p, const __grid_constant__ CUtensorMap tm_q,
+               const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v) {
+  extern __shared__ uint8_t smem_raw[];
+  // 128-byte-swizzled tiles need 1024-byte aligned bases
+  const uint32_t raw = smem_addr(smem_raw);
+  const uint32_t base = (raw + 1023u) & ~1023u;
+  uint8_t* smem = smem_raw + (base - raw);
+  const uint32_t q_smem = base;
+  const uint32_t kv_smem = base + 2 * kTileBytes;
+  Barriers* bar = reinterpret_cast<Barriers*>(smem + 2 * kTileBytes + kSlots * kTileBytes);
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  if (tid == 0) {
+    for (int t = 0; t < 2; ++t) {
+      mbar_init(smem_addr(&bar->q_full[t]), 1);
+      mbar_init(smem_addr(&bar->q_empty[t]), 1);
+      mbar_init(smem_addr(&bar->s_full[t]), 1);
+      mbar_init(smem_addr(&bar->p_full[t]), 4);
+      mbar_init(smem_addr(&bar->o_done[t]), 1);
+      mbar_init(smem_addr(&bar->o_free[t]), 4);
+    }
+    for (int s = 0; s < kSlots; ++s) {
+      mbar_init(smem_addr(&bar->kv_full[s]), 1);
+      mbar_init(smem_addr(&bar->kv_empty[s]), 1);
+    }
+    bar->abort_flag = 0;
+    fence_barrier_init();
+  }
+  if (warp == 8) {
+    tmem_alloc(smem_addr(&bar->tmem_base), 512);
+    tmem_relinquish();
+  }
+  if (warp == 9 && lane == 0) {
+    tma_prefetch_desc(&tm_q);
+    tma_prefetch_desc(&tm_k);
+    tma_prefetch_desc(&tm_v);
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = bar->tmem_base;
+
+  if (warp < 8) {
+    softmax_loop<T>(p, bar, tmem, warp >> 2, warp & 3, lane);
+  } else if (warp == 8) {
+    if (lane == 0) mma_loop<AB_FMT>(p, bar, q_smem, kv_smem, tmem);
+    __syncwarp();
+  } else {
+    if (lane == 0) producer_loop(p, &tm_q, &tm_k, &tm_v, bar, q_smem, kv_smem);
+    __syncwarp();
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  const int aborted = bar->abort_flag;
+  if (aborted) {
+    // give copies that may still be in flight time to land before the shared memory is released
+    for (int i = 0; i < 64; ++i) __nanosleep(2000);
+    if (tid == 0) atomicExch(p.status, 1 + blockIdx.x);
+    __syncthreads();
+  }
+  if (warp == 8) {
+    tc_fence_after();
+    tmem_dealloc(tmem, 512);
+  }
+}
+
+// ------------------------------------------------------------------------------------------------
+// host
+// ------------------------------------------------------------------------------------------------
+using EncodeFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                              const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                              CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeFn get_encode() {
+  static EncodeFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) == cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeFn>(ptr);
+  });
+  return fn;
+}
+
+// (d, heads, rows, batch) view of a (batch, rows, heads, d)-strided 16-bit tensor; box = 64 x 1 x 128 x 1.
+static bool encode_map(CUtensorMap* m, const void* ptr, int dtype, int d, int heads, int64_t rows, int64_t batch,
+                       int64_t head_stride, int64_t row_stride, int64_t batch_stride) {
+  EncodeFn enc = get_encode();
+  if (!enc) return false;
+  cuuint64_t dims[4] = {(cuuint64_t)d, (cuuint64_t)heads, (cuuint64_t)rows, (cuuint64_t)batch};
+  cuuint64_t strides[3] = {(cuuint64_t)head_stride * 2, (cuuint64_t)row_stride * 2, (cuuint64_t)batch_stride * 2};
+  if (batch == 1) strides[2] = (cuuint64_t)rows * row_stride * 2;
+  cuuint32_t box[4] = {64, 1, (cuuint32_t)kBlockN, 1};
+  cuuint32_t estr[4] = {1, 1, 1, 1};
+  CUresult r = enc(m, dtype == FA_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 4,
+                   const_cast<void*>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                   CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS;
+}
+
+static int32_t* status_word() {
+  static int32_t* words[64] = {nullptr};
+  static std::mutex mu;
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+  std::lock_guard<std::mutex> lock(mu);
+  if (!words[dev]) {
+    if (cudaMalloc(&words[dev], sizeof(int32_t)) != cudaSuccess) return nullptr;
+    cudaMemset(words[dev], 0, sizeof(int32_t));
+  }
+  return words[dev];
+}
+
+}  // namespace tc5
+
+bool tc5_eligible(const fa_fwd_params& a, bool is_causal, bool is_local, int wl_on_device) {
+  (void)is_causal;
+  (void)is_local;
+  if (a.d != 128 || a.seqlen_q < 128) return false;
+  if (a.cu_seqlens_q || a.cu_seqlens_k) return false;  // varlen: not yet
+  if (a.seqused_k || a.block_table || a.k_new || a.alibi_slopes || a.cache_batch_idx || a.rotary_cos) return false;
+  if (a.softcap > 0.f || a.partial_out || a.kv_total > 0 || wl_on_device) return false;
+  if ((a.cu_seqlens_q != nullptr) != (a.cu_seqlens_k != nullptr)) return false;
+  // TMA: 16-byte aligned bases and strides
+  auto al = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; };
+  if (!al(a.q) || !al(a.k) || !al(a.v) || !al(a.o)) return false;
+  const int64_t st[] = {a.q_row_stride, a.q_head_stride, a.q_batch_stride, a.k_row_stride, a.k_head_stride,
+                        a.k_batch_stride, a.v_row_stride, a.v_head_stride, a.v_batch_stride,
+                        a.o_row_stride, a.o_head_stride, a.o_batch_stride};
+  for (int64_t s : st)
+    if (s % 8 != 0 || s < 0) return false;
+  return true;
+}
+
+void tc5_fill_plan(const fa_fwd_params& a, fa_fwd_plan* pl) {
+  const int m_tiles = (a.seqlen_q + tc5::kTileM - 1) / tc5::kTileM;
+  const long long total = (long long)m_tiles * a.b * a.h;
+  int num_sm = a.num_sm;
+  if (num_sm <= 0) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&num_sm, cudaDevAttrMultiProcessorCount, dev);
+  }
+  pl->kernel = FA_KERNEL_TCGEN05;
+  pl->config = 0;
+  pl->pack_gqa = 0;
+  pl->block_m = tc5::kTileM;
+  pl->block_n = tc5::kBlockN;
+  pl->m_blocks = m_tiles;
+  pl->num_splits = 1;
+  pl->blocks_per_split = 0;
+  pl->grid = (int)std::min<long long>(total, num_sm > 0 ? num_sm : 148);
+  pl->threads = tc5::kThreads;
+  pl->smem_bytes = tc5::kSmemBytes;
+  pl->launches = 1;
+  pl->workspace_bytes = 0;
+}
+
+int tc5_launch(const fa_fwd_params& a, const fa_fwd_plan& pl, cudaStream_t st, std::string* err) {
+  using namespace tc5;
+  Tc5Params p;
+  std::memset(&p, 0, sizeof(p));
+  p.a = a;
+  p.is_causal = pl.is_causal;
+  p.is_local = pl.is_local;
+  p.wl = pl.window_left;
+  p.wr = pl.window_right;
+  p.group = a.h / a.h_k;
+  p.m_tiles = pl.m_blocks;
+  p.total_tiles = pl.m_blocks * a.b * a.h;
+  p.scale_log2 = a.softmax_scale * kLog2e;
+  p.status = status_word();
+  if (!p.status) { *err = "cannot allocate the device status word"; return FA_ERR_CUDA; }
+  const bool varlen = a.cu_seqlens_q != nullptr;
+  CUtensorMap tq, tk, tv;
+  bool ok = true;
+  if (varlen) {
+    // total_k is not passed explicitly: rows past the end of the tensor are never addressed by a
+    // valid (row < k_len) key, so a generous bound of b * max_seqlen_k rows would over-read; use the
+    // exact total from the caller-provided upper bound instead.
+    ok = false;
+  }
+  if (!varlen) {
+    ok = encode_map(&tq, a.q, a.dtype, a.d, a.h, a.seqlen_q, a.b, a.q_head_stride, a.q_row_stride, a.q_batch_stride) &&
+         encode_map(&tk, a.k, a.dtype, a.d, a.h_k, a.seqlen_k, a.b, a.k_head_stride, a.k_row_stride, a.k_batch_stride) &&
+         encode_map(&tv, a.v, a.dtype, a.d, a.h_k, a.seqlen_k, a.b, a.v_head_stride, a.v_row_stride, a.v_batch_stride);
+  }
+  if (!ok) { *err = "cuTensorMapEncodeTiled failed"; return FA_ERR_CUDA; }
+  cudaError_t e;
+  if (a.dtype == FA_BF16) {
+    auto kern = fwd_tc5_kernel<__nv_bfloat16, 1>;
+    e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+    if (e == cudaSuccess) {
+      kern<<<pl.grid, kThreads, kSmemBytes, st>>>(p, tq, tk, tv);
+      e = cudaGetLastError();
+    }
+  } else {
+    auto kern = fwd_tc5_kernel<__half, 0>;
+    e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+    if (e == cudaSuccess) {
+      kern<<<pl.grid, kThreads, kSmemBytes, st>>>(p, tq, tk, tv);
+      e = cudaGetLastError();
+    }
+  }
+  if (e != cudaSuccess) { *err = std::string("tcgen05 kernel launch: ") + cudaGetErrorString(e); return FA_ERR_CUDA; }
+  return FA_OK;
+}
+
+int tc5_read_status(cudaStream_t st) {
+  int32_t* w = tc5::status_word();
+  if (!w) return 0;
+  int32_t v = 0;
+  if (cudaStreamSynchronize(st) != cudaSuccess) return -1;
+  if (cudaMemcpy(&v, w, sizeof(v), cudaMemcpyDeviceToHost) != cudaSuccess) return -1;
+  if (v != 0) cudaMemset(w, 0, sizeof(v));
+  return v;
 }
 
 }  // namespace fa

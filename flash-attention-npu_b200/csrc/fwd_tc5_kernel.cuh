@@ -1,0 +1,109 @@
+// Prefill attention-forward kernel for sm_100a: tcgen05 MMA with accumulators in TMEM, K/V tiles
+// streamed by TMA through a shared-memory ring, online softmax in registers (one thread per
+// query row), persistent CTAs.
+//
+// It replaces, for dense / varlen prefill, the cube+vector pipeline of the reference kernel
+// (csrc/arch22/flash_attn_npu_v2/mha_fwd_kvcache.cpp:632-965: QK -> online softmax -> PV ->
+// rescale O, with S / P / O_tmp round-tripping through a global workspace).  Here S, P and O never
+// leave the SM: S and O live in TMEM, P overwrites S in TMEM as 16-bit pairs and feeds the second
+// MMA directly.
+//
+// CTA = 10 warps:  warps 0-3  softmax + epilogue of query sub-tile 0 (128 rows)
+//                  warps 4-7  softmax + epilogue of query sub-tile 1 (128 rows)
+//                  warp  8    MMA issuer (one elected lane)
+//                  warp  9    TMA producer (one elected lane)
+// TMEM (512 columns): S0 [0,128)  S1 [128,256)  O0 [256,384)  O1 [384,512); P_t aliases S_t.
+// The two sub-tiles ping-pong: while the softmax warps of one work on S, the tensor core runs
+// P.V of the other and the next Q.K^T.
+#pragma once
+
+#include "common.cuh"
+#include "tc5_ptx.cuh"
+
+namespace fa {
+namespace tc5 {
+
+constexpr int kBlockM = 128;          // rows of one query sub-tile
+constexpr int kTileM = 2 * kBlockM;   // rows of one CTA tile
+constexpr int kBlockN = 128;          // keys per KV block
+constexpr int kSlots = 4;             // ring of 32 KiB K / V buffers
+constexpr int kThreads = 320;
+constexpr int kHalfBytes = kBlockN * 128;   // one 64-column half of a [128 x 128] 16-bit tile (128-byte rows)
+constexpr int kTileBytes = 2 * kHalfBytes;  // 32 KiB
+constexpr int kSmemBytes = 2 * kTileBytes + kSlots * kTileBytes + 1024 /*alignment*/ + 256 /*barriers*/;
+constexpr float kRescaleThreshold = 8.0f;   // log2 units: keep the old max while it is within 2^8
+
+struct Tc5Params {
+  fa_fwd_params a;
+  int32_t is_causal, is_local, wl, wr;
+  int32_t group;    // h / h_k
+  int32_t m_tiles;  // ceil(max seqlen_q / 256)
+  int32_t total_tiles;
+  float scale_log2;
+  int32_t* status;  // device word: 0 ok, otherwise the wait that gave up
+};
+
+struct TileInfo {
+  int bi, hh, hk, q_row0, q_len, k_row0, k_len, koff;
+  int row0[2];  // first row (within the sequence) of each sub-tile
+  int jlo[2], jhi[2];
+  bool has[2];
+  int ulo, uhi;  // union of the block ranges
+};
+
+__device__ __forceinline__ void tile_info(const Tc5Params& p, int n, TileInfo& ti) {
+  const int per_m = p.a.b * p.a.h;
+  const int mt = p.m_tiles - 1 - n / per_m;  // heavy (late, causal) tiles first
+  const int rem = n % per_m;
+  ti.bi = rem / p.a.h;
+  ti.hh = rem % p.a.h;
+  ti.hk = ti.hh / p.group;
+  ti.q_row0 = 0;
+  ti.q_len = p.a.seqlen_q;
+  ti.k_row0 = 0;
+  ti.k_len = p.a.seqlen_k;
+  if (p.a.cu_seqlens_q) {
+    ti.q_row0 = p.a.cu_seqlens_q[ti.bi];
+    ti.q_len = p.a.cu_seqlens_q[ti.bi + 1] - ti.q_row0;
+  }
+  if (p.a.cu_seqlens_k) {
+    ti.k_row0 = p.a.cu_seqlens_k[ti.bi];
+    ti.k_len = p.a.cu_seqlens_k[ti.bi + 1] - ti.k_row0;
+  }
+  ti.koff = ti.k_len - ti.q_len;
+  ti.ulo = 0x7fffffff;
+  ti.uhi = 0;
+#pragma unroll
+  for (int t = 0; t < 2; ++t) {
+    const int r0 = mt * kTileM + t * kBlockM;
+    ti.row0[t] = r0;
+    ti.jlo[t] = ti.jhi[t] = 0;
+    ti.has[t] = false;
+    if (r0 < ti.q_len) {
+      const int i_min = r0, i_max = min(ti.q_len, r0 + kBlockM) - 1;
+      int j_lo = 0, j_hi = ti.k_len;
+      if (p.is_causal) j_hi = min(ti.k_len, i_max + ti.koff + 1);
+      if (p.is_local) {
+        j_hi = min(ti.k_len, i_max + ti.koff + p.wr + 1);
+        j_lo = max(0, i_min + ti.koff - p.wl);
+      }
+      if (j_hi > j_lo) {
+        ti.jlo[t] = j_lo / kBlockN;
+        ti.jhi[t] = ceil_div(j_hi, kBlockN);
+        ti.has[t] = true;
+        ti.ulo = min(ti.ulo, ti.jlo[t]);
+        ti.uhi = max(ti.uhi, ti.jhi[t]);
+      }
+    }
+  }
+  if (ti.uhi == 0) ti.ulo = 0;
+}
+
+struct Barriers {
+  uint64_t q_full[2], q_empty[2], kv_full[kSlots], kv_empty[kSlots], s_full[2], p_full[2], o_done[2], o_free[2];
+  uint32_t tmem_base;
+  int abort_flag;
+};
+
+}  // namespace tc5
+}  // namespace fa

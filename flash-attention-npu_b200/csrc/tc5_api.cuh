@@ -15,5 +15,7 @@ bool tc5_eligible(const fa_fwd_params& a, bool is_causal, bool is_local, int wl_
 // Overwrites the tile fields of the plan for the tcgen05 kernel.
 void tc5_fill_plan(const fa_fwd_params& a, fa_fwd_plan* pl);
 int tc5_launch(const fa_fwd_params& a, const fa_fwd_plan& pl, cudaStream_t st, std::string* err);
+// Synchronises the stream, then returns and clears the device status word (0 = every wait completed).
+int tc5_read_status(cudaStream_t st);
 
 }  // namespace fa

@@ -70,7 +70,7 @@ class CombineParams(C.Structure):
 # every symbol include/fa_b200.h declares
 EXPORTS = (
     "fa_b200_fwd", "fa_b200_fwd_plan", "fa_b200_combine", "fa_b200_normalize_window",
-    "fa_b200_last_error", "fa_b200_status_string", "fa_b200_abi_version",
+    "fa_b200_check_status", "fa_b200_last_error", "fa_b200_status_string", "fa_b200_abi_version",
 )
 
 _lib = None
@@ -93,6 +93,8 @@ def load() -> C.CDLL:
     lib.fa_b200_combine.restype = C.c_int
     lib.fa_b200_normalize_window.argtypes = [_i32, _i32, _i32] + [C.POINTER(_i32)] * 4
     lib.fa_b200_normalize_window.restype = C.c_int
+    lib.fa_b200_check_status.argtypes = [_p]
+    lib.fa_b200_check_status.restype = C.c_int
     lib.fa_b200_last_error.restype = C.c_char_p
     lib.fa_b200_status_string.argtypes = [C.c_int]
     lib.fa_b200_status_string.restype = C.c_char_p

@@ -24,6 +24,7 @@
  *                               (and the Python-level flash_attn_combine,
  *                                flash_attn_npu_v3/interface_arch22.py:930-931)
  *   fa_b200_normalize_window    the window normalisation block, flash_api.cpp:483-494
+ *   fa_b200_check_status        (none: device-side wait watchdog of this library)
  */
 #ifndef FA_B200_H
 #define FA_B200_H
@@ -151,6 +152,12 @@ int fa_b200_combine(const fa_combine_params* p, void* stream);
 /* Host-only window normalisation; writes the normalised window and the two mode flags. */
 int fa_b200_normalize_window(int32_t seqlen_q, int32_t max_seqlen_k, int32_t causal, int32_t* window_left,
                              int32_t* window_right, int32_t* is_causal, int32_t* is_local);
+
+/* Synchronises `stream` and reports whether any bounded device-side wait of earlier launches gave
+ * up (FA_ERR_CUDA) -- the kernels never spin forever; a protocol failure ends up here instead of
+ * a hung GPU.  Clears the flag.  No counterpart in the reference (its kernels block in
+ * CrossCoreWaitFlag, csrc/arch22/flash_attn_npu_v2/mha_fwd_kvcache.cpp:999-1001). */
+int fa_b200_check_status(void* stream);
 
 /* Message of the last error on the calling thread ("" if none). */
 const char* fa_b200_last_error(void);
