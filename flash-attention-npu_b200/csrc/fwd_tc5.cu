@@ -4,6 +4,7 @@
 
 #include <algorithm>
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <mutex>
 #include <string>
@@ -191,6 +192,8 @@ int tc5_launch(const fa_fwd_params& a, const fa_fwd_plan& pl, cudaStream_t st, s
   p.m_tiles = pl.m_blocks;
   p.total_tiles = pl.m_blocks * a.b * a.h;
   p.scale_log2 = a.softmax_scale * kLog2e;
+  p.rescale_threshold = 0.f;
+  if (const char* e = std::getenv("FA_B200_RESCALE_THRESHOLD")) p.rescale_threshold = (float)std::atof(e);  // tuning override
   p.status = status_word();
   if (!p.status) { *err = "cannot allocate the device status word"; return FA_ERR_CUDA; }
   const bool varlen = a.cu_seqlens_q != nullptr;

@@ -31,7 +31,6 @@ constexpr int kThreads = 320;
 constexpr int kHalfBytes = kBlockN * 128;   // one 64-column half of a [128 x 128] 16-bit tile (128-byte rows)
 constexpr int kTileBytes = 2 * kHalfBytes;  // 32 KiB
 constexpr int kSmemBytes = 2 * kTileBytes + kSlots * kTileBytes + 1024 /*alignment*/ + 256 /*barriers*/;
-constexpr float kRescaleThreshold = 8.0f;   // log2 units: keep the old max while it is within 2^8
 
 struct Tc5Params {
   fa_fwd_params a;
@@ -40,6 +39,10 @@ struct Tc5Params {
   int32_t m_tiles;  // ceil(max seqlen_q / 256)
   int32_t total_tiles;
   float scale_log2;
+  // log2 units: the running max is only advanced (and O rescaled) when it grew by more than this.
+  // 0 = always (P <= 1 and the row maximum has P = 1 exactly, like the golden); > 0 trades a few
+  // ulps of P rounding on sharply peaked rows for fewer O rescales.
+  float rescale_threshold;
   int32_t* status;  // device word: 0 ok, otherwise the wait that gave up
 };
 

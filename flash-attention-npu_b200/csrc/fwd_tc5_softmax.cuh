@@ -2,7 +2,7 @@
 // thread per query row (TMEM lane).  Restates the arithmetic of the reference's OnlineSoftmax and
 // RescaleO epilogues (csrc/arch22/flash_attn_npu_v2/online_softmax.hpp:479-803,
 // rescale_o.hpp:299-534) in the log2 domain: P = exp2(S * scale*log2e - m * scale*log2e), P rounded
-// to the input dtype before P.V, O rescaled only when the running max moved by more than 2^8,
+// to the input dtype before P.V, O rescaled only when the running max moved (by more than an optional threshold),
 // final O / l and LSE = m * scale + ln(l).
 #pragma once
 
@@ -82,9 +82,9 @@ __device__ __forceinline__ void softmax_loop(const Tc5Params& p, Barriers* bar, 
         }
       const float blk_max = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
       float m_new = fmaxf(m_run, blk_max);
-      // keep the old reference max while the true max is within 2^8 of it (results stay exact:
-      // numerator and denominator use the same reference)
-      if (m_run != -INFINITY && (m_new - m_run) * scale_log2 <= kRescaleThreshold) m_new = m_run;
+      // optional lazy update: keep the old reference max while the true max is within the threshold
+      // (numerator and denominator use the same reference, so the result stays consistent)
+      if (m_run != -INFINITY && (m_new - m_run) * scale_log2 <= p.rescale_threshold) m_new = m_run;
       const float m_use = (m_new == -INFINITY) ? 0.f : m_new;
       const float corr = fast_exp2((m_run - m_use) * scale_log2);  // 0 when m_run = -inf
       const bool rescale = (m_new != m_run) && (j > ti.jlo[t]);
