@@ -35,8 +35,12 @@ fwd_tc5_kernel(const __grid_constant__ Tc5Params p, const __grid_constant__ CUte
       mbar_init(smem_addr(&bar->q_full[t]), 1);
       mbar_init(smem_addr(&bar->q_empty[t]), 1);
       mbar_init(smem_addr(&bar->s_full[t]), 1);
-      mbar_init(smem_addr(&bar->p_full[t]), 4);
+      mbar_init(smem_addr(&bar->p_full[t][0]), 4);
+      mbar_init(smem_addr(&bar->p_full[t][1]), 4);
+      mbar_init(smem_addr(&bar->corr_ready[t]), 4);
+      mbar_init(smem_addr(&bar->o_ready[t]), 4);
       mbar_init(smem_addr(&bar->o_done[t]), 1);
+      mbar_init(smem_addr(&bar->stats_ready[t]), 4);
       mbar_init(smem_addr(&bar->o_free[t]), 4);
     }
     for (int s = 0; s < kSlots; ++s) {
@@ -46,11 +50,11 @@ fwd_tc5_kernel(const __grid_constant__ Tc5Params p, const __grid_constant__ CUte
     bar->abort_flag = 0;
     fence_barrier_init();
   }
-  if (warp == 8) {
+  if (warp == kMmaWarp) {
     tmem_alloc(smem_addr(&bar->tmem_base), 512);
     tmem_relinquish();
   }
-  if (warp == 9 && lane == 0) {
+  if (warp == kTmaWarp && lane == 0) {
     tma_prefetch_desc(&tm_q);
     tma_prefetch_desc(&tm_k);
     tma_prefetch_desc(&tm_v);
@@ -62,10 +66,12 @@ fwd_tc5_kernel(const __grid_constant__ Tc5Params p, const __grid_constant__ CUte
 
   if (warp < 8) {
     softmax_loop<T>(p, bar, tmem, warp >> 2, warp & 3, lane);
-  } else if (warp == 8) {
+  } else if (warp < 12) {
+    correction_loop<T>(p, bar, tmem, warp & 3, lane);
+  } else if (warp == kMmaWarp) {
     if (lane == 0) mma_loop<AB_FMT>(p, bar, q_smem, kv_smem, tmem);
     __syncwarp();
-  } else {
+  } else if (warp == kTmaWarp) {
     if (lane == 0) producer_loop(p, &tm_q, &tm_k, &tm_v, bar, q_smem, kv_smem);
     __syncwarp();
   }
@@ -79,7 +85,7 @@ fwd_tc5_kernel(const __grid_constant__ Tc5Params p, const __grid_constant__ CUte
     if (tid == 0) atomicExch(p.status, 1 + blockIdx.x);
     __syncthreads();
   }
-  if (warp == 8) {
+  if (warp == kMmaWarp) {
     tc_fence_after();
     tmem_dealloc(tmem, 512);
   }

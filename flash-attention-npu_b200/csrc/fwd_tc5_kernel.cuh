@@ -8,10 +8,12 @@
 // leave the SM: S and O live in TMEM, P overwrites S in TMEM as 16-bit pairs and feeds the second
 // MMA directly.
 //
-// CTA = 10 warps:  warps 0-3  softmax + epilogue of query sub-tile 0 (128 rows)
-//                  warps 4-7  softmax + epilogue of query sub-tile 1 (128 rows)
-//                  warp  8    MMA issuer (one elected lane)
-//                  warp  9    TMA producer (one elected lane)
+// CTA = 16 warps:  warps 0-3    softmax of query sub-tile 0 (128 rows, one thread per row)
+//                  warps 4-7    softmax of query sub-tile 1
+//                  warps 8-11   correction (rescale of O in TMEM when a row maximum moved) and
+//                               epilogue (O / l -> global, LSE) for both sub-tiles
+//                  warp  12     MMA issuer (one elected lane)
+//                  warp  13     TMA producer (one elected lane)      warps 14-15 idle
 // TMEM (512 columns): S0 [0,128)  S1 [128,256)  O0 [256,384)  O1 [384,512); P_t aliases S_t.
 // The two sub-tiles ping-pong: while the softmax warps of one work on S, the tensor core runs
 // P.V of the other and the next Q.K^T.
@@ -27,10 +29,11 @@ constexpr int kBlockM = 128;          // rows of one query sub-tile
 constexpr int kTileM = 2 * kBlockM;   // rows of one CTA tile
 constexpr int kBlockN = 128;          // keys per KV block
 constexpr int kSlots = 4;             // ring of 32 KiB K / V buffers
-constexpr int kThreads = 320;
+constexpr int kThreads = 512;
+constexpr int kMmaWarp = 12, kTmaWarp = 13;
 constexpr int kHalfBytes = kBlockN * 128;   // one 64-column half of a [128 x 128] 16-bit tile (128-byte rows)
 constexpr int kTileBytes = 2 * kHalfBytes;  // 32 KiB
-constexpr int kSmemBytes = 2 * kTileBytes + kSlots * kTileBytes + 1024 /*alignment*/ + 256 /*barriers*/;
+constexpr int kSmemBytes = 2 * kTileBytes + kSlots * kTileBytes + 1024 /*alignment*/ + 4096 /*barriers, row statistics*/;
 
 struct Tc5Params {
   fa_fwd_params a;
@@ -103,9 +106,20 @@ __device__ __forceinline__ void tile_info(const Tc5Params& p, int n, TileInfo& t
 }
 
 struct Barriers {
-  uint64_t q_full[2], q_empty[2], kv_full[kSlots], kv_empty[kSlots], s_full[2], p_full[2], o_done[2], o_free[2];
+  uint64_t q_full[2], q_empty[2], kv_full[kSlots], kv_empty[kSlots];
+  uint64_t s_full[2];      // MMA -> softmax: S_t = Q_t K_j^T is in TMEM
+  // softmax -> MMA: half h (64 keys) of P_t is in TMEM.  One barrier per half: a waiter must never
+  // fall two phases behind a barrier, which two arrivals per block on one barrier would allow.
+  uint64_t p_full[2][2];
+  uint64_t corr_ready[2];  // softmax -> correction: rescale factors of block j are in shared memory
+  uint64_t o_ready[2];     // correction -> MMA: O_t has been rescaled, P.V of block j may accumulate
+  uint64_t o_done[2];      // MMA -> correction: P.V of a block has completed
+  uint64_t stats_ready[2]; // softmax -> correction: final (max, sum) of the tile are in shared memory
+  uint64_t o_free[2];      // correction -> MMA: the epilogue has read O_t
   uint32_t tmem_base;
   int abort_flag;
+  float corr[2][kBlockM];
+  float row_max[2][kBlockM], row_sum[2][kBlockM];
 };
 
 }  // namespace tc5

@@ -63,7 +63,7 @@ __device__ __forceinline__ void mma_loop(const Tc5Params& p, Barriers* bar, uint
   volatile int* abort_flag = &bar->abort_flag;
   constexpr uint32_t idesc_qk = make_idesc(AB_FMT, kBlockM, kBlockN, 0);
   constexpr uint32_t idesc_pv = make_idesc(AB_FMT, kBlockM, 128, 1);
-  uint32_t kv_cnt = 0, q_cnt[2] = {0, 0}, p_cnt[2] = {0, 0}, ofree_cnt[2] = {0, 0};
+  uint32_t kv_cnt = 0, q_cnt[2] = {0, 0}, p_cnt[2] = {0, 0}, ofree_cnt[2] = {0, 0}, oready_cnt[2] = {0, 0};
 
   for (int n = blockIdx.x; n < p.total_tiles; n += gridDim.x) {
     TileInfo ti;
@@ -82,23 +82,30 @@ __device__ __forceinline__ void mma_loop(const Tc5Params& p, Barriers* bar, uint
     auto issue_pv = [&](int t) -> bool {
       const int j = pend_j[t];
       pend_j[t] = -1;
-      if (!mbar_wait(smem_addr(&bar->p_full[t]), p_cnt[t] & 1, abort_flag)) return false;
-      ++p_cnt[t];
-      if (!mbar_wait(smem_addr(&bar->kv_full[pend_slot[t]]), pend_par[t], abort_flag)) return false;
       if (first_pv[t]) {  // the previous tile's epilogue must have read O_t
         if (!mbar_wait(smem_addr(&bar->o_free[t]), (ofree_cnt[t] & 1) ^ 1, abort_flag)) return false;
         ++ofree_cnt[t];
+      } else {            // the correction warps must have rescaled O_t for this block
+        if (!mbar_wait(smem_addr(&bar->o_ready[t]), oready_cnt[t] & 1, abort_flag)) return false;
+        ++oready_cnt[t];
       }
-      tc_fence_after();
+      if (!mbar_wait(smem_addr(&bar->kv_full[pend_slot[t]]), pend_par[t], abort_flag)) return false;
       const uint32_t v_base = kv_smem + pend_slot[t] * kTileBytes;
       const uint32_t d_tmem = tmem + 256 + t * 128;
       const uint32_t a_tmem = tmem + t * 128;
 #pragma unroll
-      for (int ks = 0; ks < kBlockN / 16; ++ks) {
-        // V tile: [half][128 keys][64 cols]: 16 keys per step = 2 KiB; N chunks of 64 columns 16 KiB apart
-        const uint64_t b_desc = make_smem_desc(v_base + ks * 2048, kHalfBytes, 1024);
-        mma_ts(d_tmem, a_tmem + ks * 8, b_desc, idesc_pv, (first_pv[t] && ks == 0) ? 0u : 1u);
+      for (int half = 0; half < 2; ++half) {  // P arrives in two halves of 64 keys
+        if (!mbar_wait(smem_addr(&bar->p_full[t][half]), p_cnt[t] & 1, abort_flag)) return false;
+        tc_fence_after();
+#pragma unroll
+        for (int k4 = 0; k4 < 4; ++k4) {
+          const int ks = half * 4 + k4;
+          // V tile: [half][128 keys][64 cols]: 16 keys per step = 2 KiB; N chunks of 64 columns 16 KiB apart
+          const uint64_t b_desc = make_smem_desc(v_base + ks * 2048, kHalfBytes, 1024);
+          mma_ts(d_tmem, a_tmem + ks * 8, b_desc, idesc_pv, (first_pv[t] && ks == 0) ? 0u : 1u);
+        }
       }
+      ++p_cnt[t];
       first_pv[t] = false;
       mma_commit(smem_addr(&bar->o_done[t]));
       const bool other_uses = (t == 0) && ti.has[1] && j >= ti.jlo[1] && j < ti.jhi[1];

@@ -1,15 +1,57 @@
-// Softmax + epilogue role of the tcgen05 prefill kernel: 128 threads per query sub-tile, one
-// thread per query row (TMEM lane).  Restates the arithmetic of the reference's OnlineSoftmax and
-// RescaleO epilogues (csrc/arch22/flash_attn_npu_v2/online_softmax.hpp:479-803,
-// rescale_o.hpp:299-534) in the log2 domain: P = exp2(S * scale*log2e - m * scale*log2e), P rounded
-// to the input dtype before P.V, O rescaled only when the running max moved (by more than an optional threshold),
-// final O / l and LSE = m * scale + ln(l).
+// Softmax role and correction / epilogue role of the tcgen05 prefill kernel.
+//
+// Softmax: 128 threads per query sub-tile, one thread per query row (TMEM lane).  It restates the
+// arithmetic of the reference's OnlineSoftmax epilogue
+// (csrc/arch22/flash_attn_npu_v2/online_softmax.hpp:479-803) in the log2 domain:
+//   P = exp2(S * scale*log2e - m * scale*log2e), rounded to the input dtype before P.V.
+// S is read from TMEM twice (first for the row maximum, then for the exponentials) 32 columns at a
+// time so that a thread never holds more than two 32-column chunks in registers.
+//
+// Correction: 128 threads serving both sub-tiles.  When a row maximum moved it multiplies O (in
+// TMEM) by exp2((m_old - m_new) * scale*log2e) between two P.V accumulations, off the softmax
+// threads' critical path, and at the end of a tile writes O / l and LSE = m*scale + ln(l)
+// (RescaleO, csrc/arch22/flash_attn_npu_v2/rescale_o.hpp:299-534).
 #pragma once
 
 #include "fwd_tc5_kernel.cuh"
 
 namespace fa {
 namespace tc5 {
+
+__device__ __forceinline__ float chunk_max(const uint32_t (&a)[32], float m) {
+  float m0 = m, m1 = -INFINITY, m2 = -INFINITY, m3 = -INFINITY;
+#pragma unroll
+  for (int e = 0; e < 32; e += 8) {
+    m0 = max3(m0, __uint_as_float(a[e]), __uint_as_float(a[e + 1]));
+    m1 = max3(m1, __uint_as_float(a[e + 2]), __uint_as_float(a[e + 3]));
+    m2 = max3(m2, __uint_as_float(a[e + 4]), __uint_as_float(a[e + 5]));
+    m3 = max3(m3, __uint_as_float(a[e + 6]), __uint_as_float(a[e + 7]));
+  }
+  return fmaxf(fmaxf(m0, m1), fmaxf(m2, m3));
+}
+
+__device__ __forceinline__ void chunk_mask(uint32_t (&a)[32], int col_first, int lo, int hi) {
+#pragma unroll
+  for (int e = 0; e < 32; ++e) {
+    const int col = col_first + e;
+    if (col < lo || col > hi) a[e] = 0xff800000u;  // -inf
+  }
+}
+
+// 32 scores -> 16 packed 16-bit pairs of P, accumulating the fp32 row sum (two partial sums).
+template <typename T>
+__device__ __forceinline__ void chunk_exp(const uint32_t (&a)[32], uint64_t scale2, uint64_t negms2, uint64_t& sum2,
+                                          uint32_t (&pk)[16]) {
+#pragma unroll
+  for (int e = 0; e < 32; e += 2) {
+    const uint64_t x2 = fma_f32x2(pack_f32x2(__uint_as_float(a[e]), __uint_as_float(a[e + 1])), scale2, negms2);
+    float x0, x1;
+    unpack_f32x2(x2, x0, x1);
+    const float p0 = fast_exp2(x0), p1 = fast_exp2(x1);
+    sum2 = add_f32x2(sum2, pack_f32x2(p0, p1));
+    pk[e >> 1] = pack2<T>(p0, p1);
+  }
+}
 
 template <typename T>
 __device__ __forceinline__ void softmax_loop(const Tc5Params& p, Barriers* bar, uint32_t tmem, int t, int warp_in_wg,
@@ -18,24 +60,21 @@ __device__ __forceinline__ void softmax_loop(const Tc5Params& p, Barriers* bar, 
   const int row = warp_in_wg * 32 + lane;
   const uint32_t lane_addr = (uint32_t)(warp_in_wg * 32) << 16;
   const uint32_t s_tmem = tmem + lane_addr + t * 128;
-  const uint32_t o_tmem = tmem + lane_addr + 256 + t * 128;
-  uint32_t s_cnt = 0, od_cnt = 0;
+  uint32_t s_cnt = 0;
   const float scale_log2 = p.scale_log2;
+  const uint64_t scale2 = pack_f32x2(scale_log2, scale_log2);
 
   for (int n = blockIdx.x; n < p.total_tiles; n += gridDim.x) {
     TileInfo ti;
     tile_info(p, n, ti);
     if (ti.row0[t] >= ti.q_len) continue;
     const int i = ti.row0[t] + row;
-    const bool row_valid = i < ti.q_len;
-    T* o_ptr = reinterpret_cast<T*>(p.a.o) + (int64_t)ti.bi * p.a.o_batch_stride +
-               (int64_t)(ti.q_row0 + i) * p.a.o_row_stride + (int64_t)ti.hh * p.a.o_head_stride;
-    float* lse_ptr = p.a.lse + (int64_t)ti.bi * p.a.lse_batch_stride + (int64_t)ti.hh * p.a.lse_head_stride +
-                     ti.q_row0 + i;
-    if (!ti.has[t]) {  // no visible key for the whole sub-tile
-      if (row_valid) {
+    if (!ti.has[t]) {  // no visible key for the whole sub-tile: O = 0, LSE = +inf
+      if (i < ti.q_len) {
+        T* o_ptr = reinterpret_cast<T*>(p.a.o) + (int64_t)ti.bi * p.a.o_batch_stride +
+                   (int64_t)(ti.q_row0 + i) * p.a.o_row_stride + (int64_t)ti.hh * p.a.o_head_stride;
         for (int c = 0; c < p.a.d; c += 8) *reinterpret_cast<uint4*>(o_ptr + c) = make_uint4(0, 0, 0, 0);
-        *lse_ptr = INFINITY;
+        p.a.lse[(int64_t)ti.bi * p.a.lse_batch_stride + (int64_t)ti.hh * p.a.lse_head_stride + ti.q_row0 + i] = INFINITY;
       }
       continue;
     }
@@ -49,113 +88,197 @@ __device__ __forceinline__ void softmax_loop(const Tc5Params& p, Barriers* bar, 
     float m_run = -INFINITY, l_run = 0.f;
 
     for (int j = ti.jlo[t]; j < ti.jhi[t]; ++j) {
-      if (!mbar_wait(smem_addr(&bar->s_full[t]), s_cnt & 1, abort_flag)) return;
-      ++s_cnt;
-      tc_fence_after();
-      uint32_t s[4][32];
-#pragma unroll
-      for (int c = 0; c < 4; ++c) tmem_ld32(s_tmem + c * 32, s[c]);
-      tmem_wait_ld();
-
       const int col0 = j * kBlockN;
       bool need_mask = col0 + kBlockN > ti.k_len;
       if (p.is_causal || p.is_local) need_mask = need_mask || (col0 + kBlockN - 1 > i_min + ti.koff + (p.is_local ? p.wr : 0));
       if (p.is_local) need_mask = need_mask || (col0 < i_max + ti.koff - p.wl);
-      if (need_mask) {
-#pragma unroll
-        for (int c = 0; c < 4; ++c)
-#pragma unroll
-          for (int e = 0; e < 32; ++e) {
-            const int col = col0 + c * 32 + e;
-            if (col < lo || col > hi) s[c][e] = 0xff800000u;  // -inf
-          }
-      }
-      float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
-#pragma unroll
-      for (int c = 0; c < 4; ++c)
-#pragma unroll
-        for (int e = 0; e < 32; e += 4) {
-          mx0 = fmaxf(mx0, __uint_as_float(s[c][e]));
-          mx1 = fmaxf(mx1, __uint_as_float(s[c][e + 1]));
-          mx2 = fmaxf(mx2, __uint_as_float(s[c][e + 2]));
-          mx3 = fmaxf(mx3, __uint_as_float(s[c][e + 3]));
-        }
-      const float blk_max = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
+
+      if (!mbar_wait(smem_addr(&bar->s_full[t]), s_cnt & 1, abort_flag)) return;
+      ++s_cnt;
+      tc_fence_after();
+      uint32_t a[32], b[32];
+      // ---- pass 1: row maximum ----
+      tmem_ld32(s_tmem, a);
+      tmem_ld32(s_tmem + 32, b);
+      tmem_wait_ld();
+      if (need_mask) { chunk_mask(a, col0, lo, hi); chunk_mask(b, col0 + 32, lo, hi); }
+      float blk_max = chunk_max(a, -INFINITY);
+      blk_max = chunk_max(b, blk_max);
+      tmem_ld32(s_tmem + 64, a);
+      tmem_ld32(s_tmem + 96, b);
+      tmem_wait_ld();
+      if (need_mask) { chunk_mask(a, col0 + 64, lo, hi); chunk_mask(b, col0 + 96, lo, hi); }
+      blk_max = chunk_max(a, blk_max);
+      blk_max = chunk_max(b, blk_max);
+      // start re-reading the first chunks while the scalar bookkeeping runs
+      tmem_ld32(s_tmem, a);
+      tmem_ld32(s_tmem + 32, b);
+
       float m_new = fmaxf(m_run, blk_max);
       // optional lazy update: keep the old reference max while the true max is within the threshold
-      // (numerator and denominator use the same reference, so the result stays consistent)
       if (m_run != -INFINITY && (m_new - m_run) * scale_log2 <= p.rescale_threshold) m_new = m_run;
       const float m_use = (m_new == -INFINITY) ? 0.f : m_new;
       const float corr = fast_exp2((m_run - m_use) * scale_log2);  // 0 when m_run = -inf
-      const bool rescale = (m_new != m_run) && (j > ti.jlo[t]);
+      if (j > ti.jlo[t]) {
+        bar->corr[t][row] = (m_new != m_run) ? corr : 1.f;
+        __syncwarp();
+        if (lane == 0) mbar_arrive(smem_addr(&bar->corr_ready[t]));
+      }
       m_run = m_new;
       const float neg_ms = -m_use * scale_log2;
+      const uint64_t negms2 = pack_f32x2(neg_ms, neg_ms);
 
-      float sum0 = 0.f, sum1 = 0.f;
-      uint32_t pk[2][32];
-#pragma unroll
-      for (int c = 0; c < 4; ++c)
-#pragma unroll
-        for (int e = 0; e < 32; e += 2) {
-          const float p0 = fast_exp2(fmaf(__uint_as_float(s[c][e]), scale_log2, neg_ms));
-          const float p1 = fast_exp2(fmaf(__uint_as_float(s[c][e + 1]), scale_log2, neg_ms));
-          sum0 += p0;
-          sum1 += p1;
-          pk[c >> 1][(c & 1) * 16 + (e >> 1)] = pack2<T>(p0, p1);
-        }
-      l_run = l_run * corr + (sum0 + sum1);
-
-      if (j > ti.jlo[t]) {  // P.V of the previous block has finished accumulating into O_t
-        if (!mbar_wait(smem_addr(&bar->o_done[t]), od_cnt & 1, abort_flag)) return;
-        ++od_cnt;
-        if (__any_sync(0xffffffffu, rescale)) {
-          tc_fence_after();
-          const float f = rescale ? corr : 1.f;
-#pragma unroll
-          for (int c = 0; c < 4; ++c) {
-            uint32_t o[32];
-            tmem_ld32(o_tmem + c * 32, o);
-            tmem_wait_ld();
-#pragma unroll
-            for (int e = 0; e < 32; ++e) o[e] = __float_as_uint(__uint_as_float(o[e]) * f);
-            tmem_st32(o_tmem + c * 32, o);
-          }
-        }
-      }
-      tmem_st32(s_tmem, pk[0]);
-      tmem_st32(s_tmem + 32, pk[1]);
+      // ---- pass 2: exponentials, P -> TMEM (overwrites the S columns already consumed) ----
+      uint64_t sum2 = pack_f32x2(0.f, 0.f);
+      uint32_t pk[16];
+      tmem_wait_ld();
+      if (need_mask) { chunk_mask(a, col0, lo, hi); chunk_mask(b, col0 + 32, lo, hi); }
+      chunk_exp<T>(a, scale2, negms2, sum2, pk);
+      tmem_ld32(s_tmem + 64, a);
+      tmem_st16(s_tmem, pk);
+      chunk_exp<T>(b, scale2, negms2, sum2, pk);
+      tmem_ld32(s_tmem + 96, b);
+      tmem_st16(s_tmem + 16, pk);
       tmem_wait_st();
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(smem_addr(&bar->p_full[t]));
-    }
-
-    // ---- epilogue: O_t / l -> global, LSE ----
-    if (!mbar_wait(smem_addr(&bar->o_done[t]), od_cnt & 1, abort_flag)) return;
-    ++od_cnt;
-    tc_fence_after();
-    const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
-#pragma unroll
-    for (int c = 0; c < 4; ++c) {
-      uint32_t o[32];
-      tmem_ld32(o_tmem + c * 32, o);
+      if (lane == 0) mbar_arrive(smem_addr(&bar->p_full[t][0]));  // first 64 keys of P are ready
       tmem_wait_ld();
-      if (row_valid) {
+      if (need_mask) { chunk_mask(a, col0 + 64, lo, hi); chunk_mask(b, col0 + 96, lo, hi); }
+      chunk_exp<T>(a, scale2, negms2, sum2, pk);
+      tmem_st16(s_tmem + 32, pk);
+      chunk_exp<T>(b, scale2, negms2, sum2, pk);
+      tmem_st16(s_tmem + 48, pk);
+      tmem_wait_st();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_addr(&bar->p_full[t][1]));  // last 64 keys
+      float s0, s1;
+      unpack_f32x2(sum2, s0, s1);
+      l_run = l_run * corr + (s0 + s1);
+    }
+    // final statistics for the epilogue
+    bar->row_max[t][row] = m_run;
+    bar->row_sum[t][row] = l_run;
+    __syncwarp();
+    if (lane == 0) mbar_arrive(smem_addr(&bar->stats_ready[t]));
+  }
+}
+
+// Multiplies the 128 fp32 columns of one TMEM lane by f (two chunks in flight).
+__device__ __forceinline__ void rescale_o(uint32_t o_tmem, float f) {
+  const uint64_t f2 = pack_f32x2(f, f);
+  uint32_t a[32], b[32];
+  tmem_ld32(o_tmem, a);
+  tmem_ld32(o_tmem + 32, b);
+  tmem_wait_ld();
 #pragma unroll
-        for (int e = 0; e < 32; e += 8) {
-          uint4 w;
-          w.x = pack2<T>(__uint_as_float(o[e]) * inv, __uint_as_float(o[e + 1]) * inv);
-          w.y = pack2<T>(__uint_as_float(o[e + 2]) * inv, __uint_as_float(o[e + 3]) * inv);
-          w.z = pack2<T>(__uint_as_float(o[e + 4]) * inv, __uint_as_float(o[e + 5]) * inv);
-          w.w = pack2<T>(__uint_as_float(o[e + 6]) * inv, __uint_as_float(o[e + 7]) * inv);
-          *reinterpret_cast<uint4*>(o_ptr + c * 32 + e) = w;
+  for (int half = 0; half < 2; ++half) {
+#pragma unroll
+    for (int e = 0; e < 32; e += 2) {
+      float x0, x1;
+      unpack_f32x2(mul_f32x2(pack_f32x2(__uint_as_float(a[e]), __uint_as_float(a[e + 1])), f2), x0, x1);
+      a[e] = __float_as_uint(x0);
+      a[e + 1] = __float_as_uint(x1);
+      unpack_f32x2(mul_f32x2(pack_f32x2(__uint_as_float(b[e]), __uint_as_float(b[e + 1])), f2), x0, x1);
+      b[e] = __float_as_uint(x0);
+      b[e + 1] = __float_as_uint(x1);
+    }
+    tmem_st32(o_tmem + half * 64, a);
+    tmem_st32(o_tmem + half * 64 + 32, b);
+    if (half == 0) {
+      tmem_ld32(o_tmem + 64, a);
+      tmem_ld32(o_tmem + 96, b);
+      tmem_wait_ld();
+    }
+  }
+  tmem_wait_st();
+}
+
+template <typename T>
+__device__ __forceinline__ void correction_loop(const Tc5Params& p, Barriers* bar, uint32_t tmem, int warp_in_wg,
+                                                int lane) {
+  volatile int* abort_flag = &bar->abort_flag;
+  const int row = warp_in_wg * 32 + lane;
+  const uint32_t lane_addr = (uint32_t)(warp_in_wg * 32) << 16;
+  uint32_t cr_cnt[2] = {0, 0}, od_cnt[2] = {0, 0}, st_cnt[2] = {0, 0};
+
+  for (int n = blockIdx.x; n < p.total_tiles; n += gridDim.x) {
+    TileInfo ti;
+    tile_info(p, n, ti);
+    if (ti.uhi <= ti.ulo) continue;
+    for (int j = ti.ulo; j < ti.uhi; ++j) {
+#pragma unroll
+      for (int t = 0; t < 2; ++t) {
+        if (!(ti.has[t] && j > ti.jlo[t] && j < ti.jhi[t])) continue;
+        if (!mbar_wait(smem_addr(&bar->corr_ready[t]), cr_cnt[t] & 1, abort_flag)) return;
+        ++cr_cnt[t];
+        const float f = bar->corr[t][row];
+        if (!mbar_wait(smem_addr(&bar->o_done[t]), od_cnt[t] & 1, abort_flag)) return;  // P.V of block j-1 done
+        ++od_cnt[t];
+        if (__any_sync(0xffffffffu, f != 1.f)) {
+          tc_fence_after();
+          rescale_o(tmem + lane_addr + 256 + t * 128, f);
+          tc_fence_before();
         }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(smem_addr(&bar->o_ready[t]));
       }
     }
-    tc_fence_before();
-    __syncwarp();
-    if (lane == 0) mbar_arrive(smem_addr(&bar->o_free[t]));
-    if (row_valid) *lse_ptr = l_run > 0.f ? (m_run * p.a.softmax_scale + __logf(l_run)) : INFINITY;
+    // ---- epilogue of both sub-tiles ----
+#pragma unroll
+    for (int t = 0; t < 2; ++t) {
+      if (!ti.has[t]) continue;
+      if (!mbar_wait(smem_addr(&bar->stats_ready[t]), st_cnt[t] & 1, abort_flag)) return;
+      ++st_cnt[t];
+      const float m_run = bar->row_max[t][row], l_run = bar->row_sum[t][row];
+      if (!mbar_wait(smem_addr(&bar->o_done[t]), od_cnt[t] & 1, abort_flag)) return;  // last P.V done
+      ++od_cnt[t];
+      tc_fence_after();
+      const int i = ti.row0[t] + row;
+      const bool row_valid = i < ti.q_len;
+      T* o_ptr = reinterpret_cast<T*>(p.a.o) + (int64_t)ti.bi * p.a.o_batch_stride +
+                 (int64_t)(ti.q_row0 + i) * p.a.o_row_stride + (int64_t)ti.hh * p.a.o_head_stride;
+      const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
+      const uint32_t o_tmem = tmem + lane_addr + 256 + t * 128;
+      uint32_t a[32], b[32];
+      tmem_ld32(o_tmem, a);
+      tmem_ld32(o_tmem + 32, b);
+#pragma unroll
+      for (int half = 0; half < 2; ++half) {
+        tmem_wait_ld();
+        if (row_valid) {
+#pragma unroll
+          for (int e = 0; e < 32; e += 8) {
+            uint4 w;
+            w.x = pack2<T>(__uint_as_float(a[e]) * inv, __uint_as_float(a[e + 1]) * inv);
+            w.y = pack2<T>(__uint_as_float(a[e + 2]) * inv, __uint_as_float(a[e + 3]) * inv);
+            w.z = pack2<T>(__uint_as_float(a[e + 4]) * inv, __uint_as_float(a[e + 5]) * inv);
+            w.w = pack2<T>(__uint_as_float(a[e + 6]) * inv, __uint_as_float(a[e + 7]) * inv);
+            *reinterpret_cast<uint4*>(o_ptr + half * 64 + e) = w;
+          }
+#pragma unroll
+          for (int e = 0; e < 32; e += 8) {
+            uint4 w;
+            w.x = pack2<T>(__uint_as_float(b[e]) * inv, __uint_as_float(b[e + 1]) * inv);
+            w.y = pack2<T>(__uint_as_float(b[e + 2]) * inv, __uint_as_float(b[e + 3]) * inv);
+            w.z = pack2<T>(__uint_as_float(b[e + 4]) * inv, __uint_as_float(b[e + 5]) * inv);
+            w.w = pack2<T>(__uint_as_float(b[e + 6]) * inv, __uint_as_float(b[e + 7]) * inv);
+            *reinterpret_cast<uint4*>(o_ptr + half * 64 + 32 + e) = w;
+          }
+        }
+        if (half == 0) {
+          tmem_ld32(o_tmem + 64, a);
+          tmem_ld32(o_tmem + 96, b);
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_addr(&bar->o_free[t]));
+      if (row_valid)
+        p.a.lse[(int64_t)ti.bi * p.a.lse_batch_stride + (int64_t)ti.hh * p.a.lse_head_stride + ti.q_row0 + i] =
+            l_run > 0.f ? (m_run * p.a.softmax_scale + __logf(l_run)) : INFINITY;
+    }
   }
 }
 
