@@ -18,7 +18,7 @@ INCLUDE = os.path.join(os.path.dirname(HERE), "include")
 LIB = os.path.join(HERE, "libfa_b200.so")
 NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
 FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "--use_fast_math",
-         "-Xcompiler", "-fPIC", "-I", INCLUDE, "-I", CSRC]
+         "-Xcompiler", "-fPIC", "-I", INCLUDE, "-I", CSRC] + os.environ.get("FA_B200_NVCC_FLAGS", "").split()
 
 
 def _newest(paths):

@@ -42,10 +42,11 @@ fwd_tc5_kernel(const __grid_constant__ Tc5Params p, const __grid_constant__ CUte
       mbar_init(smem_addr(&bar->o_done[t]), 1);
       mbar_init(smem_addr(&bar->stats_ready[t]), 4);
       mbar_init(smem_addr(&bar->o_free[t]), 4);
+      mbar_init(smem_addr(&bar->mma_turn[t]), 1);
     }
     for (int s = 0; s < kSlots; ++s) {
       mbar_init(smem_addr(&bar->kv_full[s]), 1);
-      mbar_init(smem_addr(&bar->kv_empty[s]), 1);
+      mbar_init(smem_addr(&bar->kv_empty[s]), 2);
     }
     bar->abort_flag = 0;
     fence_barrier_init();
@@ -64,16 +65,21 @@ fwd_tc5_kernel(const __grid_constant__ Tc5Params p, const __grid_constant__ CUte
   tc_fence_after();
   const uint32_t tmem = bar->tmem_base;
 
+  // Register budget: 512 threads start with 128 registers each; the softmax warps need the 128
+  // scores of a row plus working set, the other roles need far fewer.
   if (warp < 8) {
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 176;\n");
     softmax_loop<T>(p, bar, tmem, warp >> 2, warp & 3, lane);
   } else if (warp < 12) {
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 96;\n");
     correction_loop<T>(p, bar, tmem, warp & 3, lane);
-  } else if (warp == kMmaWarp) {
-    if (lane == 0) mma_loop<AB_FMT>(p, bar, q_smem, kv_smem, tmem);
-    __syncwarp();
+  } else {
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 64;\n");
+  }
+  if (warp == kMmaWarp || warp == kMmaWarp + 1) {
+    mma_loop<AB_FMT>(p, bar, q_smem, kv_smem, tmem, warp - kMmaWarp);  // warp-uniform; one elected lane issues
   } else if (warp == kTmaWarp) {
-    if (lane == 0) producer_loop(p, &tm_q, &tm_k, &tm_v, bar, q_smem, kv_smem);
-    __syncwarp();
+    producer_loop(p, &tm_q, &tm_k, &tm_v, bar, q_smem, kv_smem);  // warp-uniform; one elected lane issues
   }
 
   tc_fence_before();
@@ -202,6 +208,12 @@ int tc5_launch(const fa_fwd_params& a, const fa_fwd_plan& pl, cudaStream_t st, s
   if (const char* e = std::getenv("FA_B200_RESCALE_THRESHOLD")) p.rescale_threshold = (float)std::atof(e);  // tuning override
   p.status = status_word();
   if (!p.status) { *err = "cannot allocate the device status word"; return FA_ERR_CUDA; }
+#ifdef FA_TC5_TRACE
+  static long long* trace_buf = nullptr;
+  if (!trace_buf) cudaMalloc(&trace_buf, sizeof(long long) * kTraceSlots * kTraceLen);
+  cudaMemsetAsync(trace_buf, 0, sizeof(long long) * kTraceSlots * kTraceLen, st);
+  p.trace = trace_buf;
+#endif
   const bool varlen = a.cu_seqlens_q != nullptr;
   CUtensorMap tq, tk, tv;
   bool ok = true;
@@ -234,6 +246,19 @@ int tc5_launch(const fa_fwd_params& a, const fa_fwd_plan& pl, cudaStream_t st, s
     }
   }
   if (e != cudaSuccess) { *err = std::string("tcgen05 kernel launch: ") + cudaGetErrorString(e); return FA_ERR_CUDA; }
+#ifdef FA_TC5_TRACE
+  if (const char* path = std::getenv("FA_B200_TC5_TRACE_FILE")) {
+    static long long host[kTraceSlots * kTraceLen];
+    cudaStreamSynchronize(st);
+    cudaMemcpy(host, trace_buf, sizeof(host), cudaMemcpyDeviceToHost);
+    if (FILE* f = std::fopen(path, "w")) {
+      for (int s = 0; s < kTraceSlots; ++s)
+        for (int i = 0; i < kTraceLen; ++i)
+          if (host[s * kTraceLen + i]) std::fprintf(f, "%d %lld %lld\n", s, host[s * kTraceLen + i] >> 8, host[s * kTraceLen + i] & 255);
+      std::fclose(f);
+    }
+  }
+#endif
   return FA_OK;
 }
 

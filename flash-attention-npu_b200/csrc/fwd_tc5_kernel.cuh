@@ -12,8 +12,8 @@
 //                  warps 4-7    softmax of query sub-tile 1
 //                  warps 8-11   correction (rescale of O in TMEM when a row maximum moved) and
 //                               epilogue (O / l -> global, LSE) for both sub-tiles
-//                  warp  12     MMA issuer (one elected lane)
-//                  warp  13     TMA producer (one elected lane)      warps 14-15 idle
+//                  warps 12-13  MMA issuers, one per sub-tile (one elected lane each)
+//                  warp  14     TMA producer (one elected lane)      warp 15 idle
 // TMEM (512 columns): S0 [0,128)  S1 [128,256)  O0 [256,384)  O1 [384,512); P_t aliases S_t.
 // The two sub-tiles ping-pong: while the softmax warps of one work on S, the tensor core runs
 // P.V of the other and the next Q.K^T.
@@ -30,7 +30,7 @@ constexpr int kTileM = 2 * kBlockM;   // rows of one CTA tile
 constexpr int kBlockN = 128;          // keys per KV block
 constexpr int kSlots = 4;             // ring of 32 KiB K / V buffers
 constexpr int kThreads = 512;
-constexpr int kMmaWarp = 12, kTmaWarp = 13;
+constexpr int kMmaWarp = 12 /* and 13: one per sub-tile */, kTmaWarp = 14;
 constexpr int kHalfBytes = kBlockN * 128;   // one 64-column half of a [128 x 128] 16-bit tile (128-byte rows)
 constexpr int kTileBytes = 2 * kHalfBytes;  // 32 KiB
 constexpr int kSmemBytes = 2 * kTileBytes + kSlots * kTileBytes + 1024 /*alignment*/ + 4096 /*barriers, row statistics*/;
@@ -47,7 +47,29 @@ struct Tc5Params {
   // ulps of P rounding on sharply peaked rows for fewer O rescales.
   float rescale_threshold;
   int32_t* status;  // device word: 0 ok, otherwise the wait that gave up
+#ifdef FA_TC5_TRACE
+  long long* trace;  // [slot][kTraceLen] (clock << 8 | tag), CTA 0 only (debug builds)
+#endif
 };
+
+#ifdef FA_TC5_TRACE
+constexpr int kTraceLen = 2048;
+constexpr int kTraceSlots = 5;
+struct Tracer {
+  long long* buf;
+  int n;
+  __device__ Tracer(const Tc5Params& p, int slot, bool on) : buf(on && blockIdx.x == 0 ? p.trace + slot * kTraceLen : nullptr), n(0) {}
+  __device__ void operator()(int tag) {
+    if (buf && n < kTraceLen) buf[n++] = (clock64() << 8) | (long long)(tag & 255);
+  }
+};
+#define FA_TR(tr, tag) (tr)(tag)
+#else
+struct Tracer {
+  __device__ Tracer(const Tc5Params&, int, bool) {}
+};
+#define FA_TR(tr, tag) ((void)0)
+#endif
 
 struct TileInfo {
   int bi, hh, hk, q_row0, q_len, k_row0, k_len, koff;
@@ -116,6 +138,7 @@ struct Barriers {
   uint64_t o_done[2];      // MMA -> correction: P.V of a block has completed
   uint64_t stats_ready[2]; // softmax -> correction: final (max, sum) of the tile are in shared memory
   uint64_t o_free[2];      // correction -> MMA: the epilogue has read O_t
+  uint64_t mma_turn[2];    // MMA warp <-> MMA warp: whose turn it is to issue
   uint32_t tmem_base;
   int abort_flag;
   float corr[2][kBlockM];

@@ -4,8 +4,8 @@
 // arithmetic of the reference's OnlineSoftmax epilogue
 // (csrc/arch22/flash_attn_npu_v2/online_softmax.hpp:479-803) in the log2 domain:
 //   P = exp2(S * scale*log2e - m * scale*log2e), rounded to the input dtype before P.V.
-// S is read from TMEM twice (first for the row maximum, then for the exponentials) 32 columns at a
-// time so that a thread never holds more than two 32-column chunks in registers.
+// The 128 scores of a row are held in registers (the softmax warps raise their register budget
+// with setmaxnreg, the other roles lower theirs).
 //
 // Correction: 128 threads serving both sub-tiles.  When a row maximum moved it multiplies O (in
 // TMEM) by exp2((m_old - m_new) * scale*log2e) between two P.V accumulations, off the softmax
@@ -61,6 +61,7 @@ __device__ __forceinline__ void softmax_loop(const Tc5Params& p, Barriers* bar, 
   const uint32_t lane_addr = (uint32_t)(warp_in_wg * 32) << 16;
   const uint32_t s_tmem = tmem + lane_addr + t * 128;
   uint32_t s_cnt = 0;
+  Tracer tr(p, t, warp_in_wg == 0 && lane == 0);
   const float scale_log2 = p.scale_log2;
   const uint64_t scale2 = pack_f32x2(scale_log2, scale_log2);
 
@@ -95,24 +96,20 @@ __device__ __forceinline__ void softmax_loop(const Tc5Params& p, Barriers* bar, 
 
       if (!mbar_wait(smem_addr(&bar->s_full[t]), s_cnt & 1, abort_flag)) return;
       ++s_cnt;
+      FA_TR(tr, 1);
       tc_fence_after();
-      uint32_t a[32], b[32];
-      // ---- pass 1: row maximum ----
-      tmem_ld32(s_tmem, a);
-      tmem_ld32(s_tmem + 32, b);
+      // ---- all 128 scores of the row into registers (one TMEM round trip) ----
+      uint32_t sc[4][32];
+#pragma unroll
+      for (int c = 0; c < 4; ++c) tmem_ld32(s_tmem + c * 32, sc[c]);
       tmem_wait_ld();
-      if (need_mask) { chunk_mask(a, col0, lo, hi); chunk_mask(b, col0 + 32, lo, hi); }
-      float blk_max = chunk_max(a, -INFINITY);
-      blk_max = chunk_max(b, blk_max);
-      tmem_ld32(s_tmem + 64, a);
-      tmem_ld32(s_tmem + 96, b);
-      tmem_wait_ld();
-      if (need_mask) { chunk_mask(a, col0 + 64, lo, hi); chunk_mask(b, col0 + 96, lo, hi); }
-      blk_max = chunk_max(a, blk_max);
-      blk_max = chunk_max(b, blk_max);
-      // start re-reading the first chunks while the scalar bookkeeping runs
-      tmem_ld32(s_tmem, a);
-      tmem_ld32(s_tmem + 32, b);
+      if (need_mask) {
+#pragma unroll
+        for (int c = 0; c < 4; ++c) chunk_mask(sc[c], col0 + c * 32, lo, hi);
+      }
+      float blk_max = chunk_max(sc[0], -INFINITY);
+#pragma unroll
+      for (int c = 1; c < 4; ++c) blk_max = chunk_max(sc[c], blk_max);
 
       float m_new = fmaxf(m_run, blk_max);
       // optional lazy update: keep the old reference max while the true max is within the threshold
@@ -124,35 +121,32 @@ __device__ __forceinline__ void softmax_loop(const Tc5Params& p, Barriers* bar, 
         __syncwarp();
         if (lane == 0) mbar_arrive(smem_addr(&bar->corr_ready[t]));
       }
+      FA_TR(tr, 2);
       m_run = m_new;
       const float neg_ms = -m_use * scale_log2;
       const uint64_t negms2 = pack_f32x2(neg_ms, neg_ms);
 
-      // ---- pass 2: exponentials, P -> TMEM (overwrites the S columns already consumed) ----
+      // ---- exponentials, P -> TMEM (overwrites the S columns, which are all in registers now) ----
       uint64_t sum2 = pack_f32x2(0.f, 0.f);
       uint32_t pk[16];
-      tmem_wait_ld();
-      if (need_mask) { chunk_mask(a, col0, lo, hi); chunk_mask(b, col0 + 32, lo, hi); }
-      chunk_exp<T>(a, scale2, negms2, sum2, pk);
-      tmem_ld32(s_tmem + 64, a);
+      chunk_exp<T>(sc[0], scale2, negms2, sum2, pk);
       tmem_st16(s_tmem, pk);
-      chunk_exp<T>(b, scale2, negms2, sum2, pk);
-      tmem_ld32(s_tmem + 96, b);
+      chunk_exp<T>(sc[1], scale2, negms2, sum2, pk);
       tmem_st16(s_tmem + 16, pk);
       tmem_wait_st();
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(smem_addr(&bar->p_full[t][0]));  // first 64 keys of P are ready
-      tmem_wait_ld();
-      if (need_mask) { chunk_mask(a, col0 + 64, lo, hi); chunk_mask(b, col0 + 96, lo, hi); }
-      chunk_exp<T>(a, scale2, negms2, sum2, pk);
+      FA_TR(tr, 3);
+      chunk_exp<T>(sc[2], scale2, negms2, sum2, pk);
       tmem_st16(s_tmem + 32, pk);
-      chunk_exp<T>(b, scale2, negms2, sum2, pk);
+      chunk_exp<T>(sc[3], scale2, negms2, sum2, pk);
       tmem_st16(s_tmem + 48, pk);
       tmem_wait_st();
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(smem_addr(&bar->p_full[t][1]));  // last 64 keys
+      FA_TR(tr, 4);
       float s0, s1;
       unpack_f32x2(sum2, s0, s1);
       l_run = l_run * corr + (s0 + s1);
@@ -202,6 +196,7 @@ __device__ __forceinline__ void correction_loop(const Tc5Params& p, Barriers* ba
   const int row = warp_in_wg * 32 + lane;
   const uint32_t lane_addr = (uint32_t)(warp_in_wg * 32) << 16;
   uint32_t cr_cnt[2] = {0, 0}, od_cnt[2] = {0, 0}, st_cnt[2] = {0, 0};
+  Tracer tr(p, 2, warp_in_wg == 0 && lane == 0);
 
   for (int n = blockIdx.x; n < p.total_tiles; n += gridDim.x) {
     TileInfo ti;
@@ -213,6 +208,7 @@ __device__ __forceinline__ void correction_loop(const Tc5Params& p, Barriers* ba
         if (!(ti.has[t] && j > ti.jlo[t] && j < ti.jhi[t])) continue;
         if (!mbar_wait(smem_addr(&bar->corr_ready[t]), cr_cnt[t] & 1, abort_flag)) return;
         ++cr_cnt[t];
+        FA_TR(tr, 10 + t);
         const float f = bar->corr[t][row];
         if (!mbar_wait(smem_addr(&bar->o_done[t]), od_cnt[t] & 1, abort_flag)) return;  // P.V of block j-1 done
         ++od_cnt[t];
@@ -223,6 +219,7 @@ __device__ __forceinline__ void correction_loop(const Tc5Params& p, Barriers* ba
         }
         __syncwarp();
         if (lane == 0) mbar_arrive(smem_addr(&bar->o_ready[t]));
+        FA_TR(tr, 12 + t);
       }
     }
     // ---- epilogue of both sub-tiles ----
