@@ -16,7 +16,7 @@
 namespace fa {
 namespace tc5 {
 
-template <typename T, uint32_t AB_FMT>
+template <typename T, uint32_t AB_FMT, int POLY>
 __global__ void __launch_bounds__(kThreads, 1)
 fwd_tc5_kernel(const __grid_constant__ Tc5Params p, const __grid_constant__ CUtensorMap tm_q,
                const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v) {
@@ -69,7 +69,7 @@ fwd_tc5_kernel(const __grid_constant__ Tc5Params p, const __grid_constant__ CUte
   // scores of a row plus working set, the other roles need far fewer.
   if (warp < 8) {
     asm volatile("setmaxnreg.inc.sync.aligned.u32 176;\n");
-    softmax_loop<T>(p, bar, tmem, warp >> 2, warp & 3, lane);
+    softmax_loop<T, POLY>(p, bar, tmem, warp >> 2, warp & 3, lane);
   } else if (warp < 12) {
     asm volatile("setmaxnreg.dec.sync.aligned.u32 96;\n");
     correction_loop<T>(p, bar, tmem, warp & 3, lane);
@@ -206,6 +206,8 @@ int tc5_launch(const fa_fwd_params& a, const fa_fwd_plan& pl, cudaStream_t st, s
   p.scale_log2 = a.softmax_scale * kLog2e;
   p.rescale_threshold = 0.f;
   if (const char* e = std::getenv("FA_B200_RESCALE_THRESHOLD")) p.rescale_threshold = (float)std::atof(e);  // tuning override
+  if (const char* e = std::getenv("FA_B200_TC5_WAIT_FULL_P")) p.tune_wait_full_p = std::atoi(e);
+  if (const char* e = std::getenv("FA_B200_TC5_POLY")) p.tune_poly = std::atoi(e);
   p.status = status_word();
   if (!p.status) { *err = "cannot allocate the device status word"; return FA_ERR_CUDA; }
 #ifdef FA_TC5_TRACE
@@ -229,21 +231,20 @@ int tc5_launch(const fa_fwd_params& a, const fa_fwd_plan& pl, cudaStream_t st, s
          encode_map(&tv, a.v, a.dtype, a.d, a.h_k, a.seqlen_k, a.b, a.v_head_stride, a.v_row_stride, a.v_batch_stride);
   }
   if (!ok) { *err = "cuTensorMapEncodeTiled failed"; return FA_ERR_CUDA; }
-  cudaError_t e;
-  if (a.dtype == FA_BF16) {
-    auto kern = fwd_tc5_kernel<__nv_bfloat16, 1>;
+  cudaError_t e = cudaErrorInvalidValue;
+  auto launch = [&](auto kern) {
     e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
     if (e == cudaSuccess) {
       kern<<<pl.grid, kThreads, kSmemBytes, st>>>(p, tq, tk, tv);
       e = cudaGetLastError();
     }
-  } else {
-    auto kern = fwd_tc5_kernel<__half, 0>;
-    e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
-    if (e == cudaSuccess) {
-      kern<<<pl.grid, kThreads, kSmemBytes, st>>>(p, tq, tk, tv);
-      e = cudaGetLastError();
-    }
+  };
+  const bool bf = a.dtype == FA_BF16;
+  switch (p.tune_poly) {
+    case 0: bf ? launch(fwd_tc5_kernel<__nv_bfloat16, 1, 0>) : launch(fwd_tc5_kernel<__half, 0, 0>); break;
+    case 1: bf ? launch(fwd_tc5_kernel<__nv_bfloat16, 1, 1>) : launch(fwd_tc5_kernel<__half, 0, 1>); break;
+    case 2: bf ? launch(fwd_tc5_kernel<__nv_bfloat16, 1, 2>) : launch(fwd_tc5_kernel<__half, 0, 2>); break;
+    default: bf ? launch(fwd_tc5_kernel<__nv_bfloat16, 1, 3>) : launch(fwd_tc5_kernel<__half, 0, 3>); break;
   }
   if (e != cudaSuccess) { *err = std::string("tcgen05 kernel launch: ") + cudaGetErrorString(e); return FA_ERR_CUDA; }
 #ifdef FA_TC5_TRACE

@@ -46,6 +46,8 @@ struct Tc5Params {
   // 0 = always (P <= 1 and the row maximum has P = 1 exactly, like the golden); > 0 trades a few
   // ulps of P rounding on sharply peaked rows for fewer O rescales.
   float rescale_threshold;
+  int32_t tune_wait_full_p;  // experiment: the MMA warp waits for all of P before taking its turn
+  int32_t tune_poly;         // experiment: exponentials evaluated by polynomial out of every 4 pairs
   int32_t* status;  // device word: 0 ok, otherwise the wait that gave up
 #ifdef FA_TC5_TRACE
   long long* trace;  // [slot][kTraceLen] (clock << 8 | tag), CTA 0 only (debug builds)

@@ -137,6 +137,7 @@ __device__ __forceinline__ void mma_loop(const Tc5Params& p, Barriers* bar, uint
 #pragma unroll
       for (int ks = 0; ks < 8; ++ks) vd[ks] = v_desc + (uint64_t)(ks * (2048 >> 4));
       if (!mbar_wait(bar_pfull0, p_cnt & 1, abort_flag)) return false;  // first 64 keys of P
+      if (p.tune_wait_full_p && !mbar_wait(bar_pfull1, p_cnt & 1, abort_flag)) return false;
       if (!mbar_wait(bar_turn_mine, (turn_cnt & 1) ^ turn_flip, abort_flag)) return false;
       have_turn = true;
       FA_TR(tr, 24);

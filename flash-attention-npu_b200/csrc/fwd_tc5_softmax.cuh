@@ -38,22 +38,53 @@ __device__ __forceinline__ void chunk_mask(uint32_t (&a)[32], int col_first, int
   }
 }
 
+// exp2 of two values on the FMA / ALU pipes instead of the special-function unit, which is the
+// co-bottleneck of this kernel (16 exponentials per clock per SM against 8192 tensor flops per clock).
+// x = n + f with n = round(x), f in [-0.5, 0.5]; 2^f by a degree-4 minimax polynomial (relative
+// error 2.7e-6, far below the rounding of P to 16 bits); n is added to the exponent field.
+__device__ __forceinline__ void poly_exp2_x2(uint64_t x2, float& p0, float& p1) {
+  float x0, x1;
+  unpack_f32x2(x2, x0, x1);
+  x2 = pack_f32x2(fmaxf(x0, -126.f), fmaxf(x1, -126.f));
+  const uint64_t magic2 = pack_f32x2(12582912.f, 12582912.f);  // 1.5 * 2^23: adds round(x) into the mantissa
+  const uint64_t xf2 = add_f32x2(x2, magic2);
+  const uint64_t xi2 = add_f32x2(xf2, pack_f32x2(-12582912.f, -12582912.f));
+  const uint64_t f2 = fma_f32x2(xi2, pack_f32x2(-1.f, -1.f), x2);
+  uint64_t r2 = pack_f32x2(0.009570096619427204f, 0.009570096619427204f);
+  r2 = fma_f32x2(r2, f2, pack_f32x2(0.05591785907745361f, 0.05591785907745361f));
+  r2 = fma_f32x2(r2, f2, pack_f32x2(0.240247443318367f, 0.240247443318367f));
+  r2 = fma_f32x2(r2, f2, pack_f32x2(0.6931217908859253f, 0.6931217908859253f));
+  r2 = fma_f32x2(r2, f2, pack_f32x2(0.9999992847442627f, 0.9999992847442627f));
+  float r0, r1, n0, n1;
+  unpack_f32x2(r2, r0, r1);
+  unpack_f32x2(xf2, n0, n1);
+  p0 = __uint_as_float(__float_as_uint(r0) + (__float_as_uint(n0) << 23));
+  p1 = __uint_as_float(__float_as_uint(r1) + (__float_as_uint(n1) << 23));
+}
+
 // 32 scores -> 16 packed 16-bit pairs of P, accumulating the fp32 row sum (two partial sums).
-template <typename T>
-__device__ __forceinline__ void chunk_exp(const uint32_t (&a)[32], uint64_t scale2, uint64_t negms2, uint64_t& sum2,
+// POLY of every 4 pairs use the polynomial, the others the special-function unit.
+template <typename T, int POLY>
+__device__ __forceinline__ void chunk_exp(const uint32_t (&a)[32], uint64_t scale2, uint64_t negms2, uint64_t (&sum2)[4],
                                           uint32_t (&pk)[16]) {
 #pragma unroll
   for (int e = 0; e < 32; e += 2) {
     const uint64_t x2 = fma_f32x2(pack_f32x2(__uint_as_float(a[e]), __uint_as_float(a[e + 1])), scale2, negms2);
-    float x0, x1;
-    unpack_f32x2(x2, x0, x1);
-    const float p0 = fast_exp2(x0), p1 = fast_exp2(x1);
-    sum2 = add_f32x2(sum2, pack_f32x2(p0, p1));
+    float p0, p1;
+    if (((e >> 1) & 3) < POLY) {
+      poly_exp2_x2(x2, p0, p1);
+    } else {
+      float x0, x1;
+      unpack_f32x2(x2, x0, x1);
+      p0 = fast_exp2(x0);
+      p1 = fast_exp2(x1);
+    }
+    sum2[(e >> 1) & 3] = add_f32x2(sum2[(e >> 1) & 3], pack_f32x2(p0, p1));  // four independent chains
     pk[e >> 1] = pack2<T>(p0, p1);
   }
 }
 
-template <typename T>
+template <typename T, int POLY>
 __device__ __forceinline__ void softmax_loop(const Tc5Params& p, Barriers* bar, uint32_t tmem, int t, int warp_in_wg,
                                              int lane) {
   volatile int* abort_flag = &bar->abort_flag;
@@ -127,20 +158,22 @@ __device__ __forceinline__ void softmax_loop(const Tc5Params& p, Barriers* bar, 
       const uint64_t negms2 = pack_f32x2(neg_ms, neg_ms);
 
       // ---- exponentials, P -> TMEM (overwrites the S columns, which are all in registers now) ----
-      uint64_t sum2 = pack_f32x2(0.f, 0.f);
+      uint64_t sum2[4];
+#pragma unroll
+      for (int q = 0; q < 4; ++q) sum2[q] = pack_f32x2(0.f, 0.f);
       uint32_t pk[16];
-      chunk_exp<T>(sc[0], scale2, negms2, sum2, pk);
+      chunk_exp<T, POLY>(sc[0], scale2, negms2, sum2, pk);
       tmem_st16(s_tmem, pk);
-      chunk_exp<T>(sc[1], scale2, negms2, sum2, pk);
+      chunk_exp<T, POLY>(sc[1], scale2, negms2, sum2, pk);
       tmem_st16(s_tmem + 16, pk);
       tmem_wait_st();
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(smem_addr(&bar->p_full[t][0]));  // first 64 keys of P are ready
       FA_TR(tr, 3);
-      chunk_exp<T>(sc[2], scale2, negms2, sum2, pk);
+      chunk_exp<T, POLY>(sc[2], scale2, negms2, sum2, pk);
       tmem_st16(s_tmem + 32, pk);
-      chunk_exp<T>(sc[3], scale2, negms2, sum2, pk);
+      chunk_exp<T, POLY>(sc[3], scale2, negms2, sum2, pk);
       tmem_st16(s_tmem + 48, pk);
       tmem_wait_st();
       tc_fence_before();
@@ -148,7 +181,7 @@ __device__ __forceinline__ void softmax_loop(const Tc5Params& p, Barriers* bar, 
       if (lane == 0) mbar_arrive(smem_addr(&bar->p_full[t][1]));  // last 64 keys
       FA_TR(tr, 4);
       float s0, s1;
-      unpack_f32x2(sum2, s0, s1);
+      unpack_f32x2(add_f32x2(add_f32x2(sum2[0], sum2[1]), add_f32x2(sum2[2], sum2[3])), s0, s1);
       l_run = l_run * corr + (s0 + s1);
     }
     // final statistics for the epilogue
