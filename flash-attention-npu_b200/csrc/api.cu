@@ -267,9 +267,61 @@ static int run_fwd(const fa_fwd_params& a, void* workspace, size_t workspace_byt
   return FA_OK;
 }
 
+// ------------------------------------------------------------------------------------------------
+// Allocation-free variant of the split-KV path.
+//
+// Some hosts may not allocate device memory once they are running: a serving process whose whole
+// memory budget is carved up at start-up, a runtime that owns the GPU heap through its own arena,
+// a latency-critical loop that forbids allocator calls.  For them the split partials live in this
+// file-scope device array instead of a caller-supplied workspace.  Every GPU that loads the library
+// holds kNoAllocScratchBytes of it until the process exits.
+//
+// In host code `g_noalloc_scratch` is only a stand-in for the symbol, not a device address; the
+// address is obtained once per device, with that device current, through cudaGetSymbolAddress.
+// ------------------------------------------------------------------------------------------------
+constexpr size_t kNoAllocScratchBytes = 32u << 20;
+static __device__ __align__(256) unsigned char g_noalloc_scratch[kNoAllocScratchBytes];
+
+static int noalloc_scratch_ptr(void** out) {
+  static void* ptrs[64] = {nullptr};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return fail(FA_ERR_CUDA, "cannot query the current device");
+  if (!ptrs[dev]) {
+    void* ptr = nullptr;
+    cudaError_t e = cudaGetSymbolAddress(&ptr, g_noalloc_scratch);
+    if (e != cudaSuccess || !ptr)
+      return fail(FA_ERR_CUDA, std::string("cudaGetSymbolAddress(scratch): ") + cudaGetErrorString(e));
+    ptrs[dev] = ptr;
+  }
+  *out = ptrs[dev];
+  return FA_OK;
+}
+
+static int run_fwd_noalloc(const fa_fwd_params& a_in, cudaStream_t st) {
+  fa_fwd_params a = a_in;
+  a.kernel = FA_KERNEL_MMA;  // the register-accumulator kernel and the merge allocate nothing
+  Planned P;
+  int rc = make_plan(a, &P);
+  if (rc != FA_OK) return rc;
+  if (P.pl.workspace_bytes > kNoAllocScratchBytes)
+    return fail(FA_ERR_WORKSPACE, "this problem needs " + std::to_string(P.pl.workspace_bytes) +
+                                      " bytes of split-KV scratch but the built-in scratch array holds " +
+                                      std::to_string(kNoAllocScratchBytes) + "; lower num_splits or use fa_b200_fwd");
+  void* scratch = nullptr;
+  rc = noalloc_scratch_ptr(&scratch);
+  if (rc != FA_OK) return rc;
+  return run_fwd(a, scratch, kNoAllocScratchBytes, st);
+}
+
 }  // namespace fa
 
 extern "C" {
+
+int fa_b200_fwd_noalloc(const fa_fwd_params* p, void* stream) {
+  if (!p) return fa::fail(FA_ERR_INVALID, "null params");
+  fa::g_err.clear();
+  return fa::run_fwd_noalloc(*p, reinterpret_cast<cudaStream_t>(stream));
+}
 
 int fa_b200_fwd(const fa_fwd_params* p, void* workspace, size_t workspace_bytes, void* stream) {
   if (!p) return fa::fail(FA_ERR_INVALID, "null params");

@@ -69,7 +69,7 @@ class CombineParams(C.Structure):
 
 # every symbol include/fa_b200.h declares
 EXPORTS = (
-    "fa_b200_fwd", "fa_b200_fwd_plan", "fa_b200_combine", "fa_b200_normalize_window",
+    "fa_b200_fwd", "fa_b200_fwd_noalloc", "fa_b200_fwd_plan", "fa_b200_combine", "fa_b200_normalize_window",
     "fa_b200_check_status", "fa_b200_last_error", "fa_b200_status_string", "fa_b200_abi_version",
 )
 
@@ -87,6 +87,8 @@ def load() -> C.CDLL:
     lib = C.CDLL(LIB_PATH)
     lib.fa_b200_fwd.argtypes = [C.POINTER(FwdParams), _p, C.c_size_t, _p]
     lib.fa_b200_fwd.restype = C.c_int
+    lib.fa_b200_fwd_noalloc.argtypes = [C.POINTER(FwdParams), _p]
+    lib.fa_b200_fwd_noalloc.restype = C.c_int
     lib.fa_b200_fwd_plan.argtypes = [C.POINTER(FwdParams), C.POINTER(FwdPlan)]
     lib.fa_b200_fwd_plan.restype = C.c_int
     lib.fa_b200_combine.argtypes = [C.POINTER(CombineParams), _p]

@@ -166,6 +166,20 @@ def attention_forward(q, k, v, *, out=None, return_plan=False, **kw) -> Tuple[to
     return out, lse
 
 
+def attention_forward_noalloc(q, k, v, out, lse, **kw) -> None:
+    """Same forward as ``attention_forward`` through ``fa_b200_fwd_noalloc``: the caller passes the
+    output tensors (``out`` like q, ``lse`` fp32 (b, h, s_q) or (h, total_q)) and the library
+    allocates nothing -- the split-KV scratch is a fixed 32 MiB array inside the library.  Meant
+    for hosts that may not touch an allocator while serving.  Calls that overlap on the GPU share
+    that scratch and race; the first call on a device should not be made under stream capture."""
+    lib = L.load()
+    if not (q.is_cuda and k.is_cuda and v.is_cuda and out.is_cuda and lse.is_cuda):
+        raise RuntimeError("flash_b200 runs on CUDA tensors only (there is no CPU implementation)")
+    with torch.cuda.device(q.device):
+        p = build_params(q, k, v, out, lse, num_sm=_num_sm(q.device), **kw)
+        L.check(lib.fa_b200_fwd_noalloc(C.byref(p), torch.cuda.current_stream(q.device).cuda_stream))
+
+
 def combine(o_partial: torch.Tensor, lse_partial: torch.Tensor, out: Optional[torch.Tensor] = None,
             out_dtype: Optional[torch.dtype] = None, partial_out: bool = False):
     """Merge of split partials.  o_partial (n, b, s, h, d) fp32, lse_partial (n, b, s, h) fp32

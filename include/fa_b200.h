@@ -25,6 +25,7 @@
  *                                flash_attn_npu_v3/interface_arch22.py:930-931)
  *   fa_b200_normalize_window    the window normalisation block, flash_api.cpp:483-494
  *   fa_b200_check_status        (none: device-side wait watchdog of this library)
+ *   fa_b200_fwd_noalloc         (none: allocation-free variant of fa_b200_fwd)
  */
 #ifndef FA_B200_H
 #define FA_B200_H
@@ -141,6 +142,19 @@ typedef struct fa_combine_params {
  * in-place append + rotary, split-KV with its merge.  `workspace` (device memory, 256-byte
  * aligned) must hold fa_fwd_plan.workspace_bytes; it may be NULL when that is 0. */
 int fa_b200_fwd(const fa_fwd_params* p, void* workspace, size_t workspace_bytes, void* stream);
+
+/* fa_b200_fwd for callers that must not allocate device memory: same arguments and results,
+ * but the split-KV partials go to a 32 MiB array that is part of the library image (every GPU
+ * that loads the library holds it until the process exits) instead of a caller workspace, and the
+ * call makes no cudaMalloc / cudaFree or any other allocating call.  It always uses the
+ * register-accumulator kernel.  A problem whose plan needs more than 32 MiB of scratch is
+ * refused with FA_ERR_WORKSPACE (pass a smaller num_splits, or use fa_b200_fwd).
+ * The first call on a device looks up the array's device address; make that first call outside
+ * any stream capture.  All calls share the one array, which keeps the previous call's contents
+ * (nothing in it needs clearing: every slot that is read is written first), so two calls that
+ * overlap on the GPU -- different streams or threads -- race on it.
+ * This entry point has no counterpart in the reference. */
+int fa_b200_fwd_noalloc(const fa_fwd_params* p, void* stream);
 
 /* Host-only: validates `p` and reports what fa_b200_fwd would launch.  Needs no GPU when
  * p->num_sm > 0. */
