@@ -12,6 +12,7 @@
 #include <string>
 
 #include "combine.cuh"
+#include "decode_configs.cuh"
 #include "mma_configs.cuh"
 #include "tc5_api.cuh"
 
@@ -115,6 +116,35 @@ static int make_plan(const fa_fwd_params& a, Planned* out) {
   }
   MmaConfigInfo ci;
   if (!mma_config_info(hd_pad, cfg, &ci)) return fail(FA_ERR_UNSUPPORTED, "no tile configuration");
+  // ---- producer / consumer decode kernel: <= 32 packed rows, head dim <= 128 (> 64), rows that can
+  //      be moved by 16-byte aligned bulk copies ----
+  int kernel_id = FA_KERNEL_MMA;
+  {
+    auto al16 = [](const void* ptr) { return (reinterpret_cast<uintptr_t>(ptr) & 15) == 0; };
+    const bool strides_ok = a.k_row_stride % 8 == 0 && a.k_head_stride % 8 == 0 && a.k_batch_stride % 8 == 0 &&
+                            a.v_row_stride % 8 == 0 && a.v_head_stride % 8 == 0 && a.v_batch_stride % 8 == 0;
+    // K / V stages are fetched by tiled TMA loads: exact head dim 128, 16-byte aligned strides, a
+    // per-sequence length vector, and pages that hold whole key blocks
+    const bool eligible = a.d == 128 && rows_max <= 32 && rows_max > 0 && !a.cu_seqlens_k && strides_ok &&
+                          al16(a.k) && al16(a.v) && a.k_batch_stride > 0 && a.v_batch_stride > 0 &&
+                          (!a.block_table || a.page_size % 128 == 0);
+    if (a.kernel == FA_KERNEL_DECODE && !eligible)
+      return fail(FA_ERR_UNSUPPORTED, "the decode kernel does not cover this problem");
+    if (eligible && (a.kernel == FA_KERNEL_DECODE || a.kernel == FA_KERNEL_AUTO)) {
+      int dcfg = rows_max <= 16 ? 0 : 4;
+      if (const char* e = std::getenv("FA_B200_DECODE_CONFIG")) {  // tuning override: decode tile configuration
+        const int forced = std::atoi(e);
+        DecodeConfigInfo t;
+        if (decode_config_info(hd_pad, forced, &t) && t.block_m >= rows_max) dcfg = forced;
+      }
+      DecodeConfigInfo di;
+      if (decode_config_info(hd_pad, dcfg, &di)) {
+        kernel_id = FA_KERNEL_DECODE;
+        cfg = dcfg;
+        ci = MmaConfigInfo{di.block_m, di.block_n, di.threads, di.smem_bytes};
+      }
+    }
+  }
   const int m_blocks = std::max(1, ceil_div(rows_max, ci.block_m));
   const int heads_eff = a.h / gp;
 
@@ -151,7 +181,7 @@ static int make_plan(const fa_fwd_params& a, Planned* out) {
   }
 
   fa_fwd_plan& pl = out->pl;
-  pl.kernel = FA_KERNEL_MMA;
+  pl.kernel = kernel_id;
   pl.config = cfg;
   pl.pack_gqa = pack;
   pl.block_m = ci.block_m;
@@ -186,7 +216,7 @@ static int make_plan(const fa_fwd_params& a, Planned* out) {
   kp.lse_elems = lse_elems;
 
   // ---- tcgen05 prefill kernel eligibility ----
-  if (a.kernel != FA_KERNEL_MMA && tc5_eligible(a, is_causal, is_local, wl_on_device)) {
+  if (a.kernel != FA_KERNEL_MMA && a.kernel != FA_KERNEL_DECODE && tc5_eligible(a, is_causal, is_local, wl_on_device)) {
     tc5_fill_plan(a, &pl);
   } else if (a.kernel == FA_KERNEL_TCGEN05) {
     return fail(FA_ERR_UNSUPPORTED, "the tcgen05 kernel does not cover this problem");
@@ -226,6 +256,19 @@ static int run_fwd(const fa_fwd_params& a, void* workspace, size_t workspace_byt
   }
   cudaError_t e = cudaErrorInvalidValue;
   const bool bf = a.dtype == FA_BF16;
+  if (P.pl.kernel == FA_KERNEL_DECODE) {
+    kp.status = device_status_word();
+    CUtensorMap tm_k, tm_v;
+    const bool paged = a.block_table != nullptr;
+    // the outer extent (cache rows / pages) is not part of the parameters; it only bounds the TMA's
+    // out-of-range check, which the kernel never relies on in that dimension
+    const int64_t rows = paged ? a.page_size : a.seqlen_k, outer = int64_t(1) << 30;
+    if (!tma_encode_rows(&tm_k, a.k, a.dtype, a.d, a.h_k, rows, outer, a.k_head_stride, a.k_row_stride, a.k_batch_stride, P.pl.block_n) ||
+        !tma_encode_rows(&tm_v, a.v, a.dtype, a.d, a.h_k, rows, outer, a.v_head_stride, a.v_row_stride, a.v_batch_stride, P.pl.block_n))
+      return fail(FA_ERR_CUDA, "cuTensorMapEncodeTiled failed for the KV cache");
+    e = bf ? launch_decode_128_bf16(P.pl.config, kp, tm_k, tm_v, P.pl.grid, st)
+           : launch_decode_128_fp16(P.pl.config, kp, tm_k, tm_v, P.pl.grid, st);
+  } else
   switch (P.hd_pad) {
     case 64: e = bf ? launch_mma_64_bf16(P.pl.config, kp, P.pl.grid, st) : launch_mma_64_fp16(P.pl.config, kp, P.pl.grid, st); break;
     case 128: e = bf ? launch_mma_128_bf16(P.pl.config, kp, P.pl.grid, st) : launch_mma_128_fp16(P.pl.config, kp, P.pl.grid, st); break;

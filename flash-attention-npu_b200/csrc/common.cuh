@@ -28,6 +28,7 @@ struct KParams {
   float* o_partial;   // [split][lse_index][d] fp32 (num_splits > 1)
   float* lse_partial; // [split][lse_index]
   int64_t lse_elems;  // elements of the LSE tensor
+  int32_t* status;    // device status word (bounded waits that gave up), may be null
 };
 
 __host__ __device__ inline int ceil_div(int a, int b) { return (a + b - 1) / b; }

@@ -1,0 +1,37 @@
+// Tile configurations of the producer / consumer decode kernel (head dim padded to 128).
+//   X(index, MT, NCW, BN, STAGES)      MT = 1: <= 16 packed rows, MT = 2: <= 32 packed rows
+#pragma once
+
+#include <cuda.h>
+
+#include "fwd_decode.cuh"
+
+#define FA_DECODE_CONFIGS_128(X) \
+  X(0, 1, 4, 64, 5) X(1, 1, 8, 128, 3) X(2, 1, 4, 64, 2) X(3, 1, 4, 64, 3) \
+  X(4, 2, 4, 64, 5) X(5, 2, 8, 128, 3) X(6, 2, 4, 64, 3) X(7, 1, 8, 128, 2) X(8, 2, 8, 128, 2)
+
+namespace fa {
+
+struct DecodeConfigInfo {
+  int block_m, block_n, threads, smem_bytes;
+};
+
+inline bool decode_config_info(int hd, int cfg, DecodeConfigInfo* out) {
+  if (hd != 128) return false;
+#define FA_X(I_, MT_, NCW_, BN_, ST_)                                                 \
+  if (cfg == I_) {                                                                    \
+    using Tr = DecTraits<128, __nv_bfloat16, MT_, NCW_, BN_, ST_>;                    \
+    *out = DecodeConfigInfo{Tr::BM, Tr::BN, Tr::NTHREADS, Tr::SMEM_BYTES};            \
+    return true;                                                                      \
+  }
+  FA_DECODE_CONFIGS_128(FA_X)
+#undef FA_X
+  return false;
+}
+
+cudaError_t launch_decode_128_bf16(int cfg, const KParams& p, const CUtensorMap& tm_k, const CUtensorMap& tm_v, int grid,
+                                   cudaStream_t st);
+cudaError_t launch_decode_128_fp16(int cfg, const KParams& p, const CUtensorMap& tm_k, const CUtensorMap& tm_v, int grid,
+                                   cudaStream_t st);
+
+}  // namespace fa

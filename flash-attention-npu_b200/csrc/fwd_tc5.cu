@@ -119,13 +119,13 @@ static EncodeFn get_encode() {
 
 // (d, heads, rows, batch) view of a (batch, rows, heads, d)-strided 16-bit tensor; box = 64 x 1 x 128 x 1.
 static bool encode_map(CUtensorMap* m, const void* ptr, int dtype, int d, int heads, int64_t rows, int64_t batch,
-                       int64_t head_stride, int64_t row_stride, int64_t batch_stride) {
+                       int64_t head_stride, int64_t row_stride, int64_t batch_stride, int box_rows = kBlockN) {
   EncodeFn enc = get_encode();
   if (!enc) return false;
   cuuint64_t dims[4] = {(cuuint64_t)d, (cuuint64_t)heads, (cuuint64_t)rows, (cuuint64_t)batch};
   cuuint64_t strides[3] = {(cuuint64_t)head_stride * 2, (cuuint64_t)row_stride * 2, (cuuint64_t)batch_stride * 2};
   if (batch == 1) strides[2] = (cuuint64_t)rows * row_stride * 2;
-  cuuint32_t box[4] = {64, 1, (cuuint32_t)kBlockN, 1};
+  cuuint32_t box[4] = {64, 1, (cuuint32_t)box_rows, 1};
   cuuint32_t estr[4] = {1, 1, 1, 1};
   CUresult r = enc(m, dtype == FA_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 4,
                    const_cast<void*>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
@@ -261,6 +261,13 @@ int tc5_launch(const fa_fwd_params& a, const fa_fwd_plan& pl, cudaStream_t st, s
   }
 #endif
   return FA_OK;
+}
+
+int32_t* device_status_word() { return tc5::status_word(); }
+
+bool tma_encode_rows(CUtensorMap* m, const void* ptr, int dtype, int d, int heads, int64_t rows, int64_t outer,
+                     int64_t head_stride, int64_t row_stride, int64_t outer_stride, int box_rows) {
+  return tc5::encode_map(m, ptr, dtype, d, heads, rows, outer, head_stride, row_stride, outer_stride, box_rows);
 }
 
 int tc5_read_status(cudaStream_t st) {

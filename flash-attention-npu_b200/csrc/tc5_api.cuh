@@ -1,6 +1,7 @@
 // Interface between the host planner and the tcgen05 / TMEM / TMA prefill kernel.
 #pragma once
 
+#include <cuda.h>
 #include <cuda_runtime.h>
 
 #include <string>
@@ -17,5 +18,11 @@ void tc5_fill_plan(const fa_fwd_params& a, fa_fwd_plan* pl);
 int tc5_launch(const fa_fwd_params& a, const fa_fwd_plan& pl, cudaStream_t st, std::string* err);
 // Synchronises the stream, then returns and clears the device status word (0 = every wait completed).
 int tc5_read_status(cudaStream_t st);
+// 4-D TMA descriptor (d, heads, rows, outer) over a 16-bit tensor with element strides; box =
+// 64 columns x 1 head x box_rows rows x 1, 128-byte swizzle.  Returns false when the driver refuses.
+bool tma_encode_rows(CUtensorMap* m, const void* ptr, int dtype, int d, int heads, int64_t rows, int64_t outer,
+                     int64_t head_stride, int64_t row_stride, int64_t outer_stride, int box_rows);
+// Device word shared by all kernels with bounded waits (allocated on first use, one per device).
+int32_t* device_status_word();
 
 }  // namespace fa

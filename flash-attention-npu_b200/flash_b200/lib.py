@@ -14,7 +14,7 @@ LIB_PATH = os.path.join(_PKG, "libfa_b200.so")
 
 FA_OK = 0
 FA_FP16, FA_BF16, FA_FP32_OUT = 0, 1, 2
-KERNEL_AUTO, KERNEL_MMA, KERNEL_TCGEN05 = 0, 1, 2
+KERNEL_AUTO, KERNEL_MMA, KERNEL_TCGEN05, KERNEL_DECODE = 0, 1, 2, 3
 
 _p = C.c_void_p
 _i64 = C.c_int64

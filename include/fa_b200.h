@@ -52,7 +52,8 @@ enum fa_dtype { FA_FP16 = 0, FA_BF16 = 1 };
 enum fa_kernel_id {
   FA_KERNEL_AUTO = 0,
   FA_KERNEL_MMA = 1,    /* register-accumulator kernel (decode, paged, ragged shapes) */
-  FA_KERNEL_TCGEN05 = 2 /* tcgen05 / TMEM / TMA prefill kernel */
+  FA_KERNEL_TCGEN05 = 2, /* tcgen05 / TMEM / TMA prefill kernel */
+  FA_KERNEL_DECODE = 3   /* producer / consumer split-KV decode kernel (bulk-copy streaming) */
 };
 
 typedef struct fa_fwd_params {
