@@ -131,7 +131,7 @@ static int make_plan(const fa_fwd_params& a, Planned* out) {
     if (a.kernel == FA_KERNEL_DECODE && !eligible)
       return fail(FA_ERR_UNSUPPORTED, "the decode kernel does not cover this problem");
     if (eligible && (a.kernel == FA_KERNEL_DECODE || a.kernel == FA_KERNEL_AUTO)) {
-      int dcfg = rows_max <= 16 ? 0 : 4;
+      int dcfg = rows_max <= 16 ? 3 : 5;  // measured best: two resident CTAs of 1x4 consumer warps / one CTA of 2x4
       if (const char* e = std::getenv("FA_B200_DECODE_CONFIG")) {  // tuning override: decode tile configuration
         const int forced = std::atoi(e);
         DecodeConfigInfo t;
@@ -163,11 +163,33 @@ static int make_plan(const fa_fwd_params& a, Planned* out) {
   int ns = 1;
   if (a.num_splits >= 1) {
     ns = std::min(a.num_splits, max_blocks);
+  } else if (kernel_id == FA_KERNEL_DECODE) {
+    const bool window_bound = is_local && wl >= 0 && range < max_k_bound;
+    if (a.seqused_k && a.kv_total == 0 && !window_bound) {
+      // Ragged lengths (only their upper bound is known here): CTAs of about 3 K keys keep the tail
+      // short without paying the per-CTA fixed cost too often (measured on lengths U[1024, 8191]).
+      ns = std::max(1, std::min(max_blocks / 2, ceil_div(max_blocks * ci.block_n, 3072)));
+    } else {
+      // Uniform ranges: a CTA costs its KV blocks plus a fixed part worth about 512 keys (launch,
+      // first TMA latency, epilogue); CTAs run in waves of num_sm * resident CTAs.
+      const long long resident = std::max(1, (227 * 1024) / std::max(1, ci.smem_bytes));
+      const long long slots = (long long)num_sm * resident;
+      const double fixed = 512.0 / ci.block_n;
+      double best = 1e30;
+      for (int cand = 1; cand <= std::max(1, max_blocks / 2); ++cand) {
+        const long long waves = (base * cand + slots - 1) / slots;
+        const double cost = (double)waves * (ceil_div(max_blocks, cand) + fixed);
+        if (cost < best * 0.97) { best = cost; ns = cand; }  // prefer fewer splits unless clearly better
+      }
+    }
   } else if (base < 8LL * num_sm && max_blocks >= 16) {
     long long per_sm = 16;
     if (const char* e = std::getenv("FA_B200_CTAS_PER_SM")) per_sm = std::max(1, std::atoi(e));  // tuning override
     long long want = (per_sm * num_sm + base - 1) / base;
     ns = (int)std::max(1LL, std::min<long long>(want, max_blocks / 8));
+  }
+  if (const char* e = std::getenv("FA_B200_NUM_SPLITS")) {  // tuning override of the split heuristic
+    if (a.num_splits == 0) ns = std::max(1, std::min(std::atoi(e), max_blocks));
   }
   int bps = ceil_div(max_blocks, ns);
   ns = ceil_div(max_blocks, bps);

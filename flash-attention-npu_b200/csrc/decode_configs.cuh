@@ -1,5 +1,5 @@
 // Tile configurations of the producer / consumer decode kernel (head dim padded to 128).
-//   X(index, MT, NCW, BN, STAGES)      MT = 1: <= 16 packed rows, MT = 2: <= 32 packed rows
+//   X(index, MT, WM, WN, BN, STAGES)   rows per CTA = 16 * MT * WM, consumer warps = WM * WN
 #pragma once
 
 #include <cuda.h>
@@ -7,8 +7,9 @@
 #include "fwd_decode.cuh"
 
 #define FA_DECODE_CONFIGS_128(X) \
-  X(0, 1, 4, 64, 5) X(1, 1, 8, 128, 3) X(2, 1, 4, 64, 2) X(3, 1, 4, 64, 3) \
-  X(4, 2, 4, 64, 5) X(5, 2, 8, 128, 3) X(6, 2, 4, 64, 3) X(7, 1, 8, 128, 2) X(8, 2, 8, 128, 2)
+  X(0, 1, 1, 4, 64, 5) X(1, 1, 1, 8, 128, 3) X(2, 1, 1, 4, 64, 2) X(3, 1, 1, 4, 64, 3) \
+  X(4, 2, 1, 4, 64, 3) X(5, 1, 2, 4, 128, 3) X(6, 1, 2, 4, 128, 2) X(7, 1, 2, 2, 64, 3) X(8, 2, 1, 8, 128, 2) \
+  X(9, 1, 2, 4, 64, 4) X(10, 1, 2, 4, 64, 3)
 
 namespace fa {
 
@@ -18,9 +19,9 @@ struct DecodeConfigInfo {
 
 inline bool decode_config_info(int hd, int cfg, DecodeConfigInfo* out) {
   if (hd != 128) return false;
-#define FA_X(I_, MT_, NCW_, BN_, ST_)                                                 \
+#define FA_X(I_, MT_, WM_, WN_, BN_, ST_)                                                 \
   if (cfg == I_) {                                                                    \
-    using Tr = DecTraits<128, __nv_bfloat16, MT_, NCW_, BN_, ST_>;                    \
+    using Tr = DecTraits<128, __nv_bfloat16, MT_, WM_, WN_, BN_, ST_>;                    \
     *out = DecodeConfigInfo{Tr::BM, Tr::BN, Tr::NTHREADS, Tr::SMEM_BYTES};            \
     return true;                                                                      \
   }

@@ -19,14 +19,16 @@
 
 namespace fa {
 
-template <int HD_, typename T_, int MT_, int NCW_, int BN_, int ST_>
+// Consumer warps form a WM x WN grid: WM splits the packed query rows (16 * MT rows per warp), WN
+// splits the keys of a stage.
+template <int HD_, typename T_, int MT_, int WM_, int WN_, int BN_, int ST_>
 struct DecTraits {
   using T = T_;
-  static constexpr int HD = HD_, MT = MT_, NCW = NCW_, BN = BN_, ST = ST_;
+  static constexpr int HD = HD_, MT = MT_, WM = WM_, WN = WN_, NCW = WM_ * WN_, BN = BN_, ST = ST_;
   static_assert(HD == 128, "K / V tiles arrive as two 64-column TMA boxes");
-  static constexpr int BM = 16 * MT;
+  static constexpr int BM = 16 * MT * WM;
   static constexpr int NTHREADS = 32 * (NCW + 1);
-  static constexpr int NW = BN / NCW;
+  static constexpr int NW = BN / WN;
   static constexpr int NT = NW / 8;
   static constexpr int KS = HD / 16;
   static constexpr int DT = HD / 8;
@@ -37,10 +39,10 @@ struct DecTraits {
   static constexpr int STAGE_BYTES = 2 * KV_BYTES;
   static constexpr int PIPE_BYTES = ST * STAGE_BYTES;
   static constexpr int SLAB_LD = HD + 4;
-  static constexpr int SLAB_BYTES = NCW * BM * SLAB_LD * 4;
+  static constexpr int SLAB_BYTES = WN * BM * SLAB_LD * 4;
   static constexpr int MAIN_BYTES = PIPE_BYTES > SLAB_BYTES ? PIPE_BYTES : SLAB_BYTES;
   static constexpr int Q_BYTES = BM * PITCH;
-  static constexpr int ML_BYTES = NCW * BM * 8;
+  static constexpr int ML_BYTES = WN * BM * 8;
   static constexpr int BAR_BYTES = 128 + 2 * ST * 8;
   // [pipeline | Q | (m, l) | barriers], the pipeline at a 1024-byte aligned base
   static constexpr int SMEM_BYTES = 1024 + MAIN_BYTES + Q_BYTES + ML_BYTES + BAR_BYTES;

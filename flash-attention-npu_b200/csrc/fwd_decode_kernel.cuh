@@ -11,14 +11,14 @@ fwd_decode_kernel(const __grid_constant__ KParams p, const __grid_constant__ CUt
                   const __grid_constant__ CUtensorMap tm_v) {
   using T = typename Tr::T;
   constexpr int MT = Tr::MT, NT = Tr::NT, DT = Tr::DT, KS = Tr::KS, BN = Tr::BN, BM = Tr::BM, ST = Tr::ST;
-  constexpr int NCW = Tr::NCW, PITCH = Tr::PITCH;
+  constexpr int NCW = Tr::NCW, WN = Tr::WN, PITCH = Tr::PITCH;
   extern __shared__ __align__(128) uint8_t smem[];
-  __shared__ int s_red[32];
   __shared__ float s_lse[Tr::BM];
   __shared__ int s_abort;
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int g8 = lane >> 2, t4 = lane & 3;
+  const int wm = (warp < Tr::NCW) ? warp / Tr::WN : 0;  // row group of a consumer warp
 
   // ---- which tile (same enumeration as fwd_mma_kernel; m_blocks == 1 here) ----
   int idx = blockIdx.x;
@@ -66,15 +66,11 @@ fwd_decode_kernel(const __grid_constant__ KParams p, const __grid_constant__ CUt
 
   int wl = p.wl;
   const int wr = p.wr;
-  if (p.wl_on_device) {
+  if (p.wl_on_device) {  // every warp reduces the batch maximum of the key lengths by itself (no block barrier)
     int mx = 0;
-    for (int i = tid; i < p.a.b; i += Tr::NTHREADS) mx = max(mx, p.a.seqused_k[i] + p.a.seqlen_new);
+    for (int i = lane; i < p.a.b; i += 32) mx = max(mx, p.a.seqused_k[i] + p.a.seqlen_new);
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) mx = max(mx, __shfl_xor_sync(0xffffffffu, mx, o));
-    if (lane == 0) s_red[warp] = mx;
-    __syncthreads();
-    mx = 0;
-    for (int w = 0; w < Tr::NTHREADS / 32; ++w) mx = max(mx, s_red[w]);
     if (mx > 0 && wl >= mx - 1) wl = -1;
   }
   const bool is_causal = wl < 0 && wr == 0;
@@ -108,10 +104,12 @@ fwd_decode_kernel(const __grid_constant__ KParams p, const __grid_constant__ CUt
     s_abort = 0;
     tc5::fence_barrier_init();
   }
-  // ---- Q tile -> shared memory (rotated when rotary tables are given); padded rows, no swizzle ----
-  {
+  __syncthreads();  // barriers initialised; from here the producer warp runs ahead of the consumers
+  // ---- Q tile -> shared memory by the consumer warps (rotated when rotary tables are given);
+  //      padded rows, no swizzle.  The producer is already fetching the first K / V stages. ----
+  if (warp < NCW) {
     const bool rot_per_token = is_causal || is_local;
-    for (int c = tid; c < BM * Tr::CHUNKS; c += Tr::NTHREADS) {
+    for (int c = tid; c < BM * Tr::CHUNKS; c += NCW * 32) {
       const int row = c / Tr::CHUNKS, ch = c % Tr::CHUNKS;
       uint4 q4 = make_uint4(0, 0, 0, 0);
       if (row < rows_total && ch * 8 < p.a.d) {
@@ -127,8 +125,8 @@ fwd_decode_kernel(const __grid_constant__ KParams p, const __grid_constant__ CUt
       }
       asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};\n" ::"r"(q_base + row * PITCH + ch * 16), "r"(q4.x), "r"(q4.y), "r"(q4.z), "r"(q4.w));
     }
+    asm volatile("bar.sync 1, %0;\n" ::"n"(NCW * 32));  // consumer warps only
   }
-  __syncthreads();
 
   float o_acc[MT][DT][4];
   float m_run[MT][2], l_run[MT][2];
@@ -146,7 +144,7 @@ fwd_decode_kernel(const __grid_constant__ KParams p, const __grid_constant__ CUt
     if (lane == 0) { tc5::tma_prefetch_desc(&tm_k); tc5::tma_prefetch_desc(&tm_v); }
     decode_producer<Tr>(p, sv, &tm_k, &tm_v, pipe_base, full0, empty0, my_lo, n_blocks, hk, batch_row, &s_abort);
   } else {
-    const int wn = warp;
+    const int wn = warp % WN;
     // per-thread row bounds (thread owns rows g8 and g8 + 8 of each m-tile)
     int row_lo[MT][2], row_hi[MT][2], row_i[MT][2];
     float slope_l2[MT][2];
@@ -154,7 +152,7 @@ fwd_decode_kernel(const __grid_constant__ KParams p, const __grid_constant__ CUt
     for (int mt = 0; mt < MT; ++mt)
 #pragma unroll
       for (int hf = 0; hf < 2; ++hf) {
-        const int r = mt * 16 + g8 + 8 * hf;
+        const int r = (wm * MT + mt) * 16 + g8 + 8 * hf;
         const int i = r / p.gp;
         row_i[mt][hf] = i;
         int lo = 0, hi = sv.k_len - 1;
@@ -182,7 +180,7 @@ fwd_decode_kernel(const __grid_constant__ KParams p, const __grid_constant__ CUt
 #pragma unroll
         for (int ks = 0; ks < KS; ++ks) {
           const int m = lane >> 3, r = lane & 7;
-          const int row = mt * 16 + (m & 1) * 8 + r;
+          const int row = (wm * MT + mt) * 16 + (m & 1) * 8 + r;
           ldmatrix_x4(qf[mt][ks][0], qf[mt][ks][1], qf[mt][ks][2], qf[mt][ks][3],
                       q_base + row * PITCH + (ks * 2 + (m >> 1)) * 16);
         }
@@ -213,7 +211,7 @@ fwd_decode_kernel(const __grid_constant__ KParams p, const __grid_constant__ CUt
             for (int e = 0; e < 4; ++e) a[mt][e] = qf[mt][ks][e];
           } else {
             const int m = lane >> 3, r = lane & 7;
-            const int row = mt * 16 + (m & 1) * 8 + r;
+            const int row = (wm * MT + mt) * 16 + (m & 1) * 8 + r;
             ldmatrix_x4(a[mt][0], a[mt][1], a[mt][2], a[mt][3], q_base + row * PITCH + (ks * 2 + (m >> 1)) * 16);
           }
         }
@@ -239,23 +237,34 @@ fwd_decode_kernel(const __grid_constant__ KParams p, const __grid_constant__ CUt
 #pragma unroll
         for (int hf = 0; hf < 2; ++hf) {
           float mx = -INFINITY;
+          if (!need_mask && !has_softcap) {  // interior block: scale only
 #pragma unroll
-          for (int nt = 0; nt < NT; ++nt)
+            for (int nt = 0; nt < NT; ++nt)
 #pragma unroll
-            for (int e = 0; e < 2; ++e) {
-              float x = s_acc[mt][nt][hf * 2 + e] * sc_mul;
-              if (has_softcap) {
-                const float ex = __expf(2.f * x);
-                x = cap_l2 * (1.f - __fdividef(2.f, ex + 1.f));
+              for (int e = 0; e < 2; ++e) {
+                const float x = s_acc[mt][nt][hf * 2 + e] * sc_mul;
+                s_acc[mt][nt][hf * 2 + e] = x;
+                mx = fmaxf(mx, x);
               }
-              if (need_mask) {
-                const int j = col0 + nt * 8 + 2 * t4 + e;
-                if (has_alibi) x -= slope_l2[mt][hf] * fabsf((float)(row_i[mt][hf] + koff - j));
-                if (j < row_lo[mt][hf] || j > row_hi[mt][hf]) x = -INFINITY;
+          } else {
+#pragma unroll
+            for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+              for (int e = 0; e < 2; ++e) {
+                float x = s_acc[mt][nt][hf * 2 + e] * sc_mul;
+                if (has_softcap) {
+                  const float ex = __expf(2.f * x);
+                  x = cap_l2 * (1.f - __fdividef(2.f, ex + 1.f));
+                }
+                if (need_mask) {
+                  const int j = col0 + nt * 8 + 2 * t4 + e;
+                  if (has_alibi) x -= slope_l2[mt][hf] * fabsf((float)(row_i[mt][hf] + koff - j));
+                  if (j < row_lo[mt][hf] || j > row_hi[mt][hf]) x = -INFINITY;
+                }
+                s_acc[mt][nt][hf * 2 + e] = x;
+                mx = fmaxf(mx, x);
               }
-              s_acc[mt][nt][hf * 2 + e] = x;
-              mx = fmaxf(mx, x);
-            }
+          }
           mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
           mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
           const float m_new = fmaxf(m_run[mt][hf], mx);
@@ -328,7 +337,7 @@ fwd_decode_kernel(const __grid_constant__ KParams p, const __grid_constant__ CUt
         l += __shfl_xor_sync(0xffffffffu, l, 1);
         l += __shfl_xor_sync(0xffffffffu, l, 2);
         l_run[mt][hf] = l;
-        if (t4 == 0) ml[warp * BM + mt * 16 + g8 + 8 * hf] = make_float2(m_run[mt][hf], l);
+        if (t4 == 0) ml[(warp % WN) * BM + (wm * MT + mt) * 16 + g8 + 8 * hf] = make_float2(m_run[mt][hf], l);
       }
   }
   __syncthreads();
@@ -337,19 +346,19 @@ fwd_decode_kernel(const __grid_constant__ KParams p, const __grid_constant__ CUt
     for (int mt = 0; mt < MT; ++mt)
 #pragma unroll
       for (int hf = 0; hf < 2; ++hf) {
-        const int trow = mt * 16 + g8 + 8 * hf;
+        const int trow = (wm * MT + mt) * 16 + g8 + 8 * hf;
         float m_all = -INFINITY;
 #pragma unroll
-        for (int w = 0; w < NCW; ++w) m_all = fmaxf(m_all, ml[w * BM + trow].x);
+        for (int w = 0; w < WN; ++w) m_all = fmaxf(m_all, ml[w * BM + trow].x);
         const float m_use = (m_all == -INFINITY) ? 0.f : m_all;
         float l_all = 0.f;
 #pragma unroll
-        for (int w = 0; w < NCW; ++w) {
+        for (int w = 0; w < WN; ++w) {
           const float2 x = ml[w * BM + trow];
           l_all += x.y * fast_exp2(x.x - m_use);
         }
         const float f = (l_all > 0.f) ? fast_exp2(m_run[mt][hf] - m_use) / l_all : 0.f;
-        float* dst = slab + (size_t)(warp * BM + trow) * Tr::SLAB_LD;
+        float* dst = slab + (size_t)((warp % WN) * BM + trow) * Tr::SLAB_LD;
 #pragma unroll
         for (int dt = 0; dt < DT; ++dt)
           *reinterpret_cast<float2*>(dst + dt * 8 + 2 * t4) = make_float2(o_acc[mt][dt][hf * 2] * f, o_acc[mt][dt][hf * 2 + 1] * f);
@@ -357,9 +366,9 @@ fwd_decode_kernel(const __grid_constant__ KParams p, const __grid_constant__ CUt
   }
   for (int trow = tid; trow < BM; trow += Tr::NTHREADS) {
     float m_all = -INFINITY, l_all = 0.f;
-    for (int w = 0; w < NCW; ++w) m_all = fmaxf(m_all, ml[w * BM + trow].x);
+    for (int w = 0; w < WN; ++w) m_all = fmaxf(m_all, ml[w * BM + trow].x);
     const float m_use = (m_all == -INFINITY) ? 0.f : m_all;
-    for (int w = 0; w < NCW; ++w) {
+    for (int w = 0; w < WN; ++w) {
       const float2 x = ml[w * BM + trow];
       l_all += x.y * fast_exp2(x.x - m_use);
     }
@@ -383,7 +392,7 @@ fwd_decode_kernel(const __grid_constant__ KParams p, const __grid_constant__ CUt
     if (c4 >= p.a.d || (dead && to_partial)) continue;
     float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
-    for (int w = 0; w < NCW; ++w) {
+    for (int w = 0; w < WN; ++w) {
       const float4 x = *reinterpret_cast<const float4*>(slab + (size_t)(w * BM + trow) * Tr::SLAB_LD + c4);
       acc.x += x.x; acc.y += x.y; acc.z += x.z; acc.w += x.w;
     }
