@@ -405,11 +405,16 @@ def main():
     barrier()
     total_ms = ev[0].elapsed_time(ev[-1])
     per = sorted(ev[i].elapsed_time(ev[i + 1]) for i in range(args.steps))
-    # keep the GPU busy a little longer so the clock sampler sees load even for short runs
-    t_end = time.time() + (0.6 if args.steps > 2 else 0.0)
-    while rank == 0 and time.time() < t_end:
+    # Keep the GPU busy a little longer so the clock sampler sees load even for short runs.  The
+    # number of extra steps is derived from the rank-reduced time, so every rank runs the same count
+    # (a workload with a collective would deadlock otherwise).
+    t0 = torch.tensor([total_ms], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(t0, op=dist.ReduceOp.MAX)
+    n_extra = int(min(2000, 600.0 / max(float(t0[0]) / args.steps, 1e-3))) if args.steps > 2 else 0
+    for _ in range(n_extra):
         wl.step()
-    torch.cuda.synchronize()
+    barrier()
     clocks = sampler.stop() if rank == 0 else None
 
     # ---- end-to-end timing (host buffers) ----

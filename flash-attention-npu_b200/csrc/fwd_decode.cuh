@@ -90,7 +90,7 @@ __device__ __forceinline__ void decode_fix_rows(const KParams& p, const SeqView<
 }
 
 // Producer: one elected lane issues four tiled TMA loads per stage (K and V, two 64-column halves
-// each).  Tensor maps are 4-D (d, kv head, row, batch-or-page); never multicast.
+// each).  Tensor maps are 4-D (d, kv head, row, batch-or-page); every load targets the issuing CTA only.
 template <class Tr>
 __device__ __forceinline__ void decode_producer(const KParams& p, const SeqView<typename Tr::T>& sv,
                                                 const CUtensorMap* tm_k, const CUtensorMap* tm_v, uint32_t pipe_base,

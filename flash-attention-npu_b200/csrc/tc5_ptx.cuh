@@ -1,5 +1,5 @@
 // Inline-PTX wrappers for the Blackwell (sm_100a) features the prefill kernel uses:
-// mbarrier, TMA tiled loads (never multicast), tcgen05 MMA / commit / ld / st, TMEM allocation.
+// mbarrier, TMA tiled loads (each into the issuing CTA only), tcgen05 MMA / commit / ld / st, TMEM allocation.
 // Every wait is bounded: after kSpinLimit polls it raises the CTA's abort flag and returns false,
 // so a protocol bug ends in an error status instead of a hung GPU.
 #pragma once
@@ -62,7 +62,7 @@ __device__ __forceinline__ void fence_proxy_async() {
   asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
 }
 
-// ---------------- TMA (tiled, 4-D, no multicast) ----------------
+// ---------------- TMA (tiled, 4-D, CTA-local destination) ----------------
 __device__ __forceinline__ void tma_prefetch_desc(const CUtensorMap* m) {
   asm volatile("prefetch.tensormap [%0];\n" ::"l"(reinterpret_cast<uint64_t>(m)) : "memory");
 }
