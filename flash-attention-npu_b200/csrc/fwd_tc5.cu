@@ -29,7 +29,11 @@ fwd_tc5_kernel(const __grid_constant__ Tc5Params p, const __grid_constant__ CUte
   const uint32_t kv_smem = base + 2 * kTileBytes;
   Barriers* bar = reinterpret_cast<Barriers*>(smem + 2 * kTileBytes + kSlots * kTileBytes);
 
-  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  // The warp index and the TMEM base are broadcast from lane 0 so that the compiler knows they are
+  // warp-uniform: everything the MMA / TMA roles derive from them (barrier addresses, descriptors,
+  // TMEM addresses) can then live on the uniform datapath, which is what tcgen05.mma reads.
+  const int tid = threadIdx.x, lane = tid & 31;
+  const int warp = __shfl_sync(0xffffffffu, tid >> 5, 0);
   if (tid == 0) {
     for (int t = 0; t < 2; ++t) {
       mbar_init(smem_addr(&bar->q_full[t]), 1);
@@ -63,7 +67,7 @@ fwd_tc5_kernel(const __grid_constant__ Tc5Params p, const __grid_constant__ CUte
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
-  const uint32_t tmem = bar->tmem_base;
+  const uint32_t tmem = __shfl_sync(0xffffffffu, bar->tmem_base, 0);
 
   // Register budget: 512 threads start with 128 registers each; the softmax warps need the 128
   // scores of a row plus working set, the other roles need far fewer.
