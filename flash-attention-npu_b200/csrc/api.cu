@@ -428,7 +428,13 @@ int fa_b200_check_status(void* stream) {
   const int v = fa::tc5_read_status(reinterpret_cast<cudaStream_t>(stream));
   if (v == 0) return FA_OK;
   if (v < 0) return fa::fail(FA_ERR_CUDA, "cannot read the device status word");
-  return fa::fail(FA_ERR_CUDA, "a bounded device-side wait gave up in CTA " + std::to_string(v - 1) +
+  if (v & 0x40000000)
+    return fa::fail(FA_ERR_CUDA, "a bounded device-side wait gave up in CTA " + std::to_string(v & 0xffffff) +
+                                     " of the decode kernel (results of that launch are invalid)");
+  if (v & 0x20000000)
+    return fa::fail(FA_ERR_CUDA, "the tcgen05 kernel found its shared memory base not 1024-byte aligned (nothing was computed)");
+  return fa::fail(FA_ERR_CUDA, "bounded device-side wait " + std::to_string((v >> 16) & 0xff) + " gave up in CTA " +
+                                   std::to_string((v & 0xffff) - 1) +
                                    " of the tcgen05 kernel (results of that launch are invalid)");
 }
 

@@ -20,14 +20,18 @@ template <typename T, uint32_t AB_FMT, int POLY>
 __global__ void __launch_bounds__(kThreads, 1)
 fwd_tc5_kernel(const __grid_constant__ Tc5Params p, const __grid_constant__ CUtensorMap tm_q,
                const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v) {
-  extern __shared__ uint8_t smem_raw[];
-  // 128-byte-swizzled tiles need 1024-byte aligned bases
-  const uint32_t raw = smem_addr(smem_raw);
-  const uint32_t base = (raw + 1023u) & ~1023u;
-  uint8_t* smem = smem_raw + (base - raw);
+  // 128-byte-swizzled tiles need 1024-byte aligned bases; the whole 227 KiB are in use, so the base
+  // itself must be aligned (checked below) instead of being rounded up.
+  extern __shared__ __align__(1024) uint8_t smem[];
+  const uint32_t base = smem_addr(smem);
+  if ((base & 1023u) != 0) {
+    if (threadIdx.x == 0) atomicExch(p.status, 0x20000000);
+    return;
+  }
   const uint32_t q_smem = base;
-  const uint32_t kv_smem = base + 2 * kTileBytes;
-  Barriers* bar = reinterpret_cast<Barriers*>(smem + 2 * kTileBytes + kSlots * kTileBytes);
+  const uint32_t p_smem = base + 2 * kTileBytes;
+  const uint32_t kv_smem = base + 4 * kTileBytes;
+  Barriers* bar = reinterpret_cast<Barriers*>(smem + 4 * kTileBytes + kSlots * kTileBytes);
 
   // The warp index and the TMEM base are broadcast from lane 0 so that the compiler knows they are
   // warp-uniform: everything the MMA / TMA roles derive from them (barrier addresses, descriptors,
@@ -39,6 +43,7 @@ fwd_tc5_kernel(const __grid_constant__ Tc5Params p, const __grid_constant__ CUte
       mbar_init(smem_addr(&bar->q_full[t]), 1);
       mbar_init(smem_addr(&bar->q_empty[t]), 1);
       mbar_init(smem_addr(&bar->s_full[t]), 1);
+      mbar_init(smem_addr(&bar->s_free[t]), 4);
       mbar_init(smem_addr(&bar->p_full[t][0]), 4);
       mbar_init(smem_addr(&bar->p_full[t][1]), 4);
       mbar_init(smem_addr(&bar->corr_ready[t]), 4);
@@ -46,7 +51,6 @@ fwd_tc5_kernel(const __grid_constant__ Tc5Params p, const __grid_constant__ CUte
       mbar_init(smem_addr(&bar->o_done[t]), 1);
       mbar_init(smem_addr(&bar->stats_ready[t]), 4);
       mbar_init(smem_addr(&bar->o_free[t]), 4);
-      mbar_init(smem_addr(&bar->mma_turn[t]), 1);
     }
     for (int s = 0; s < kSlots; ++s) {
       mbar_init(smem_addr(&bar->kv_full[s]), 1);
@@ -72,18 +76,16 @@ fwd_tc5_kernel(const __grid_constant__ Tc5Params p, const __grid_constant__ CUte
   // Register budget: 512 threads start with 128 registers each; the softmax warps need the 128
   // scores of a row plus working set, the other roles need far fewer.
   if (warp < 8) {
-    asm volatile("setmaxnreg.inc.sync.aligned.u32 176;\n");
-    softmax_loop<T, POLY>(p, bar, tmem, warp >> 2, warp & 3, lane);
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;\n" ::"n"(kRegsSoftmax));
+    softmax_loop<T, POLY>(p, bar, tmem, p_smem, warp >> 2, warp & 3, lane);
   } else if (warp < 12) {
-    asm volatile("setmaxnreg.dec.sync.aligned.u32 96;\n");
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;\n" ::"n"(kRegsCorr));
     correction_loop<T>(p, bar, tmem, warp & 3, lane);
   } else {
-    asm volatile("setmaxnreg.dec.sync.aligned.u32 64;\n");
-  }
-  if (warp == kMmaWarp || warp == kMmaWarp + 1) {
-    mma_loop<AB_FMT>(p, bar, q_smem, kv_smem, tmem, warp - kMmaWarp);  // warp-uniform; one elected lane issues
-  } else if (warp == kTmaWarp) {
-    producer_loop(p, &tm_q, &tm_k, &tm_v, bar, q_smem, kv_smem);  // warp-uniform; one elected lane issues
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;\n" ::"n"(kRegsMma));
+    // warp-uniform role code; one elected lane issues
+    if (warp == kMmaWarp || warp == kMmaWarp + 1) mma_loop<AB_FMT>(p, bar, q_smem, p_smem, kv_smem, tmem, warp - kMmaWarp);
+    else if (warp == kTmaWarp) producer_loop(p, &tm_q, &tm_k, &tm_v, bar, q_smem, kv_smem);
   }
 
   tc_fence_before();
@@ -92,7 +94,7 @@ fwd_tc5_kernel(const __grid_constant__ Tc5Params p, const __grid_constant__ CUte
   if (aborted) {
     // give copies that may still be in flight time to land before the shared memory is released
     for (int i = 0; i < 64; ++i) __nanosleep(2000);
-    if (tid == 0) atomicExch(p.status, 1 + blockIdx.x);
+    if (tid == 0) atomicExch(p.status, (aborted << 16) | (1 + blockIdx.x));
     __syncthreads();
   }
   if (warp == kMmaWarp) {
@@ -210,7 +212,6 @@ int tc5_launch(const fa_fwd_params& a, const fa_fwd_plan& pl, cudaStream_t st, s
   p.scale_log2 = a.softmax_scale * kLog2e;
   p.rescale_threshold = 0.f;
   if (const char* e = std::getenv("FA_B200_RESCALE_THRESHOLD")) p.rescale_threshold = (float)std::atof(e);  // tuning override
-  if (const char* e = std::getenv("FA_B200_TC5_WAIT_FULL_P")) p.tune_wait_full_p = std::atoi(e);
   if (const char* e = std::getenv("FA_B200_TC5_POLY")) p.tune_poly = std::atoi(e);
   p.status = status_word();
   if (!p.status) { *err = "cannot allocate the device status word"; return FA_ERR_CUDA; }

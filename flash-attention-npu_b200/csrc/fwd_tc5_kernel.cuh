@@ -5,18 +5,21 @@
 // It replaces, for dense / varlen prefill, the cube+vector pipeline of the reference kernel
 // (csrc/arch22/flash_attn_npu_v2/mha_fwd_kvcache.cpp:632-965: QK -> online softmax -> PV ->
 // rescale O, with S / P / O_tmp round-tripping through a global workspace).  Here S, P and O never
-// leave the SM: S and O live in TMEM, P overwrites S in TMEM as 16-bit pairs and feeds the second
-// MMA directly.
+// leave the SM: S and O live in TMEM, P goes through shared memory (16-bit, the layout of an MMA
+// A operand) into the second MMA.
 //
 // CTA = 16 warps:  warps 0-3    softmax of query sub-tile 0 (128 rows, one thread per row)
 //                  warps 4-7    softmax of query sub-tile 1
 //                  warps 8-11   correction (rescale of O in TMEM when a row maximum moved) and
-//                               epilogue (O / l -> global, LSE) for both sub-tiles
+//                               epilogue (O / l -> global) for both sub-tiles
 //                  warps 12-13  MMA issuers, one per sub-tile (one elected lane each)
 //                  warp  14     TMA producer (one elected lane)      warp 15 idle
-// TMEM (512 columns): S0 [0,128)  S1 [128,256)  O0 [256,384)  O1 [384,512); P_t aliases S_t.
-// The two sub-tiles ping-pong: while the softmax warps of one work on S, the tensor core runs
-// P.V of the other and the next Q.K^T.
+// TMEM (512 columns): S0 [0,128)  S1 [128,256)  O0 [256,384)  O1 [384,512).
+// Shared memory: Q0 Q1 | P0 P1 | ring of K / V tiles (32 KiB each).
+// Dependency chain per sub-tile: a softmax thread copies its row of S into registers and frees the
+// S columns at once, so Q.K^T of the next KV block runs while this block's exponentials are
+// computed; P.V follows when P is in shared memory.  The softmax warps therefore never wait for the
+// tensor pipe in steady state, and the tensor pipe has two sub-tiles' worth of independent work.
 #pragma once
 
 #include "common.cuh"
@@ -28,12 +31,26 @@ namespace tc5 {
 constexpr int kBlockM = 128;          // rows of one query sub-tile
 constexpr int kTileM = 2 * kBlockM;   // rows of one CTA tile
 constexpr int kBlockN = 128;          // keys per KV block
-constexpr int kSlots = 4;             // ring of 32 KiB K / V buffers
+constexpr int kSlots = 3;             // ring of 32 KiB K / V buffers
 constexpr int kThreads = 512;
 constexpr int kMmaWarp = 12 /* and 13: one per sub-tile */, kTmaWarp = 14;
+// Registers per thread after the roles have re-balanced them (setmaxnreg, one value per warpgroup).
+// A CTA can only re-distribute the registers it was launched with (512 threads x 128), never more:
+// a setmaxnreg.inc that the other warpgroups' releases cannot cover would block for ever.
+#ifndef FA_TC5_REGS_SOFTMAX
+#define FA_TC5_REGS_SOFTMAX 192
+#define FA_TC5_REGS_CORR 88
+#define FA_TC5_REGS_MMA 40
+#endif
+constexpr int kRegsSoftmax = FA_TC5_REGS_SOFTMAX, kRegsCorr = FA_TC5_REGS_CORR, kRegsMma = FA_TC5_REGS_MMA;
+static_assert(256 * kRegsSoftmax + 128 * (kRegsCorr + kRegsMma) <= kThreads * 128, "more registers than the CTA was launched with");
 constexpr int kHalfBytes = kBlockN * 128;   // one 64-column half of a [128 x 128] 16-bit tile (128-byte rows)
 constexpr int kTileBytes = 2 * kHalfBytes;  // 32 KiB
-constexpr int kSmemBytes = 2 * kTileBytes + kSlots * kTileBytes + 1024 /*alignment*/ + 4096 /*barriers, row statistics*/;
+constexpr int kBarBytes = 3072;  // barriers, per-row rescale factors and 1 / l
+// Q0 Q1 | P0 P1 | ring | barriers.  The dynamic shared memory base must be 1024-byte aligned (the
+// kernel checks it): there is no room left for a round-up.
+constexpr int kSmemBytes = 4 * kTileBytes + kSlots * kTileBytes + kBarBytes;
+static_assert(kSmemBytes <= 232448, "more than the 227 KiB a CTA can have");
 
 struct Tc5Params {
   fa_fwd_params a;
@@ -46,7 +63,7 @@ struct Tc5Params {
   // 0 = always (P <= 1 and the row maximum has P = 1 exactly, like the golden); > 0 trades a few
   // ulps of P rounding on sharply peaked rows for fewer O rescales.
   float rescale_threshold;
-  int32_t tune_wait_full_p;  // experiment: the MMA warp waits for all of P before taking its turn
+  int32_t tune_reserved;
   int32_t tune_poly;         // experiment: exponentials evaluated by polynomial out of every 4 pairs
   int32_t* status;  // device word: 0 ok, otherwise the wait that gave up
 #ifdef FA_TC5_TRACE
@@ -56,7 +73,7 @@ struct Tc5Params {
 
 #ifdef FA_TC5_TRACE
 constexpr int kTraceLen = 2048;
-constexpr int kTraceSlots = 5;
+constexpr int kTraceSlots = 8;
 struct Tracer {
   long long* buf;
   int n;
@@ -129,23 +146,43 @@ __device__ __forceinline__ void tile_info(const Tc5Params& p, int n, TileInfo& t
   if (ti.uhi == 0) ti.ulo = 0;
 }
 
+// Static tile schedule.  tile_info orders tiles heaviest first; CTA c of G takes tiles
+// c, 2G-1-c, 2G+c, 4G-1-c, ... (serpentine), which evens out the per-CTA sums of a decreasing
+// sequence (causal, 4K: 1 % spread instead of 6 % with a plain stride).
+struct TileSched {
+  int round, total;
+  __device__ explicit TileSched(const Tc5Params& p) : round(0), total(p.total_tiles) {}
+  __device__ __forceinline__ int cur() const {
+    const int g = (int)gridDim.x, c = (int)blockIdx.x;
+    if (round * g >= total) return total;
+    const int n = round * g + ((round & 1) ? g - 1 - c : c);
+    return n < total ? n : total;
+  }
+  __device__ __forceinline__ int first() { return cur(); }
+  __device__ __forceinline__ int next() {
+    ++round;
+    return cur();
+  }
+};
+
 struct Barriers {
   uint64_t q_full[2], q_empty[2], kv_full[kSlots], kv_empty[kSlots];
   uint64_t s_full[2];      // MMA -> softmax: S_t = Q_t K_j^T is in TMEM
-  // softmax -> MMA: half h (64 keys) of P_t is in TMEM.  One barrier per half: a waiter must never
-  // fall two phases behind a barrier, which two arrivals per block on one barrier would allow.
+  uint64_t s_free[2];      // softmax -> MMA: every row of S_t has been copied into registers
+  // softmax -> MMA: half h (64 keys) of P_t is in shared memory.  One barrier per half: a waiter must
+  // never fall two phases behind a barrier, which two arrivals per block on one barrier would allow.
   uint64_t p_full[2][2];
   uint64_t corr_ready[2];  // softmax -> correction: rescale factors of block j are in shared memory
   uint64_t o_ready[2];     // correction -> MMA: O_t has been rescaled, P.V of block j may accumulate
-  uint64_t o_done[2];      // MMA -> correction: P.V of a block has completed
-  uint64_t stats_ready[2]; // softmax -> correction: final (max, sum) of the tile are in shared memory
+  uint64_t o_done[2];      // MMA -> correction, softmax: P.V of a block has completed (O_t updated, P_t read)
+  uint64_t stats_ready[2]; // softmax -> correction: 1 / l of the tile's rows is in shared memory
   uint64_t o_free[2];      // correction -> MMA: the epilogue has read O_t
-  uint64_t mma_turn[2];    // MMA warp <-> MMA warp: whose turn it is to issue
   uint32_t tmem_base;
   int abort_flag;
   float corr[2][kBlockM];
-  float row_max[2][kBlockM], row_sum[2][kBlockM];
+  float row_inv[2][kBlockM];
 };
+static_assert(sizeof(Barriers) <= kBarBytes, "barrier block does not fit");
 
 }  // namespace tc5
 }  // namespace fa

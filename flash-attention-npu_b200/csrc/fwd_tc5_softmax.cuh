@@ -7,9 +7,13 @@
 // The 128 scores of a row are held in registers (the softmax warps raise their register budget
 // with setmaxnreg, the other roles lower theirs).
 //
+// P leaves the thread as 16-byte chunks of 8 keys written to shared memory in the layout the MMA
+// reads an A operand in (128-byte rows, 128-byte swizzle, two 64-key halves).  At the end of a tile
+// the thread writes LSE = m*scale + ln(l) and hands 1 / l to the correction warps.
+//
 // Correction: 128 threads serving both sub-tiles.  When a row maximum moved it multiplies O (in
 // TMEM) by exp2((m_old - m_new) * scale*log2e) between two P.V accumulations, off the softmax
-// threads' critical path, and at the end of a tile writes O / l and LSE = m*scale + ln(l)
+// threads' critical path, and at the end of a tile writes O / l
 // (RescaleO, csrc/arch22/flash_attn_npu_v2/rescale_o.hpp:299-534).
 #pragma once
 
@@ -30,12 +34,17 @@ __device__ __forceinline__ float chunk_max(const uint32_t (&a)[32], float m) {
   return fmaxf(fmaxf(m0, m1), fmaxf(m2, m3));
 }
 
+// Columns outside [lo, hi] become -inf.  The valid columns of the chunk form one bit mask, so an
+// element costs a bit test and a select (per-element range compares were several times slower).
 __device__ __forceinline__ void chunk_mask(uint32_t (&a)[32], int col_first, int lo, int hi) {
+  const int n_lo = min(max(lo - col_first, 0), 32);       // first valid element of the chunk
+  const int n_hi = min(max(hi - col_first + 1, 0), 32);   // one past the last valid element
+  const uint32_t below_hi = n_hi >= 32 ? 0xffffffffu : ((1u << n_hi) - 1u);
+  const uint32_t below_lo = n_lo >= 32 ? 0xffffffffu : ((1u << n_lo) - 1u);
+  const uint32_t valid = below_hi & ~below_lo;
 #pragma unroll
-  for (int e = 0; e < 32; ++e) {
-    const int col = col_first + e;
-    if (col < lo || col > hi) a[e] = 0xff800000u;  // -inf
-  }
+  for (int e = 0; e < 32; ++e)
+    if (!((valid >> e) & 1u)) a[e] = 0xff800000u;  // -inf
 }
 
 // exp2 of two values on the FMA / ALU pipes instead of the special-function unit, which is the
@@ -76,27 +85,50 @@ __device__ __forceinline__ void chunk_exp(const uint32_t (&a)[32], uint64_t scal
     } else {
       float x0, x1;
       unpack_f32x2(x2, x0, x1);
+#if defined(FA_TC5_EXPERIMENT) && (FA_TC5_EXPERIMENT & 1)
+      p0 = x0 * 0.001f;  // what-if build: no special-function work (results are wrong)
+      p1 = x1 * 0.001f;
+#else
       p0 = fast_exp2(x0);
       p1 = fast_exp2(x1);
+#endif
     }
     sum2[(e >> 1) & 3] = add_f32x2(sum2[(e >> 1) & 3], pack_f32x2(p0, p1));  // four independent chains
     pk[e >> 1] = pack2<T>(p0, p1);
   }
 }
 
+// 32 keys of P (16 packed pairs = four 16-byte chunks) of one row into the swizzled A-operand tile.
+__device__ __forceinline__ void store_p_chunk(uint32_t p_row, uint32_t p_xor, int c, const uint32_t (&pk)[16]) {
+#pragma unroll
+  for (int q = 0; q < 4; ++q) {
+    const uint32_t kc = (uint32_t)(c * 4 + q);
+    const uint32_t addr = p_row + (kc >> 3) * kHalfBytes + (((kc & 7) ^ p_xor) << 4);
+    asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};\n" ::"r"(addr), "r"(pk[4 * q]), "r"(pk[4 * q + 1]),
+                 "r"(pk[4 * q + 2]), "r"(pk[4 * q + 3])
+                 : "memory");
+  }
+}
+
 template <typename T, int POLY>
-__device__ __forceinline__ void softmax_loop(const Tc5Params& p, Barriers* bar, uint32_t tmem, int t, int warp_in_wg,
-                                             int lane) {
+__device__ __forceinline__ void softmax_loop(const Tc5Params& p, Barriers* bar, uint32_t tmem, uint32_t p_smem, int t,
+                                             int warp_in_wg, int lane) {
   volatile int* abort_flag = &bar->abort_flag;
   const int row = warp_in_wg * 32 + lane;
   const uint32_t lane_addr = (uint32_t)(warp_in_wg * 32) << 16;
   const uint32_t s_tmem = tmem + lane_addr + t * 128;
-  uint32_t s_cnt = 0;
+  uint32_t s_cnt = 0, cr_cnt = 0, st_cnt = 0;
+  // this row of P_t: chunk kc (8 keys) of the row lives at  half(kc) + row * 128 + ((kc ^ row) & 7) * 16
+  const uint32_t p_row = p_smem + t * kTileBytes + row * 128;
+  const uint32_t p_xor = (uint32_t)(row & 7);
+  const uint32_t bar_sfree = smem_addr(&bar->s_free[t]), bar_odone = smem_addr(&bar->o_done[t]);
+  const uint32_t bar_oready = smem_addr(&bar->o_ready[t]), bar_ofree = smem_addr(&bar->o_free[t]);
   Tracer tr(p, t, warp_in_wg == 0 && lane == 0);
   const float scale_log2 = p.scale_log2;
   const uint64_t scale2 = pack_f32x2(scale_log2, scale_log2);
 
-  for (int n = blockIdx.x; n < p.total_tiles; n += gridDim.x) {
+  TileSched sched(p);
+  for (int n = sched.first(); n < p.total_tiles; n = sched.next()) {
     TileInfo ti;
     tile_info(p, n, ti);
     if (ti.row0[t] >= ti.q_len) continue;
@@ -125,7 +157,8 @@ __device__ __forceinline__ void softmax_loop(const Tc5Params& p, Barriers* bar, 
       if (p.is_causal || p.is_local) need_mask = need_mask || (col0 + kBlockN - 1 > i_min + ti.koff + (p.is_local ? p.wr : 0));
       if (p.is_local) need_mask = need_mask || (col0 < i_max + ti.koff - p.wl);
 
-      if (!mbar_wait(smem_addr(&bar->s_full[t]), s_cnt & 1, abort_flag)) return;
+      if (!mbar_wait(smem_addr(&bar->s_full[t]), s_cnt & 1, abort_flag, 41)) return;
+      const uint32_t blk = s_cnt;  // running number of this block (all tiles of this CTA)
       ++s_cnt;
       FA_TR(tr, 1);
       tc_fence_after();
@@ -134,13 +167,24 @@ __device__ __forceinline__ void softmax_loop(const Tc5Params& p, Barriers* bar, 
 #pragma unroll
       for (int c = 0; c < 4; ++c) tmem_ld32(s_tmem + c * 32, sc[c]);
       tmem_wait_ld();
+      // the S columns are free: Q.K^T of the next block may overwrite them
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar_sfree);
+#if defined(FA_TC5_EXPERIMENT) && (FA_TC5_EXPERIMENT & 4)
+      need_mask = false;  // what-if build: no masking (results are wrong)
+#endif
       if (need_mask) {
 #pragma unroll
         for (int c = 0; c < 4; ++c) chunk_mask(sc[c], col0 + c * 32, lo, hi);
       }
+#if defined(FA_TC5_EXPERIMENT) && (FA_TC5_EXPERIMENT & 2)
+      float blk_max = __uint_as_float(sc[0][0]) + 8.f;  // what-if build: no row maximum (results are wrong)
+#else
       float blk_max = chunk_max(sc[0], -INFINITY);
 #pragma unroll
       for (int c = 1; c < 4; ++c) blk_max = chunk_max(sc[c], blk_max);
+#endif
 
       float m_new = fmaxf(m_run, blk_max);
       // optional lazy update: keep the old reference max while the true max is within the threshold
@@ -148,6 +192,10 @@ __device__ __forceinline__ void softmax_loop(const Tc5Params& p, Barriers* bar, 
       const float m_use = (m_new == -INFINITY) ? 0.f : m_new;
       const float corr = fast_exp2((m_run - m_use) * scale_log2);  // 0 when m_run = -inf
       if (j > ti.jlo[t]) {
+        // The correction warps must have consumed the previous factors: this thread can be a whole
+        // block ahead of them, and neither the factor array nor the barrier phase may be reused early.
+        if (cr_cnt > 0 && !mbar_wait(bar_oready, (cr_cnt - 1) & 1, abort_flag, 47)) return;
+        ++cr_cnt;
         bar->corr[t][row] = (m_new != m_run) ? corr : 1.f;
         __syncwarp();
         if (lane == 0) mbar_arrive(smem_addr(&bar->corr_ready[t]));
@@ -157,26 +205,27 @@ __device__ __forceinline__ void softmax_loop(const Tc5Params& p, Barriers* bar, 
       const float neg_ms = -m_use * scale_log2;
       const uint64_t negms2 = pack_f32x2(neg_ms, neg_ms);
 
-      // ---- exponentials, P -> TMEM (overwrites the S columns, which are all in registers now) ----
+      // ---- exponentials, P -> shared memory ----
       uint64_t sum2[4];
 #pragma unroll
       for (int q = 0; q < 4; ++q) sum2[q] = pack_f32x2(0.f, 0.f);
       uint32_t pk[16];
       chunk_exp<T, POLY>(sc[0], scale2, negms2, sum2, pk);
-      tmem_st16(s_tmem, pk);
+      // P.V of the previous block must have read P_t before it is overwritten
+      if (blk > 0 && !mbar_wait(bar_odone, (blk - 1) & 1, abort_flag, 42)) return;
+      FA_TR(tr, 5);
+      store_p_chunk(p_row, p_xor, 0, pk);
       chunk_exp<T, POLY>(sc[1], scale2, negms2, sum2, pk);
-      tmem_st16(s_tmem + 16, pk);
-      tmem_wait_st();
-      tc_fence_before();
+      store_p_chunk(p_row, p_xor, 1, pk);
+      fence_proxy_async();  // generic-proxy stores -> visible to the MMA (async proxy)
       __syncwarp();
       if (lane == 0) mbar_arrive(smem_addr(&bar->p_full[t][0]));  // first 64 keys of P are ready
       FA_TR(tr, 3);
       chunk_exp<T, POLY>(sc[2], scale2, negms2, sum2, pk);
-      tmem_st16(s_tmem + 32, pk);
+      store_p_chunk(p_row, p_xor, 2, pk);
       chunk_exp<T, POLY>(sc[3], scale2, negms2, sum2, pk);
-      tmem_st16(s_tmem + 48, pk);
-      tmem_wait_st();
-      tc_fence_before();
+      store_p_chunk(p_row, p_xor, 3, pk);
+      fence_proxy_async();
       __syncwarp();
       if (lane == 0) mbar_arrive(smem_addr(&bar->p_full[t][1]));  // last 64 keys
       FA_TR(tr, 4);
@@ -184,11 +233,16 @@ __device__ __forceinline__ void softmax_loop(const Tc5Params& p, Barriers* bar, 
       unpack_f32x2(add_f32x2(add_f32x2(sum2[0], sum2[1]), add_f32x2(sum2[2], sum2[3])), s0, s1);
       l_run = l_run * corr + (s0 + s1);
     }
-    // final statistics for the epilogue
-    bar->row_max[t][row] = m_run;
-    bar->row_sum[t][row] = l_run;
+    // 1 / l for the epilogue, LSE from here.  The previous tile's epilogue must have read its 1 / l
+    // (a tile of a single block does not wait for anything else the epilogue does).
+    if (st_cnt > 0 && !mbar_wait(bar_ofree, (st_cnt - 1) & 1, abort_flag, 48)) return;
+    ++st_cnt;
+    bar->row_inv[t][row] = l_run > 0.f ? 1.f / l_run : 0.f;
     __syncwarp();
     if (lane == 0) mbar_arrive(smem_addr(&bar->stats_ready[t]));
+    if (i < ti.q_len)
+      p.a.lse[(int64_t)ti.bi * p.a.lse_batch_stride + (int64_t)ti.hh * p.a.lse_head_stride + ti.q_row0 + i] =
+          l_run > 0.f ? (m_run * p.a.softmax_scale + __logf(l_run)) : INFINITY;
   }
 }
 
@@ -231,7 +285,8 @@ __device__ __forceinline__ void correction_loop(const Tc5Params& p, Barriers* ba
   uint32_t cr_cnt[2] = {0, 0}, od_cnt[2] = {0, 0}, st_cnt[2] = {0, 0};
   Tracer tr(p, 2, warp_in_wg == 0 && lane == 0);
 
-  for (int n = blockIdx.x; n < p.total_tiles; n += gridDim.x) {
+  TileSched sched(p);
+  for (int n = sched.first(); n < p.total_tiles; n = sched.next()) {
     TileInfo ti;
     tile_info(p, n, ti);
     if (ti.uhi <= ti.ulo) continue;
@@ -239,11 +294,11 @@ __device__ __forceinline__ void correction_loop(const Tc5Params& p, Barriers* ba
 #pragma unroll
       for (int t = 0; t < 2; ++t) {
         if (!(ti.has[t] && j > ti.jlo[t] && j < ti.jhi[t])) continue;
-        if (!mbar_wait(smem_addr(&bar->corr_ready[t]), cr_cnt[t] & 1, abort_flag)) return;
+        if (!mbar_wait(smem_addr(&bar->corr_ready[t]), cr_cnt[t] & 1, abort_flag, 43)) return;
         ++cr_cnt[t];
         FA_TR(tr, 10 + t);
         const float f = bar->corr[t][row];
-        if (!mbar_wait(smem_addr(&bar->o_done[t]), od_cnt[t] & 1, abort_flag)) return;  // P.V of block j-1 done
+        if (!mbar_wait(smem_addr(&bar->o_done[t]), od_cnt[t] & 1, abort_flag, 44)) return;  // P.V of block j-1 done
         ++od_cnt[t];
         if (__any_sync(0xffffffffu, f != 1.f)) {
           tc_fence_after();
@@ -259,17 +314,16 @@ __device__ __forceinline__ void correction_loop(const Tc5Params& p, Barriers* ba
 #pragma unroll
     for (int t = 0; t < 2; ++t) {
       if (!ti.has[t]) continue;
-      if (!mbar_wait(smem_addr(&bar->stats_ready[t]), st_cnt[t] & 1, abort_flag)) return;
+      if (!mbar_wait(smem_addr(&bar->stats_ready[t]), st_cnt[t] & 1, abort_flag, 45)) return;
       ++st_cnt[t];
-      const float m_run = bar->row_max[t][row], l_run = bar->row_sum[t][row];
-      if (!mbar_wait(smem_addr(&bar->o_done[t]), od_cnt[t] & 1, abort_flag)) return;  // last P.V done
+      const float inv = bar->row_inv[t][row];
+      if (!mbar_wait(smem_addr(&bar->o_done[t]), od_cnt[t] & 1, abort_flag, 46)) return;  // last P.V done
       ++od_cnt[t];
       tc_fence_after();
       const int i = ti.row0[t] + row;
       const bool row_valid = i < ti.q_len;
       T* o_ptr = reinterpret_cast<T*>(p.a.o) + (int64_t)ti.bi * p.a.o_batch_stride +
                  (int64_t)(ti.q_row0 + i) * p.a.o_row_stride + (int64_t)ti.hh * p.a.o_head_stride;
-      const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
       const uint32_t o_tmem = tmem + lane_addr + 256 + t * 128;
       uint32_t a[32], b[32];
       tmem_ld32(o_tmem, a);
@@ -305,9 +359,6 @@ __device__ __forceinline__ void correction_loop(const Tc5Params& p, Barriers* ba
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(smem_addr(&bar->o_free[t]));
-      if (row_valid)
-        p.a.lse[(int64_t)ti.bi * p.a.lse_batch_stride + (int64_t)ti.hh * p.a.lse_head_stride + ti.q_row0 + i] =
-            l_run > 0.f ? (m_run * p.a.softmax_scale + __logf(l_run)) : INFINITY;
     }
   }
 }

@@ -47,12 +47,13 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
   return ok != 0;
 }
 // Bounded wait.  Returns false if the CTA is aborting (set here on expiry, or by another thread).
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+// `id` (1..255) names the wait; the first one that expires is what the abort flag holds.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int id = 1) {
   for (uint32_t i = 0; i < kSpinLimit; ++i) {
     if (mbar_try_wait(bar, parity)) return true;
     if ((i & 255u) == 255u && *abort_flag) return false;
   }
-  *abort_flag = 1;
+  if (*abort_flag == 0) *abort_flag = id;
   return false;
 }
 __device__ __forceinline__ void fence_barrier_init() {
