@@ -194,12 +194,30 @@ static int make_plan(const fa_fwd_params& a, Planned* out) {
   int bps = ceil_div(max_blocks, ns);
   ns = ceil_div(max_blocks, bps);
 
+  // Persistent decode: ragged lengths leave a tail of unequal CTAs; CTAs that stay resident and take
+  // equal shares of the KV blocks of the whole launch do not.  A unit cut by a CTA boundary is
+  // finished by the merge kernel from up to kPersistSlots partials.  (Window-bound ranges are
+  // nearly equal; there the merge launch costs what the balance gains -- measured.)
+  constexpr int kPersistSlots = 4;
+  bool persistent = false;
+  long long persist_grid = 0;
+  if (kernel_id == FA_KERNEL_DECODE && a.num_splits == 0 && !a.cu_seqlens_q && a.kv_total == 0 && !a.partial_out) {
+    const bool window_bound = is_local && wl >= 0 && range < max_k_bound;
+    const long long resident = std::max(1, (227 * 1024) / std::max(1, ci.smem_bytes));
+    persist_grid = (long long)num_sm * resident;
+    persistent = a.seqused_k != nullptr && !window_bound && base * max_blocks >= 4 * persist_grid &&
+                 base * (max_blocks + 1) < 0x3fffffffLL;
+    if (const char* e = std::getenv("FA_B200_DECODE_PERSISTENT")) persistent = persistent && std::atoi(e) != 0;  // tuning override
+    if (const char* e = std::getenv("FA_B200_DECODE_PERSISTENT_GRID")) persist_grid = std::max(1, std::atoi(e));  // tuning override
+    if (persistent) { ns = kPersistSlots; bps = 0; }
+  }
+
   const bool varlen_q = a.cu_seqlens_q != nullptr;
   const int64_t lse_elems = varlen_q ? (int64_t)a.h * a.total_q : (int64_t)a.b * a.h * a.seqlen_q;
   if (ns > 1) {
     const bool canonical = varlen_q ? (a.lse_head_stride == a.total_q)
                                     : (a.lse_batch_stride == (int64_t)a.h * a.seqlen_q && a.lse_head_stride == a.seqlen_q);
-    if (!canonical) { ns = 1; bps = max_blocks; }
+    if (!canonical) { ns = 1; bps = max_blocks; persistent = false; }
   }
 
   fa_fwd_plan& pl = out->pl;
@@ -211,7 +229,7 @@ static int make_plan(const fa_fwd_params& a, Planned* out) {
   pl.m_blocks = m_blocks;
   pl.num_splits = ns;
   pl.blocks_per_split = bps;
-  pl.grid = (int)(base * ns);
+  pl.grid = persistent ? (int)persist_grid : (int)(base * ns);
   pl.threads = ci.threads;
   pl.smem_bytes = ci.smem_bytes;
   pl.is_causal = is_causal;
@@ -234,6 +252,7 @@ static int make_plan(const fa_fwd_params& a, Planned* out) {
   kp.m_blocks = m_blocks;
   kp.num_splits = ns;
   kp.blocks_per_split = bps;
+  kp.persistent = persistent ? 1 : 0;
   kp.scale_log2 = a.softmax_scale * kLog2e;
   kp.lse_elems = lse_elems;
 

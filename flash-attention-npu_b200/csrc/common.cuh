@@ -24,6 +24,7 @@ struct KParams {
   int32_t heads_eff;  // h / gp
   int32_t m_blocks;
   int32_t num_splits, blocks_per_split;
+  int32_t persistent;  // decode kernel: persistent CTAs with equal shares of the KV blocks; num_splits = partial slots
   float scale_log2;   // softmax_scale * log2(e)   (softcap: log2(e) only, see kernel)
   float* o_partial;   // [split][lse_index][d] fp32 (num_splits > 1)
   float* lse_partial; // [split][lse_index]

@@ -94,11 +94,12 @@ __device__ __forceinline__ void decode_fix_rows(const KParams& p, const SeqView<
 template <class Tr>
 __device__ __forceinline__ void decode_producer(const KParams& p, const SeqView<typename Tr::T>& sv,
                                                 const CUtensorMap* tm_k, const CUtensorMap* tm_v, uint32_t pipe_base,
-                                                uint32_t full0, uint32_t empty0, int my_lo, int n_blocks, int hk,
-                                                int batch_row, volatile int* abort_flag) {
+                                                uint32_t full0, uint32_t empty0, int my_lo, int n_blocks,
+                                                uint32_t it_base, int hk, int batch_row, volatile int* abort_flag) {
   for (int it = 0; it < n_blocks; ++it) {
-    const int stage = it % Tr::ST;
-    if (it >= Tr::ST && !tc5::mbar_wait(empty0 + stage * 8, ((it / Tr::ST) - 1) & 1, abort_flag)) return;
+    const uint32_t git = it_base + (uint32_t)it;  // stages this CTA has filled so far: ring position and parity
+    const int stage = (int)(git % Tr::ST);
+    if (git >= (uint32_t)Tr::ST && !tc5::mbar_wait(empty0 + stage * 8, ((git / Tr::ST) - 1) & 1, abort_flag)) return;
     const uint32_t k_base = pipe_base + stage * Tr::STAGE_BYTES, v_base = k_base + Tr::KV_BYTES;
     const uint32_t full = full0 + stage * 8;
     const int t0 = (my_lo + it) * Tr::BN;

@@ -158,10 +158,11 @@ bool tc5_eligible(const fa_fwd_params& a, bool is_causal, bool is_local, int wl_
   (void)is_causal;
   (void)is_local;
   if (a.d != 128 || a.seqlen_q < 128) return false;
-  if (a.cu_seqlens_q || a.cu_seqlens_k) return false;  // varlen: not yet
+  // varlen: both sides packed, and the number of k / v rows known (TMA bound)
+  if ((a.cu_seqlens_q != nullptr) != (a.cu_seqlens_k != nullptr)) return false;
+  if (a.cu_seqlens_k && a.total_k <= 0) return false;
   if (a.seqused_k || a.block_table || a.k_new || a.alibi_slopes || a.cache_batch_idx || a.rotary_cos) return false;
   if (a.softcap > 0.f || a.partial_out || a.kv_total > 0 || wl_on_device) return false;
-  if ((a.cu_seqlens_q != nullptr) != (a.cu_seqlens_k != nullptr)) return false;
   // TMA: 16-byte aligned bases and strides
   auto al = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; };
   if (!al(a.q) || !al(a.k) || !al(a.v) || !al(a.o)) return false;
@@ -225,12 +226,13 @@ int tc5_launch(const fa_fwd_params& a, const fa_fwd_plan& pl, cudaStream_t st, s
   CUtensorMap tq, tk, tv;
   bool ok = true;
   if (varlen) {
-    // total_k is not passed explicitly: rows past the end of the tensor are never addressed by a
-    // valid (row < k_len) key, so a generous bound of b * max_seqlen_k rows would over-read; use the
-    // exact total from the caller-provided upper bound instead.
-    ok = false;
-  }
-  if (!varlen) {
+    // Packed sequences: one row axis for the whole tensor.  A tile that runs past the end of its
+    // sequence reads rows of the next one (masked by the key range, never stored), a tile that
+    // runs past the end of the tensor reads the TMA fill value.
+    ok = encode_map(&tq, a.q, a.dtype, a.d, a.h, a.total_q, 1, a.q_head_stride, a.q_row_stride, 0) &&
+         encode_map(&tk, a.k, a.dtype, a.d, a.h_k, a.total_k, 1, a.k_head_stride, a.k_row_stride, 0) &&
+         encode_map(&tv, a.v, a.dtype, a.d, a.h_k, a.total_k, 1, a.v_head_stride, a.v_row_stride, 0);
+  } else {
     ok = encode_map(&tq, a.q, a.dtype, a.d, a.h, a.seqlen_q, a.b, a.q_head_stride, a.q_row_stride, a.q_batch_stride) &&
          encode_map(&tk, a.k, a.dtype, a.d, a.h_k, a.seqlen_k, a.b, a.k_head_stride, a.k_row_stride, a.k_batch_stride) &&
          encode_map(&tv, a.v, a.dtype, a.d, a.h_k, a.seqlen_k, a.b, a.v_head_stride, a.v_row_stride, a.v_batch_stride);

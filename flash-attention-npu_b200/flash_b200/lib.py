@@ -41,7 +41,7 @@ class FwdParams(C.Structure):
             "rotary_dim", "rotary_seqlen", "rotary_interleaved", "dtype",
             "causal", "window_left", "window_right", "max_seqlen_k_known",
             "kv_pos_offset", "kv_total", "partial_out",
-            "num_splits", "kernel", "num_sm")]
+            "num_splits", "kernel", "num_sm", "total_k")]
         + [("softmax_scale", C.c_float), ("softcap", C.c_float)]
     )
 

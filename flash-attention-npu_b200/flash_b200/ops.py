@@ -80,6 +80,7 @@ def build_params(q, k, v, out, lse, *, k_new=None, v_new=None, cu_seqlens_q=None
         p.k_batch_stride, p.k_row_stride, p.k_head_stride = 0, k.stride(0), k.stride(1)
         p.v_batch_stride, p.v_row_stride, p.v_head_stride = 0, v.stride(0), v.stride(1)
         p.seqlen_k = int(max_seqlen_k)
+        p.total_k = int(k.shape[0])
     else:
         if k.dim() != 4:
             raise RuntimeError("k must be 4-dimensional")

@@ -107,6 +107,8 @@ typedef struct fa_fwd_params {
   int32_t num_splits; /* 0 heuristic, 1 never split, > 1 requested number of KV splits */
   int32_t kernel;     /* enum fa_kernel_id */
   int32_t num_sm;     /* 0 = query the current device */
+  int32_t total_k;    /* rows of k / v when cu_seqlens_k is set (0 = not given: the tcgen05 kernel, which needs
+                         the bound for its TMA descriptors, is then not used for varlen input) */
   float softmax_scale;
   float softcap; /* 0 = off */
 } fa_fwd_params;

@@ -172,3 +172,38 @@ def test_errors_raise_runtime_error():
                                     cache_leftpad=torch.zeros(1, dtype=torch.int32, device="cuda"))
     with pytest.raises(RuntimeError, match="CUDA"):
         fa2.flash_attn_func(q.cpu(), q.cpu(), q.cpu())
+
+
+@pytest.mark.parametrize("paged", [False, True])
+def test_persistent_decode_ragged(paged):
+    """Ragged cache lengths on the persistent decode path (CTAs take equal shares of the KV blocks of the whole
+    launch, units cut by a CTA boundary are merged from partials): an empty sequence, very short and full ones,
+    append + rotary in place, GQA packing."""
+    from flash_b200 import lib as L
+    from flash_b200 import ops
+    g = torch.Generator().manual_seed(77)
+    b, h, hk, d, s_cache, page = 24, 16, 4, 128, 2304, 256
+    q = U.normal((b, 1, h, d), BF, g)
+    kc, vc = U.normal((b, s_cache, hk, d), BF, g), U.normal((b, s_cache, hk, d), BF, g)
+    k, v = U.normal((b, 1, hk, d), BF, g), U.normal((b, 1, hk, d), BF, g)
+    lens = torch.randint(1, s_cache - 1, (b,), generator=g, dtype=torch.int32)
+    lens[0], lens[1], lens[2], lens[3] = 0, 1, s_cache - 1, 63
+    cos, sin = U.rotary_tables(s_cache + 8, 64, BF)
+    bt = None
+    if paged:
+        nblk = b * s_cache // page
+        perm = torch.randperm(nblk, generator=g)
+        bt = perm.view(b, s_cache // page).to(torch.int32)
+        pool_k, pool_v = torch.empty((nblk, page, hk, d), dtype=BF), torch.empty((nblk, page, hk, d), dtype=BF)
+        pool_k[perm] = kc.view(nblk, page, hk, d)
+        pool_v[perm] = vc.view(nblk, page, hk, d)
+        kc, vc = pool_k, pool_v
+    out, lse, go, gl = _run_both(q, kc, vc, k, v, lens, cos=cos, sin=sin, bt=bt, causal=True)
+    U.check_rules(out, lse, go, gl, tag=f"persistent decode paged={paged}")
+    # the plan of this problem is the persistent one: a resident grid and a fixed number of partial slots
+    _, _, plan = ops.attention_forward(q.cuda(), kc.cuda(), vc.cuda(), k_new=k.cuda(), v_new=v.cuda(),
+                                       seqused_k=lens.cuda(), block_table=None if bt is None else bt.cuda(),
+                                       rotary_cos=cos.cuda(), rotary_sin=sin.cuda(), softmax_scale=d ** -0.5,
+                                       causal=True, return_plan=True)
+    assert plan.kernel == L.KERNEL_DECODE and plan.num_splits == 4 and plan.grid <= 2 * 160
+    assert L.load().fa_b200_check_status(torch.cuda.current_stream().cuda_stream) == 0
