@@ -205,9 +205,11 @@ static int make_plan(const fa_fwd_params& a, Planned* out) {
     const bool window_bound = is_local && wl >= 0 && range < max_k_bound;
     const long long resident = std::max(1, (227 * 1024) / std::max(1, ci.smem_bytes));
     persist_grid = (long long)num_sm * resident;
-    persistent = a.seqused_k != nullptr && !window_bound && base * max_blocks >= 4 * persist_grid &&
-                 base * (max_blocks + 1) < 0x3fffffffLL;
-    if (const char* e = std::getenv("FA_B200_DECODE_PERSISTENT")) persistent = persistent && std::atoi(e) != 0;  // tuning override
+    const bool can_persist = (a.seqused_k != nullptr || window_bound) && base * max_blocks >= 4 * persist_grid &&
+                             base * (max_blocks + 1) < 0x3fffffffLL;
+    persistent = can_persist && !window_bound;
+    if (const char* e = std::getenv("FA_B200_DECODE_PERSISTENT"))  // tuning override: 0 off, 1 default rule, 2 also window-bound
+      persistent = can_persist && (std::atoi(e) == 2 || (std::atoi(e) == 1 && !window_bound));
     if (const char* e = std::getenv("FA_B200_DECODE_PERSISTENT_GRID")) persist_grid = std::max(1, std::atoi(e));  // tuning override
     if (persistent) { ns = kPersistSlots; bps = 0; }
   }

@@ -7,8 +7,9 @@
 //     per 60 cycles per SM, capped it at 1.1 TB/s).  Paged caches work through a 4-D tensor map
 //     (d, kv head, row in page, page) when page_size is a multiple of BN;
 //   * NCW consumer warps each own a slice of the stage's keys (own running max / sum / O, merged
-//     once at the end) and only wait on the stage's "full" barrier; they release it through the
-//     "empty" barrier.  No __syncthreads inside the main loop.
+//     once at the end through a slab that is not part of the ring) and only wait on the stage's
+//     "full" barrier; they release it through the "empty" barrier.  The producer never synchronises
+//     with the consumers except through the ring, also across the units a persistent CTA works on.
 // K / V tiles use the TMA 128-byte swizzle (conflict-free ldmatrix).
 // Rows of the appended range come from k_new / v_new (k rotated on the fly), rows past the end
 // are zero-filled; each consumer warp repairs the rows of its own key slice after the TMA landed.
@@ -39,12 +40,12 @@ struct DecTraits {
   static constexpr int STAGE_BYTES = 2 * KV_BYTES;
   static constexpr int PIPE_BYTES = ST * STAGE_BYTES;
   static constexpr int SLAB_LD = HD + 4;
-  static constexpr int SLAB_BYTES = WN * BM * SLAB_LD * 4;
-  static constexpr int MAIN_BYTES = PIPE_BYTES > SLAB_BYTES ? PIPE_BYTES : SLAB_BYTES;
+  static constexpr int SLAB_BYTES = BM * SLAB_LD * 4;  // merged output rows of the tile (fp32), not part of the ring
+  static constexpr int MAIN_BYTES = PIPE_BYTES + SLAB_BYTES;
   static constexpr int Q_BYTES = BM * PITCH;
   static constexpr int ML_BYTES = WN * BM * 8;
   static constexpr int BAR_BYTES = 128 + 2 * ST * 8;
-  // [pipeline | Q | (m, l) | barriers], the pipeline at a 1024-byte aligned base
+  // [pipeline | slab | Q | (m, l) | barriers], the pipeline at a 1024-byte aligned base
   static constexpr int SMEM_BYTES = 1024 + MAIN_BYTES + Q_BYTES + ML_BYTES + BAR_BYTES;
   static constexpr bool Q_IN_REGS = (MT == 1);
   static_assert(NW % 16 == 0, "each consumer warp needs a multiple of 16 keys");
@@ -92,14 +93,14 @@ __device__ __forceinline__ void decode_fix_rows(const KParams& p, const SeqView<
 // Producer: one elected lane issues four tiled TMA loads per stage (K and V, two 64-column halves
 // each).  Tensor maps are 4-D (d, kv head, row, batch-or-page); every load targets the issuing CTA only.
 template <class Tr>
-__device__ __forceinline__ void decode_producer(const KParams& p, const SeqView<typename Tr::T>& sv,
+__device__ __forceinline__ bool decode_producer(const KParams& p, const SeqView<typename Tr::T>& sv,
                                                 const CUtensorMap* tm_k, const CUtensorMap* tm_v, uint32_t pipe_base,
                                                 uint32_t full0, uint32_t empty0, int my_lo, int n_blocks,
                                                 uint32_t it_base, int hk, int batch_row, volatile int* abort_flag) {
   for (int it = 0; it < n_blocks; ++it) {
     const uint32_t git = it_base + (uint32_t)it;  // stages this CTA has filled so far: ring position and parity
     const int stage = (int)(git % Tr::ST);
-    if (git >= (uint32_t)Tr::ST && !tc5::mbar_wait(empty0 + stage * 8, ((git / Tr::ST) - 1) & 1, abort_flag)) return;
+    if (git >= (uint32_t)Tr::ST && !tc5::mbar_wait(empty0 + stage * 8, ((git / Tr::ST) - 1) & 1, abort_flag)) return false;
     const uint32_t k_base = pipe_base + stage * Tr::STAGE_BYTES, v_base = k_base + Tr::KV_BYTES;
     const uint32_t full = full0 + stage * 8;
     const int t0 = (my_lo + it) * Tr::BN;
@@ -118,6 +119,7 @@ __device__ __forceinline__ void decode_producer(const KParams& p, const SeqView<
     }
     __syncwarp();
   }
+  return true;
 }
 
 }  // namespace fa

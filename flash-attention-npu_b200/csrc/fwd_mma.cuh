@@ -123,11 +123,12 @@ __device__ __forceinline__ void load_kv_block(const KParams& p, const SeqView<ty
 // The designated CTA of a (batch, kv head) writes the appended tokens into the cache
 // (k rotated, v copied).  Bit-exact with the host formula documented at rotary_chunk.
 template <class Tr>
-__device__ __forceinline__ void append_to_cache(const KParams& p, const SeqView<typename Tr::T>& sv, int tid) {
+__device__ __forceinline__ void append_to_cache(const KParams& p, const SeqView<typename Tr::T>& sv, int tid,
+                                                int nthreads = Tr::NTHREADS) {
   using T = typename Tr::T;
   const int chunks = p.a.d >> 3;
   const int total = p.a.seqlen_new * chunks;
-  for (int c = tid; c < total; c += Tr::NTHREADS) {
+  for (int c = tid; c < total; c += nthreads) {
     const int tn = c / chunks, ch = c - tn * chunks;
     const int t = sv.l_cache + tn;
     const T* krow = sv.knew + (int64_t)tn * p.a.knew_row_stride;
