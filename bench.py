@@ -36,6 +36,16 @@ import torch  # noqa: E402
 
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
 
+# dram__bytes_read.sum + dram__bytes_write.sum of the dominant kernel, from one ncu capture of a shrunk case of each
+# workload (profiles/*.md), as (bytes, units of that case): traffic grows in proportion to the units a launch
+# processes, so a full launch is  bytes * units / units_of_the_case.
+NCU_TRAFFIC = {
+    "c2": (145.85e6 + 18.02e6, 137438953472.0, "ncu, batch 1 of 4 (profiles/fwd_tc5_kernel_c2_shrink4.md), scaled by FLOPs"),
+    "c3": (255.98e6 + 4.84e6, 253687872.0, "ncu, batch 16 of 64 (profiles/fwd_decode_kernel_c3_shrink4.md), scaled by bytes"),
+    "c4": (134.33e6 + 3.70e6, 130785280.0, "ncu, batch 8 of 32 (profiles/fwd_decode_kernel_c4_shrink4.md), scaled by bytes"),
+    "c5": (537.13e6 + 3.56e6, 537135104.0, "ncu, key length / 8 (profiles/fwd_decode_kernel_c5_shrink8.md), scaled by bytes"),
+}
+
 
 def load_peaks():
     path = os.path.join(ROOT, "MEASURED_PEAKS.json")
@@ -140,14 +150,12 @@ class Prefill:
         self.ho.copy_(out, non_blocking=True)
         self.hl.copy_(lse, non_blocking=True)
 
-    launches_per_step = 1
-
     def cpu_sample(self, budget_s):
         """Oracle on (1 batch, 4 heads) slices until the time budget is used; returns (units, seconds, text)."""
         from oracle import api as OA
         g = torch.Generator().manual_seed(2)
         done, t_total, n = 0.0, 0.0, 0
-        while t_total < budget_s and n < 32:
+        while t_total < budget_s and n < 256:
             q, k, v = [(torch.randn((1, self.s, 4, self.d), generator=g) / math.sqrt(2)).to(BF) for _ in range(3)]
             t0 = time.perf_counter()
             OA.flash_attn_func(q, k, v, causal=True)
@@ -197,7 +205,6 @@ class DecodeContiguous(DecodeBase):
         row = self.hk * self.d * 2 * 2
         self.units = float((self.lens.long() + 1).sum()) * row + 2 * self.b * self.h * self.d * 2 \
             + 2 * self.b * row + self.b * self.h * 4 + self.b * 4 + 2 * self.b * 64 * 2
-        self.launches_per_step = 2
 
     def setup_e2e(self):
         super().setup_e2e()
@@ -248,7 +255,6 @@ class DecodePaged(DecodeBase):
         self.q = torch.randn((self.b, self.s_q, self.h, self.d), generator=g, device=dev).to(BF)
         n_b = torch.clamp(self.lens.long(), max=4096 + self.s_q)
         self.units = float(n_b.sum()) * self.hk * self.d * 4 + 2 * self.q.numel() * 2 + self.b * self.h * self.s_q * 4
-        self.launches_per_step = 2
 
     def run(self, q):
         import flash_attn_npu_v2 as fa2
@@ -288,7 +294,6 @@ class DecodeLongSharded(DecodeBase):
         self.kc = torch.randn((self.b, n, self.hk, self.d), generator=g2, device=dev).to(BF)
         self.vc = torch.randn((self.b, n, self.hk, self.d), generator=g2, device=dev).to(BF)
         self.units = float(self.b) * n * self.hk * self.d * 4 + 264192
-        self.launches_per_step = 3
 
     def run(self, q):
         from flash_b200 import dist as D
@@ -398,10 +403,13 @@ def main():
     stream = torch.cuda.current_stream()
     ev = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps + 1)]
     barrier()
+    from flash_b200 import lib as _L
+    launches0 = _L.load().fa_b200_launch_count()
     ev[0].record(stream)
     for i in range(args.steps):
         wl.step()
         ev[i + 1].record(stream)
+    gpu_launches = int(_L.load().fa_b200_launch_count() - launches0)  # counted by the library, not assumed
     barrier()
     total_ms = ev[0].elapsed_time(ev[-1])
     per = sorted(ev[i].elapsed_time(ev[i + 1]) for i in range(args.steps))
@@ -453,6 +461,10 @@ def main():
         else:
             peak, runit = peaks["hbm_gbs"], "GB/s"
         strong = getattr(wl, "strong", False)
+        traffic, traffic_src = None, None
+        if args.workload in NCU_TRAFFIC:
+            t_bytes, t_units, traffic_src = NCU_TRAFFIC[args.workload]
+            traffic = t_bytes * wl.units / t_units
         line = {
             "metric": wl.metric, "value": value, "unit": wl.unit, "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": total_ms / args.steps, "higher_is_better": True,
@@ -461,10 +473,11 @@ def main():
                        else "q+k+v+o = 537 MB per step, larger than the 126 MB L2", "median_ms_per_step": med_ms,
                        "per_gpu_units": wl.units},
             "roofline": {"bound": wl.bound, "achieved": achieved, "peak": peak, "unit": runit,
-                         "frac": achieved / peak, "traffic": None, "peak_source": peaks["_source"],
-                         "per_launch": "one attention launch per step" + (" (+ merge)" if wl.launches_per_step > 1 else "")},
+                         "frac": achieved / peak, "traffic": traffic, "traffic_unit": "bytes per launch",
+                         "traffic_source": traffic_src, "peak_source": peaks["_source"],
+                         "per_launch": "one attention launch per step" + (" (+ merge)" if gpu_launches > args.steps else "")},
             "e2e": {"value": e2e, "unit": wl.unit, "h2d_bytes_per_step": wl.h2d, "d2h_bytes_per_step": wl.d2h},
-            "gpu_launches": wl.launches_per_step * args.steps,
+            "gpu_launches": gpu_launches,
             "clocks": clocks,
         }
         if not args.no_cpu_baseline and world == 1:

@@ -6,6 +6,7 @@
 #include <cuda_runtime.h>
 
 #include <algorithm>
+#include <atomic>
 #include <cstdio>
 #include <cstdlib>
 #include <cstring>
@@ -19,6 +20,7 @@
 namespace fa {
 
 static thread_local std::string g_err;
+static std::atomic<long long> g_launches{0};  // kernel launches issued so far (fa_b200_launch_count)
 
 static int fail(int code, const std::string& msg) {
   g_err = msg;
@@ -277,6 +279,7 @@ static int launch_combine(const fa_combine_params& c, cudaStream_t st) {
   else return fail(FA_ERR_INVALID, "bad out_dtype");
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return fail(FA_ERR_CUDA, std::string("combine launch: ") + cudaGetErrorString(e));
+  ++g_launches;
   return FA_OK;
 }
 
@@ -286,7 +289,11 @@ static int run_fwd(const fa_fwd_params& a, void* workspace, size_t workspace_byt
   int rc = make_plan(a, &P);
   if (rc != FA_OK) return rc;
   if (a.total_q == 0 || a.seqlen_q == 0) return FA_OK;
-  if (P.pl.kernel == FA_KERNEL_TCGEN05) return tc5_launch(a, P.pl, st, &g_err);
+  if (P.pl.kernel == FA_KERNEL_TCGEN05) {
+    rc = tc5_launch(a, P.pl, st, &g_err);
+    if (rc == FA_OK) ++g_launches;
+    return rc;
+  }
 
   KParams& kp = P.kp;
   if (P.pl.num_splits > 1) {
@@ -318,6 +325,7 @@ static int run_fwd(const fa_fwd_params& a, void* workspace, size_t workspace_byt
     case 256: e = bf ? launch_mma_256_bf16(P.pl.config, kp, P.pl.grid, st) : launch_mma_256_fp16(P.pl.config, kp, P.pl.grid, st); break;
   }
   if (e != cudaSuccess) return fail(FA_ERR_CUDA, std::string("attention kernel launch: ") + cudaGetErrorString(e));
+  ++g_launches;
 
   if (P.pl.num_splits > 1) {
     fa_combine_params c;
@@ -473,5 +481,7 @@ const char* fa_b200_status_string(int status) {
 }
 
 int fa_b200_abi_version(void) { return FA_B200_ABI_VERSION; }
+
+long long fa_b200_launch_count(void) { return fa::g_launches.load(); }
 
 }  // extern "C"

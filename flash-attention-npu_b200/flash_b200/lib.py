@@ -71,6 +71,7 @@ class CombineParams(C.Structure):
 EXPORTS = (
     "fa_b200_fwd", "fa_b200_fwd_noalloc", "fa_b200_fwd_plan", "fa_b200_combine", "fa_b200_normalize_window",
     "fa_b200_check_status", "fa_b200_last_error", "fa_b200_status_string", "fa_b200_abi_version",
+    "fa_b200_launch_count",
 )
 
 _lib = None
@@ -101,6 +102,8 @@ def load() -> C.CDLL:
     lib.fa_b200_status_string.argtypes = [C.c_int]
     lib.fa_b200_status_string.restype = C.c_char_p
     lib.fa_b200_abi_version.restype = C.c_int
+    lib.fa_b200_launch_count.restype = C.c_longlong
+    lib.fa_b200_launch_count.argtypes = []
     if lib.fa_b200_abi_version() != 1:
         raise ImportError("libfa_b200.so ABI version mismatch")
     _lib = lib

@@ -181,6 +181,11 @@ const char* fa_b200_last_error(void);
 const char* fa_b200_status_string(int status);
 int fa_b200_abi_version(void);
 
+/* Kernel launches this library has issued in this process so far (all entry points, all threads).  No counterpart
+ * in the reference; callers difference it around a region to count launches, e.g. to check that a path ran on the
+ * GPU kernels of this library and how many of them it took. */
+long long fa_b200_launch_count(void);
+
 #ifdef __cplusplus
 }
 #endif
