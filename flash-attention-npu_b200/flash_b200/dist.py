@@ -65,6 +65,29 @@ def sharded_decode(q: torch.Tensor, k_shard: torch.Tensor, v_shard: torch.Tensor
     ``local_partial`` / ``merge`` exist so that the host-side plumbing can be exercised on CPU
     ranks (gloo) with stand-in compute; they default to the CUDA kernels.
     """
+    if softmax_scale is None:
+        softmax_scale = q.shape[-1] ** (-0.5)
+    world = dist.get_world_size(group) if dist.is_initialized() else 1
+    out_dtype = out_dtype or q.dtype
+    if local_partial is None and merge is None:
+        # CUDA path: the kernel writes its partial straight into the message buffer [O | LSE] and the
+        # merge writes LSE in its final (b, h, s) layout -- no packing or transposing kernels.
+        from . import ops
+        b, s, h, d = q.shape
+        n_o, n_l = b * s * h * d, b * h * s
+        send = torch.empty(n_o + n_l, dtype=torch.float32, device=q.device)
+        ops.attention_forward(q, k_shard, v_shard, out=send[:n_o].view(b, s, h, d), lse=send[n_o:].view(b, h, s),
+                              softmax_scale=softmax_scale, causal=causal, kv_pos_offset=kv_pos_offset,
+                              kv_total=kv_total, partial_out=True)
+        if world > 1:
+            recv = torch.empty(world * send.numel(), dtype=torch.float32, device=send.device)
+            dist.all_gather_into_tensor(recv, send, group=group)
+        else:
+            recv = send
+        o_all, lse_all = unpack_gathered(recv, world, (b, s, h, d), (b, h, s))
+        lse = torch.empty((b, h, s), dtype=torch.float32, device=q.device)
+        out, _ = ops.combine(o_all, lse_all, out_dtype=out_dtype, lse_out=lse.permute(0, 2, 1))
+        return out, lse
     if local_partial is None:
         from . import ops
 
@@ -76,13 +99,9 @@ def sharded_decode(q: torch.Tensor, k_shard: torch.Tensor, v_shard: torch.Tensor
 
         def merge(o_all, lse_all, dtype):
             return ops.combine(o_all, lse_all, out_dtype=dtype)
-    if softmax_scale is None:
-        softmax_scale = q.shape[-1] ** (-0.5)
-    world = dist.get_world_size(group) if dist.is_initialized() else 1
     o_part, lse_part = local_partial(q, k_shard, v_shard)   # (b, s, h, d) fp32, (b, h, s) fp32
     if o_part.dtype != torch.float32 or lse_part.dtype != torch.float32:
         raise RuntimeError("local partials must be fp32")
-    out_dtype = out_dtype or q.dtype
     send = pack_partial(o_part, lse_part)
     if world > 1:
         recv = torch.empty(world * send.numel(), dtype=torch.float32, device=send.device)

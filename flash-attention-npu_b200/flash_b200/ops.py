@@ -116,11 +116,12 @@ def build_params(q, k, v, out, lse, *, k_new=None, v_new=None, cu_seqlens_q=None
     return p
 
 
-def attention_forward(q, k, v, *, out=None, return_plan=False, **kw) -> Tuple[torch.Tensor, torch.Tensor]:
+def attention_forward(q, k, v, *, out=None, lse=None, return_plan=False, **kw) -> Tuple[torch.Tensor, torch.Tensor]:
     """Runs the forward on the current CUDA stream.  Returns (out, lse[, plan]).
 
     out has q's shape (dtype of q, fp32 when partial_out); lse is fp32 (b, h, s_q), or
     (h, total_q) for varlen q.  k / v caches are mutated in place when k_new, v_new are given.
+    ``out`` / ``lse`` may be given (e.g. views of one message buffer); they are allocated otherwise.
     """
     lib = L.load()
     if not (q.is_cuda and k.is_cuda and v.is_cuda):
@@ -149,10 +150,11 @@ def attention_forward(q, k, v, *, out=None, return_plan=False, **kw) -> Tuple[to
             raise RuntimeError("out must have the shape and device of q and a contiguous last dimension")
         if out.dtype != (torch.float32 if partial else q.dtype):
             raise RuntimeError("out has the wrong dtype")
-    if varlen_q:
-        lse = torch.empty((q.shape[1], q.shape[0]), dtype=torch.float32, device=q.device)
-    else:
-        lse = torch.empty((q.shape[0], q.shape[2], q.shape[1]), dtype=torch.float32, device=q.device)
+    lse_shape = (q.shape[1], q.shape[0]) if varlen_q else (q.shape[0], q.shape[2], q.shape[1])
+    if lse is None:
+        lse = torch.empty(lse_shape, dtype=torch.float32, device=q.device)
+    elif tuple(lse.shape) != lse_shape or lse.dtype != torch.float32 or lse.device != q.device or not lse.is_contiguous():
+        raise RuntimeError("lse must be a contiguous fp32 tensor of shape (b, h, s_q) / (h, total_q) on q's device")
     with torch.cuda.device(q.device):
         p = build_params(q, k, v, out, lse, num_sm=_num_sm(q.device), **kw)
         plan = L.FwdPlan()
@@ -182,9 +184,10 @@ def attention_forward_noalloc(q, k, v, out, lse, **kw) -> None:
 
 
 def combine(o_partial: torch.Tensor, lse_partial: torch.Tensor, out: Optional[torch.Tensor] = None,
-            out_dtype: Optional[torch.dtype] = None, partial_out: bool = False):
+            out_dtype: Optional[torch.dtype] = None, partial_out: bool = False, lse_out: Optional[torch.Tensor] = None):
     """Merge of split partials.  o_partial (n, b, s, h, d) fp32, lse_partial (n, b, s, h) fp32
-    (natural log, -inf = empty partial) -> out (b, s, h, d), lse (b, s, h)."""
+    (natural log, -inf = empty partial) -> out (b, s, h, d), lse (b, s, h).  ``lse_out``: an fp32
+    (b, s, h) destination of any strides (e.g. the transposed view of a (b, h, s) tensor)."""
     lib = L.load()
     if not o_partial.is_cuda:
         raise RuntimeError("flash_b200 runs on CUDA tensors only (there is no CPU implementation)")
@@ -200,7 +203,12 @@ def combine(o_partial: torch.Tensor, lse_partial: torch.Tensor, out: Optional[to
     code = {torch.float16: L.FA_FP16, torch.bfloat16: L.FA_BF16, torch.float32: L.FA_FP32_OUT}[out_dtype]
     if out is None:
         out = torch.empty((b, s, h, d), dtype=out_dtype, device=o_partial.device)
-    lse = torch.empty((b, s, h), dtype=torch.float32, device=o_partial.device)
+    if lse_out is None:
+        lse = torch.empty((b, s, h), dtype=torch.float32, device=o_partial.device)
+    else:
+        if tuple(lse_out.shape) != (b, s, h) or lse_out.dtype != torch.float32 or lse_out.device != o_partial.device:
+            raise RuntimeError("lse_out must be an fp32 (batch, seqlen, nheads) tensor on the partials' device")
+        lse = lse_out
     c = L.CombineParams()
     c.o_partial, c.lse_partial, c.o, c.lse = _ptr(o_partial), _ptr(lse_partial), _ptr(out), _ptr(lse)
     c.op_split_stride, c.op_batch_stride, c.op_row_stride, c.op_head_stride = o_partial.stride()[:4]
