@@ -127,3 +127,32 @@ def test_cpu_tensors_are_refused():
     q = torch.zeros(1, 1, 2, 64, dtype=torch.bfloat16)
     with pytest.raises(RuntimeError, match="CUDA"):
         v2.flash_attn_func(q, q, q)
+
+
+def test_plan_varlen_prefill_needs_total_k_for_the_tcgen05_kernel():
+    """Packed varlen input goes to the tcgen05 kernel only when the number of k / v rows is known (its TMA
+    descriptors need the bound); otherwise to the general kernel."""
+    kw = dict(b=3, seqlen_q=512, seqlen_k=640, h=8, h_k=2, d=128, total_q=1300, cu_seqlens_q=256, cu_seqlens_k=256,
+              q_row_stride=1024, q_head_stride=128, k_row_stride=256, k_head_stride=128, v_row_stride=256,
+              v_head_stride=128, o_row_stride=1024, o_head_stride=128, lse_batch_stride=0, lse_head_stride=1300, causal=1)
+    rc, pl = _plan(_params(total_k=1500, **kw))
+    assert rc == 0 and pl.kernel == L.KERNEL_TCGEN05 and pl.block_m == 256 and pl.grid == min(148, 2 * 3 * 8)
+    rc, pl = _plan(_params(total_k=0, **kw))
+    assert rc == 0 and pl.kernel == L.KERNEL_MMA
+
+
+def test_plan_persistent_decode_for_ragged_lengths_only():
+    """Ragged cache lengths (a device-side length vector) with enough work: resident CTAs with equal shares and a
+    fixed number of partial slots.  Window-bound ranges and explicit split requests keep the plain grid."""
+    kw = dict(b=64, seqlen_q=1, seqlen_k=8192, h=32, h_k=8, d=128, total_q=64, seqused_k=256,
+              q_batch_stride=4096, q_row_stride=4096, q_head_stride=128,
+              k_batch_stride=8192 * 1024, k_row_stride=1024, k_head_stride=128,
+              v_batch_stride=8192 * 1024, v_row_stride=1024, v_head_stride=128,
+              o_batch_stride=4096, o_row_stride=4096, o_head_stride=128, lse_batch_stride=32, lse_head_stride=1, causal=1)
+    rc, pl = _plan(_params(**kw))
+    assert rc == 0 and pl.kernel == L.KERNEL_DECODE
+    assert pl.num_splits == 4 and pl.grid in (148, 296) and pl.launches == 2 and pl.workspace_bytes > 0
+    rc, pl = _plan(_params(num_splits=2, **kw))
+    assert rc == 0 and pl.num_splits == 2 and pl.grid == 64 * 8 * 2
+    rc, pl = _plan(_params(window_left=1024, window_right=0, **kw))
+    assert rc == 0 and pl.kernel == L.KERNEL_DECODE and pl.grid % (64 * 8) == 0  # plain grid: units x splits
