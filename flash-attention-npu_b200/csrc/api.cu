@@ -22,6 +22,9 @@ namespace fa {
 static thread_local std::string g_err;
 static std::atomic<long long> g_launches{0};  // kernel launches issued so far (fa_b200_launch_count)
 
+static int fail(int code, const std::string& msg);
+int fail_bwd(int code, const std::string& msg) { return fail(code, msg); }  // for bwd.cu
+void count_launches(int n) { g_launches += n; }
 static int fail(int code, const std::string& msg) {
   g_err = msg;
   return code;

@@ -72,9 +72,34 @@ def fwd_kvcache(q, kcache, vcache, k_, v_, seqlens_k_, rotary_cos_, rotary_sin_,
     return [out, lse]
 
 
-def bwd(*args, **kwargs):
-    raise NotImplementedError("the B200 backend implements the forward pass only")
+def _check_bwd_features(alibi_slopes_, p_dropout, softcap):
+    if p_dropout != 0.0:
+        raise RuntimeError("NPU FlashAttention does not support dropout")
+    if alibi_slopes_ is not None:
+        raise RuntimeError("the backward does not support alibi_slopes")
+    if softcap != 0.0:
+        raise RuntimeError("the backward does not support softcap")
 
 
-def varlen_bwd(*args, **kwargs):
-    raise NotImplementedError("the B200 backend implements the forward pass only")
+def bwd(dout, q, k, v, out, softmax_lse, dq_, dk_, dv_, alibi_slopes_, p_dropout, softmax_scale, is_causal,
+        window_size_left, window_size_right, softcap, deterministic, gen_=None, rng_state=None):
+    """Backward of ``fwd`` (argument order of the reference's pybind ``bwd``,
+    flash_attn_npu_v2/interface_arch22.py:232-252).  Returns [dq, dk, dv, softmax_d]."""
+    _check_bwd_features(alibi_slopes_, p_dropout, softcap)
+    dq, dk, dv = ops.attention_backward(dout, q, k, v, out, softmax_lse, dq=dq_, dk=dk_, dv=dv_,
+                                        softmax_scale=softmax_scale, causal=is_causal,
+                                        window_left=window_size_left, window_right=window_size_right)
+    return [dq, dk, dv, torch.empty(0, dtype=torch.float32, device=q.device)]
+
+
+def varlen_bwd(dout, q, k, v, out, softmax_lse, dq_, dk_, dv_, cu_seqlens_q, cu_seqlens_k, alibi_slopes_, max_seqlen_q,
+               max_seqlen_k, p_dropout, softmax_scale, zero_tensors, is_causal, window_size_left, window_size_right,
+               softcap, deterministic, gen_=None, rng_state=None):
+    """Backward of ``varlen_fwd`` (argument order of the reference's pybind ``varlen_bwd``)."""
+    _check_bwd_features(alibi_slopes_, p_dropout, softcap)
+    dq, dk, dv = ops.attention_backward(dout, q, k, v, out, softmax_lse, dq=dq_, dk=dk_, dv=dv_,
+                                        softmax_scale=softmax_scale, causal=is_causal,
+                                        window_left=window_size_left, window_right=window_size_right,
+                                        cu_seqlens_q=cu_seqlens_q, cu_seqlens_k=cu_seqlens_k,
+                                        max_seqlen_q=max_seqlen_q, max_seqlen_k=max_seqlen_k)
+    return [dq, dk, dv, torch.empty(0, dtype=torch.float32, device=q.device)]

@@ -5,8 +5,9 @@ flash_attn_npu_v2/interface_arch22.py of the reference (:965-1573); the native c
 ``flash_attn_npu_arch22_v2`` (here a ctypes-backed module over libfa_b200.so) positionally,
 exactly as the reference calls its pybind extension (:61-75, :1551-1572).
 
-Forward only: tensors that require grad are accepted, but no autograd graph is recorded
-(the reference's backward kernels are outside this backend).
+``flash_attn_func`` and ``flash_attn_varlen_func`` (and their packed variants) are differentiable:
+autograd Functions with the structure of the reference's (:774-824, :827-900), whose backward
+calls ``bwd`` / ``varlen_bwd`` of the extension.  The KV-cache entry point is inference only.
 """
 from __future__ import annotations
 
@@ -34,18 +35,74 @@ def _check_dropout(dropout_p):
         raise RuntimeError("NPU FlashAttention does not support dropout")
 
 
+class FlashAttnFunc(torch.autograd.Function):
+    """Dense attention with a backward (structure of the reference's FlashAttnFunc, :774-900)."""
+
+    @staticmethod
+    def forward(ctx, q, k, v, dropout_p, softmax_scale, causal, window_size, softcap, alibi_slopes, deterministic,
+                return_softmax):
+        d = q.size(3)
+        qp, kp, vp = _pad_head([maybe_contiguous(x) for x in (q, k, v)], d)
+        out_padded, lse, s_dmask, _ = _ext.fwd(qp, kp, vp, None, alibi_slopes, dropout_p, softmax_scale, causal,
+                                               window_size[0], window_size[1], softcap, False, None)
+        if any(t.requires_grad for t in (q, k, v)):
+            ctx.save_for_backward(qp, kp, vp, out_padded, lse)
+            ctx.args = (dropout_p, softmax_scale, causal, window_size, softcap, alibi_slopes, deterministic, d)
+        out = out_padded[..., :d]
+        ctx.mark_non_differentiable(lse, s_dmask)
+        return out, lse, s_dmask
+
+    @staticmethod
+    def backward(ctx, dout, *unused):
+        q, k, v, out, lse = ctx.saved_tensors
+        dropout_p, softmax_scale, causal, window_size, softcap, alibi_slopes, deterministic, d = ctx.args
+        dout_padded = _pad_head([maybe_contiguous(dout)], d)[0]
+        dq, dk, dv, _ = _ext.bwd(dout_padded, q, k, v, out, lse, None, None, None, alibi_slopes, dropout_p,
+                                 softmax_scale, causal, window_size[0], window_size[1], softcap, deterministic, None, None)
+        return dq[..., :d], dk[..., :d], dv[..., :d], None, None, None, None, None, None, None, None
+
+
+class FlashAttnVarlenFunc(torch.autograd.Function):
+    """Packed varlen attention with a backward (the reference's FlashAttnVarlenFunc)."""
+
+    @staticmethod
+    def forward(ctx, q, k, v, cu_seqlens_q, cu_seqlens_k, max_seqlen_q, max_seqlen_k, dropout_p, softmax_scale, causal,
+                window_size, softcap, alibi_slopes, deterministic, block_table):
+        d = q.size(2)
+        qp, kp, vp = _pad_head([maybe_contiguous(x) for x in (q, k, v)], d)
+        out_padded, lse, s_dmask, _ = _ext.varlen_fwd(qp, kp, vp, None, cu_seqlens_q, cu_seqlens_k, None, None,
+                                                      block_table, alibi_slopes, max_seqlen_q, max_seqlen_k, dropout_p,
+                                                      softmax_scale, False, causal, window_size[0], window_size[1],
+                                                      softcap, False, None)
+        if any(t.requires_grad for t in (q, k, v)):
+            ctx.save_for_backward(qp, kp, vp, out_padded, lse, cu_seqlens_q, cu_seqlens_k)
+            ctx.args = (max_seqlen_q, max_seqlen_k, dropout_p, softmax_scale, causal, window_size, softcap,
+                        alibi_slopes, deterministic, d)
+        out = out_padded[..., :d]
+        ctx.mark_non_differentiable(lse, s_dmask)
+        return out, lse, s_dmask
+
+    @staticmethod
+    def backward(ctx, dout, *unused):
+        q, k, v, out, lse, cu_seqlens_q, cu_seqlens_k = ctx.saved_tensors
+        (max_seqlen_q, max_seqlen_k, dropout_p, softmax_scale, causal, window_size, softcap, alibi_slopes, deterministic,
+         d) = ctx.args
+        dout_padded = _pad_head([maybe_contiguous(dout)], d)[0]
+        dq, dk, dv, _ = _ext.varlen_bwd(dout_padded, q, k, v, out, lse, None, None, None, cu_seqlens_q, cu_seqlens_k,
+                                        alibi_slopes, max_seqlen_q, max_seqlen_k, dropout_p, softmax_scale, False, causal,
+                                        window_size[0], window_size[1], softcap, deterministic, None, None)
+        return (dq[..., :d], dk[..., :d], dv[..., :d]) + (None,) * 12
+
+
 def flash_attn_func(q, k, v, dropout_p=0.0, softmax_scale=None, causal=False, window_size=(-1, -1), softcap=0.0,
                     alibi_slopes=None, deterministic=False, return_attn_probs=False):
     """q (b, s_q, h, d), k / v (b, s_k, h_k, d) -> out (b, s_q, h, d)
-    or (out, softmax_lse (b, h, s_q) fp32, S_dmask (empty)) when return_attn_probs."""
+    or (out, softmax_lse (b, h, s_q) fp32, S_dmask (empty)) when return_attn_probs.  Differentiable in q, k, v."""
     _check_dropout(dropout_p)
     if softmax_scale is None:
         softmax_scale = q.shape[-1] ** (-0.5)
-    d = q.size(3)
-    q, k, v = _pad_head([maybe_contiguous(x) for x in (q, k, v)], d)
-    out, lse, s_dmask, _ = _ext.fwd(q, k, v, None, alibi_slopes, dropout_p, softmax_scale, causal,
-                                    window_size[0], window_size[1], softcap, False, None)
-    out = out[..., :d]
+    out, lse, s_dmask = FlashAttnFunc.apply(q, k, v, dropout_p, softmax_scale, causal, tuple(window_size), softcap,
+                                            alibi_slopes, deterministic, return_attn_probs)
     return (out, lse, s_dmask) if return_attn_probs else out
 
 
@@ -71,12 +128,9 @@ def flash_attn_varlen_func(q, k, v, cu_seqlens_q, cu_seqlens_k, max_seqlen_q, ma
     _check_dropout(dropout_p)
     if softmax_scale is None:
         softmax_scale = q.shape[-1] ** (-0.5)
-    d = q.size(2)
-    q, k, v = _pad_head([maybe_contiguous(x) for x in (q, k, v)], d)
-    out, lse, s_dmask, _ = _ext.varlen_fwd(q, k, v, None, cu_seqlens_q, cu_seqlens_k, None, None, block_table,
-                                           alibi_slopes, max_seqlen_q, max_seqlen_k, dropout_p, softmax_scale,
-                                           False, causal, window_size[0], window_size[1], softcap, False, None)
-    out = out[..., :d]
+    out, lse, s_dmask = FlashAttnVarlenFunc.apply(q, k, v, cu_seqlens_q, cu_seqlens_k, max_seqlen_q, max_seqlen_k,
+                                                  dropout_p, softmax_scale, causal, tuple(window_size), softcap,
+                                                  alibi_slopes, deterministic, block_table)
     return (out, lse, s_dmask) if return_attn_probs else out
 
 

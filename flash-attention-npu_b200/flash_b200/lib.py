@@ -67,11 +67,23 @@ class CombineParams(C.Structure):
     )
 
 
+class BwdParams(C.Structure):
+    """Mirror of ``fa_bwd_params``."""
+    _fields_ = (
+        [(n, _p) for n in ("q", "k", "v", "o", "dout", "lse", "dq", "dk", "dv", "cu_seqlens_q", "cu_seqlens_k")]
+        + [(f"{t}_{s}_stride", _i64) for t in ("q", "k", "v", "o", "do", "dq", "dk", "dv") for s in ("batch", "row", "head")]
+        + [("lse_batch_stride", _i64), ("lse_head_stride", _i64)]
+        + [(n, _i32) for n in ("b", "seqlen_q", "seqlen_k", "h", "h_k", "d", "total_q", "dtype", "causal",
+                               "window_left", "window_right")]
+        + [("softmax_scale", C.c_float)]
+    )
+
+
 # every symbol include/fa_b200.h declares
 EXPORTS = (
     "fa_b200_fwd", "fa_b200_fwd_noalloc", "fa_b200_fwd_plan", "fa_b200_combine", "fa_b200_normalize_window",
     "fa_b200_check_status", "fa_b200_last_error", "fa_b200_status_string", "fa_b200_abi_version",
-    "fa_b200_launch_count",
+    "fa_b200_launch_count", "fa_b200_bwd", "fa_b200_bwd_workspace_bytes",
 )
 
 _lib = None
@@ -92,6 +104,10 @@ def load() -> C.CDLL:
     lib.fa_b200_fwd_noalloc.restype = C.c_int
     lib.fa_b200_fwd_plan.argtypes = [C.POINTER(FwdParams), C.POINTER(FwdPlan)]
     lib.fa_b200_fwd_plan.restype = C.c_int
+    lib.fa_b200_bwd.argtypes = [C.POINTER(BwdParams), _p, C.c_size_t, _p]
+    lib.fa_b200_bwd.restype = C.c_int
+    lib.fa_b200_bwd_workspace_bytes.argtypes = [C.POINTER(BwdParams)]
+    lib.fa_b200_bwd_workspace_bytes.restype = C.c_size_t
     lib.fa_b200_combine.argtypes = [C.POINTER(CombineParams), _p]
     lib.fa_b200_combine.restype = C.c_int
     lib.fa_b200_normalize_window.argtypes = [_i32, _i32, _i32] + [C.POINTER(_i32)] * 4

@@ -220,3 +220,65 @@ def combine(o_partial: torch.Tensor, lse_partial: torch.Tensor, out: Optional[to
     with torch.cuda.device(o_partial.device):
         L.check(lib.fa_b200_combine(C.byref(c), torch.cuda.current_stream(o_partial.device).cuda_stream))
     return out, lse
+
+
+def attention_backward(dout, q, k, v, out, lse, *, dq=None, dk=None, dv=None, softmax_scale=None, causal=False,
+                       window_left=-1, window_right=-1, cu_seqlens_q=None, cu_seqlens_k=None, max_seqlen_q=None,
+                       max_seqlen_k=None):
+    """dQ, dK, dV of ``attention_forward`` (dense (b, s, h, d) or packed varlen (total, h, d) tensors) from
+    the forward's ``out`` and ``lse``.  Head dim a multiple of 8, at most 128; no dropout / softcap / alibi."""
+    lib = L.load()
+    ts = (dout, q, k, v, out)
+    if not all(t.is_cuda for t in ts) or not lse.is_cuda:
+        raise RuntimeError("flash_b200 runs on CUDA tensors only (there is no CPU implementation)")
+    if any(t.dtype != q.dtype for t in ts):
+        raise RuntimeError("dout, q, k, v and out must have the same dtype")
+    if lse.dtype != torch.float32 or not lse.is_contiguous():
+        raise RuntimeError("softmax_lse must be a contiguous fp32 tensor")
+    dout, q, k, v, out = [t if t.stride(-1) == 1 else t.contiguous() for t in ts]
+    varlen = cu_seqlens_q is not None
+    _check_i32(cu_seqlens_q, "cu_seqlens_q")
+    _check_i32(cu_seqlens_k, "cu_seqlens_k")
+    dq = torch.empty_like(q) if dq is None else dq
+    dk = torch.empty_like(k) if dk is None else dk
+    dv = torch.empty_like(v) if dv is None else dv
+    for name, t, ref in (("dq", dq, q), ("dk", dk, k), ("dv", dv, v)):
+        if t.shape != ref.shape or t.dtype != ref.dtype or t.stride(-1) != 1 or not t.is_cuda:
+            raise RuntimeError(f"{name} must have the shape, dtype and device of its input and a contiguous last dimension")
+    p = L.BwdParams()
+    p.q, p.k, p.v, p.o, p.dout, p.lse = _ptr(q), _ptr(k), _ptr(v), _ptr(out), _ptr(dout), _ptr(lse)
+    p.dq, p.dk, p.dv = _ptr(dq), _ptr(dk), _ptr(dv)
+    p.cu_seqlens_q, p.cu_seqlens_k = _ptr(cu_seqlens_q), _ptr(cu_seqlens_k)
+    for name, t in (("q", q), ("k", k), ("v", v), ("o", out), ("do", dout), ("dq", dq), ("dk", dk), ("dv", dv)):
+        if varlen:
+            bs, rs, hs = 0, t.stride(0), t.stride(1)
+        else:
+            bs, rs, hs = t.stride(0), t.stride(1), t.stride(2)
+        setattr(p, f"{name}_batch_stride", bs)
+        setattr(p, f"{name}_row_stride", rs)
+        setattr(p, f"{name}_head_stride", hs)
+    if varlen:
+        if cu_seqlens_k is None or max_seqlen_q is None or max_seqlen_k is None:
+            raise RuntimeError("varlen backward needs cu_seqlens_k, max_seqlen_q and max_seqlen_k")
+        total_q, h, d = q.shape
+        h_k = k.shape[1]
+        p.b, p.seqlen_q, p.seqlen_k, p.total_q = cu_seqlens_q.numel() - 1, int(max_seqlen_q), int(max_seqlen_k), total_q
+        p.lse_batch_stride, p.lse_head_stride = 0, lse.stride(0)
+        if tuple(lse.shape) != (h, total_q):
+            raise RuntimeError("softmax_lse must be (nheads, total_q)")
+    else:
+        b, s_q, h, d = q.shape
+        h_k = k.shape[2]
+        p.b, p.seqlen_q, p.seqlen_k, p.total_q = b, s_q, k.shape[1], b * s_q
+        p.lse_batch_stride, p.lse_head_stride = lse.stride(0), lse.stride(1)
+        if tuple(lse.shape) != (b, h, s_q):
+            raise RuntimeError("softmax_lse must be (batch, nheads, seqlen_q)")
+    p.h, p.h_k, p.d = h, h_k, d
+    p.dtype, p.causal = _dtype_code(q), int(bool(causal))
+    p.window_left, p.window_right = int(window_left), int(window_right)
+    p.softmax_scale = float(softmax_scale if softmax_scale is not None else d ** -0.5)
+    with torch.cuda.device(q.device):
+        nbytes = lib.fa_b200_bwd_workspace_bytes(C.byref(p))
+        ws = torch.empty(max(nbytes, 16), dtype=torch.uint8, device=q.device)
+        L.check(lib.fa_b200_bwd(C.byref(p), _ptr(ws), nbytes, torch.cuda.current_stream(q.device).cuda_stream))
+    return dq, dk, dv

@@ -163,6 +163,46 @@ int fa_b200_fwd_noalloc(const fa_fwd_params* p, void* stream);
  * p->num_sm > 0. */
 int fa_b200_fwd_plan(const fa_fwd_params* p, fa_fwd_plan* plan);
 
+/* ------------------------------------------------------------------------------------------------
+ * Backward (dQ, dK, dV) of the dense / packed-varlen forward.  Replaces the reference's mha_bwd /
+ * mha_varlen_bwd (pybind names bwd, varlen_bwd: csrc/arch22/flash_attn_npu_v2/flash_api.cpp:1301-1309;
+ * called from flash_attn_npu_v2/interface_arch22.py:232-252); arithmetic of the reference's golden
+ * tests/fa_small_op_golden.py:160-353.  No dropout, softcap or alibi (refused by the Python layer).
+ * Head dims up to 128 (multiples of 8).  All tensors as in fa_fwd_params: device pointers, element
+ * strides, last dimension contiguous; dq / dk / dv are written completely.
+ * ------------------------------------------------------------------------------------------------ */
+typedef struct fa_bwd_params {
+  const void* q;     /* (b, s_q, h, d) or (total_q, h, d) */
+  const void* k;     /* (b, s_k, h_k, d) or (total_k, h_k, d) */
+  const void* v;
+  const void* o;     /* forward output, layout of q */
+  const void* dout;  /* gradient of o */
+  const float* lse;  /* forward softmax_lse, contiguous (b, h, s_q) / (h, total_q) */
+  void* dq;
+  void* dk;
+  void* dv;
+  const int32_t* cu_seqlens_q; /* (b + 1) or NULL */
+  const int32_t* cu_seqlens_k;
+  int64_t q_batch_stride, q_row_stride, q_head_stride;
+  int64_t k_batch_stride, k_row_stride, k_head_stride;
+  int64_t v_batch_stride, v_row_stride, v_head_stride;
+  int64_t o_batch_stride, o_row_stride, o_head_stride;
+  int64_t do_batch_stride, do_row_stride, do_head_stride;
+  int64_t dq_batch_stride, dq_row_stride, dq_head_stride;
+  int64_t dk_batch_stride, dk_row_stride, dk_head_stride;
+  int64_t dv_batch_stride, dv_row_stride, dv_head_stride;
+  int64_t lse_batch_stride, lse_head_stride;
+  int32_t b, seqlen_q, seqlen_k; /* max_seqlen_q / max_seqlen_k for varlen */
+  int32_t h, h_k, d, total_q;
+  int32_t dtype, causal, window_left, window_right;
+  float softmax_scale;
+} fa_bwd_params;
+
+/* Bytes of device scratch fa_b200_bwd needs (fp32 dQ accumulator + rowsum(dO o O)). */
+size_t fa_b200_bwd_workspace_bytes(const fa_bwd_params* p);
+/* Three launches on `stream` (plus a memset of the accumulator): rowsum, main kernel, dQ conversion. */
+int fa_b200_bwd(const fa_bwd_params* p, void* workspace, size_t workspace_bytes, void* stream);
+
 /* Merge of split partials (also used across GPUs). */
 int fa_b200_combine(const fa_combine_params* p, void* stream);
 
