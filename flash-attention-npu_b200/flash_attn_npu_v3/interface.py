@@ -5,7 +5,8 @@ flash_attn_npu_v3/interface_arch22.py of the reference (:797-1138); every call f
 single positional ``flash_attn_npu_arch22_v3.fwd`` exactly like the reference (:63-154).
 Arguments the backend does not implement (qv, *_descale, attention_chunk, seqused_q,
 cu_seqlens_k_new, rotary_seqlens, cache_leftpad) must keep their defaults, as in the reference
-(csrc/arch22/flash_attn_npu_v3/flash_api.cpp:150-162).  Forward only.
+(csrc/arch22/flash_attn_npu_v3/flash_api.cpp:150-162).  ``flash_attn_func`` and
+``flash_attn_varlen_func`` are differentiable (backward through ``flash_attn_npu_arch22_v3.bwd``).
 """
 from __future__ import annotations
 
@@ -45,6 +46,37 @@ def _forward(q, k, v, k_new=None, v_new=None, qv=None, out_=None, cu_seqlens_q=N
     return out[..., :d], lse, out_accum, lse_accum
 
 
+class _AttnFunc(torch.autograd.Function):
+    """Dense / packed-varlen attention with a backward (the reference's FlashAttnFunc / FlashAttnVarlenFunc of v3)."""
+
+    @staticmethod
+    def forward(ctx, q, k, v, kw):
+        out, lse, _, _ = _forward(q, k, v, **kw)
+        if any(t.requires_grad for t in (q, k, v)):
+            d = q.shape[-1]
+            pad = (8 - d % 8) % 8
+            qp, kp, vp = [maybe_contiguous(t) if pad == 0 else torch.nn.functional.pad(maybe_contiguous(t), [0, pad])
+                          for t in (q, k, v)]
+            op = out if pad == 0 else torch.nn.functional.pad(out, [0, pad])
+            ctx.save_for_backward(qp, kp, vp, op, lse, kw.get("cu_seqlens_q"), kw.get("cu_seqlens_k"))
+            ctx.kw, ctx.d = kw, d
+        ctx.mark_non_differentiable(lse)
+        return out, lse
+
+    @staticmethod
+    def backward(ctx, dout, *unused):
+        q, k, v, out, lse, cu_q, cu_k = ctx.saved_tensors
+        kw, d = ctx.kw, ctx.d
+        dout = maybe_contiguous(dout)
+        if q.shape[-1] != d:
+            dout = torch.nn.functional.pad(dout, [0, q.shape[-1] - d])
+        dq, dk, dv, _ = _ext.bwd(dout, q, k, v, out.contiguous(), lse, None, None, None, cu_q, cu_k, kw.get("seqused_q"),
+                                 kw.get("seqused_k"), kw.get("max_seqlen_q"), kw.get("max_seqlen_k"),
+                                 kw.get("softmax_scale"), kw.get("causal", False), kw.get("window_size_left", -1),
+                                 kw.get("window_size_right", -1), kw.get("softcap", 0.0), False, kw.get("sm_margin", 0))
+        return dq[..., :d], dk[..., :d], dv[..., :d], None
+
+
 def _default_scale(q, qv):
     return (q.shape[-1] + (qv.shape[-1] if qv is not None else 0)) ** (-0.5)
 
@@ -55,11 +87,11 @@ def flash_attn_func(q, k, v, softmax_scale=None, causal=False, qv=None, q_descal
     """q (b, s_q, h, d), k / v (b, s_k, h_k, d) -> out, or (out, softmax_lse (b, h, s_q))."""
     if softmax_scale is None:
         softmax_scale = _default_scale(q, qv)
-    out, lse, *_ = _forward(q, k, v, qv=qv, q_descale=q_descale, k_descale=k_descale, v_descale=v_descale,
-                            softmax_scale=softmax_scale, causal=causal, window_size_left=window_size[0],
-                            window_size_right=window_size[1], attention_chunk=attention_chunk, softcap=softcap,
-                            scheduler_metadata=scheduler_metadata, num_splits=num_splits, pack_gqa=pack_gqa,
-                            sm_margin=sm_margin)
+    out, lse = _AttnFunc.apply(q, k, v, dict(
+        qv=qv, q_descale=q_descale, k_descale=k_descale, v_descale=v_descale, softmax_scale=softmax_scale, causal=causal,
+        window_size_left=window_size[0], window_size_right=window_size[1], attention_chunk=attention_chunk,
+        softcap=softcap, scheduler_metadata=scheduler_metadata, num_splits=num_splits, pack_gqa=pack_gqa,
+        sm_margin=sm_margin))
     return (out, lse) if return_attn_probs else out
 
 
@@ -84,13 +116,12 @@ def flash_attn_varlen_func(q, k, v, cu_seqlens_q, cu_seqlens_k, max_seqlen_q, ma
     """q (total_q, h, d), k / v (total_k, h_k, d) -> out, or (out, softmax_lse (h, total_q))."""
     if softmax_scale is None:
         softmax_scale = _default_scale(q, qv)
-    out, lse, *_ = _forward(q, k, v, qv=qv, cu_seqlens_q=cu_seqlens_q, cu_seqlens_k=cu_seqlens_k,
-                            seqused_q=seqused_q, seqused_k=seqused_k, max_seqlen_q=max_seqlen_q,
-                            max_seqlen_k=max_seqlen_k, q_descale=q_descale, k_descale=k_descale, v_descale=v_descale,
-                            softmax_scale=softmax_scale, causal=causal, window_size_left=window_size[0],
-                            window_size_right=window_size[1], attention_chunk=attention_chunk, softcap=softcap,
-                            scheduler_metadata=scheduler_metadata, num_splits=num_splits, pack_gqa=pack_gqa,
-                            sm_margin=sm_margin)
+    out, lse = _AttnFunc.apply(q, k, v, dict(
+        qv=qv, cu_seqlens_q=cu_seqlens_q, cu_seqlens_k=cu_seqlens_k, seqused_q=seqused_q, seqused_k=seqused_k,
+        max_seqlen_q=max_seqlen_q, max_seqlen_k=max_seqlen_k, q_descale=q_descale, k_descale=k_descale,
+        v_descale=v_descale, softmax_scale=softmax_scale, causal=causal, window_size_left=window_size[0],
+        window_size_right=window_size[1], attention_chunk=attention_chunk, softcap=softcap,
+        scheduler_metadata=scheduler_metadata, num_splits=num_splits, pack_gqa=pack_gqa, sm_margin=sm_margin))
     return (out, lse) if return_attn_probs else out
 
 
