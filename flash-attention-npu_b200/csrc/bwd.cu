@@ -45,6 +45,7 @@ int fa_b200_bwd(const fa_bwd_params* a, void* workspace, size_t workspace_bytes,
     return fail_bwd(FA_ERR_INVALID, "Number of heads in key/value must divide number of heads in query");
   if (a->d <= 0 || a->d % 8 != 0) return fail_bwd(FA_ERR_INVALID, "head dimension must be a multiple of 8 (pad it on the caller side)");
   if (a->d > 128) return fail_bwd(FA_ERR_UNSUPPORTED, "the backward covers head dimensions up to 128");
+  if (a->softcap < 0.f) return fail_bwd(FA_ERR_INVALID, "softcap must be non-negative (0.0 disables softcap)");
   if ((a->cu_seqlens_q != nullptr) != (a->cu_seqlens_k != nullptr))
     return fail_bwd(FA_ERR_INVALID, "cu_seqlens_q and cu_seqlens_k must be passed together");
   const bool varlen = a->cu_seqlens_q != nullptr;
@@ -95,6 +96,7 @@ int fa_b200_bwd(const fa_bwd_params* a, void* workspace, size_t workspace_bytes,
   p.wl = wl; p.wr = wr;
   p.softmax_scale = a->softmax_scale;
   p.scale_log2 = a->softmax_scale * kLog2e;
+  p.softcap = a->softcap;
   const size_t acc_bytes = align16((size_t)rows * a->h * p.d_pad * sizeof(float));
   p.dq_accum = reinterpret_cast<float*>(workspace);
   p.delta = reinterpret_cast<float*>(reinterpret_cast<char*>(workspace) + acc_bytes);

@@ -6,6 +6,7 @@
 //   P  = exp(S * scale - LSE)            with the forward's own LSE, masked entries 0
 //   dV = P^T dO        dP = dO V^T       D_i = sum_d dO_id O_id  (= rowsum(dP o P))
 //   dS = P o (dP - D) * scale            dQ = dS K        dK = dS^T Q
+// (with softcap: S' = c tanh(S scale / c) replaces S scale, and dS gets the factor 1 - tanh^2)
 // P and dS are rounded to the input dtype before the second matmuls (as the tensor cores need),
 // all accumulation is fp32.
 //
@@ -38,6 +39,7 @@ struct BwdParams {
   int32_t b, seqlen_q, seqlen_k, h, h_k, d, d_pad, total_q;
   int32_t is_causal, is_local, wl, wr;
   float softmax_scale, scale_log2;
+  float softcap;  // 0 = off; scores become softcap * tanh(S * scale / softcap) (tests/fa_small_op_golden.py:80-89,124-125)
 };
 
 constexpr int kBwdBM = 64, kBwdBN = 64, kBwdThreads = 128;
@@ -228,10 +230,18 @@ __global__ void __launch_bounds__(kBwdThreads) bwd_kernel(const __grid_constant_
 #pragma unroll
           for (int e = 0; e < 2; ++e) {
             const int j = key0 + nt * 8 + 2 * t4 + e;
-            float pv = 0.f;
-            if (j >= lo && j <= hi) pv = fast_exp2(s_acc[nt][hf * 2 + e] * p.scale_log2 - lse2);
+            float pv = 0.f, fac = p.softmax_scale;
+            if (j >= lo && j <= hi) {
+              if (p.softcap > 0.f) {  // d/dS of softcap * tanh(S * scale / softcap) = scale * (1 - tanh^2)
+                const float th = tanhf(s_acc[nt][hf * 2 + e] * p.softmax_scale / p.softcap);
+                pv = fast_exp2(p.softcap * th * kLog2e - lse2);
+                fac = p.softmax_scale * (1.f - th * th);
+              } else {
+                pv = fast_exp2(s_acc[nt][hf * 2 + e] * p.scale_log2 - lse2);
+              }
+            }
             s_acc[nt][hf * 2 + e] = pv;
-            dp_acc[nt][hf * 2 + e] = pv * (dp_acc[nt][hf * 2 + e] - dl) * p.softmax_scale;
+            dp_acc[nt][hf * 2 + e] = pv * (dp_acc[nt][hf * 2 + e] - dl) * fac;
           }
           const uint32_t off = r * S::PPITCH + (nt * 8 + 2 * t4) * 2;
           *reinterpret_cast<uint32_t*>(smem + S::P_OFF + off) = pack2<T>(s_acc[nt][hf * 2], s_acc[nt][hf * 2 + 1]);

@@ -77,8 +77,6 @@ def _check_bwd_features(alibi_slopes_, p_dropout, softcap):
         raise RuntimeError("NPU FlashAttention does not support dropout")
     if alibi_slopes_ is not None:
         raise RuntimeError("the backward does not support alibi_slopes")
-    if softcap != 0.0:
-        raise RuntimeError("the backward does not support softcap")
 
 
 def bwd(dout, q, k, v, out, softmax_lse, dq_, dk_, dv_, alibi_slopes_, p_dropout, softmax_scale, is_causal,
@@ -88,7 +86,7 @@ def bwd(dout, q, k, v, out, softmax_lse, dq_, dk_, dv_, alibi_slopes_, p_dropout
     _check_bwd_features(alibi_slopes_, p_dropout, softcap)
     dq, dk, dv = ops.attention_backward(dout, q, k, v, out, softmax_lse, dq=dq_, dk=dk_, dv=dv_,
                                         softmax_scale=softmax_scale, causal=is_causal,
-                                        window_left=window_size_left, window_right=window_size_right)
+                                        window_left=window_size_left, window_right=window_size_right, softcap=softcap)
     return [dq, dk, dv, torch.empty(0, dtype=torch.float32, device=q.device)]
 
 
@@ -99,7 +97,7 @@ def varlen_bwd(dout, q, k, v, out, softmax_lse, dq_, dk_, dv_, cu_seqlens_q, cu_
     _check_bwd_features(alibi_slopes_, p_dropout, softcap)
     dq, dk, dv = ops.attention_backward(dout, q, k, v, out, softmax_lse, dq=dq_, dk=dk_, dv=dv_,
                                         softmax_scale=softmax_scale, causal=is_causal,
-                                        window_left=window_size_left, window_right=window_size_right,
+                                        window_left=window_size_left, window_right=window_size_right, softcap=softcap,
                                         cu_seqlens_q=cu_seqlens_q, cu_seqlens_k=cu_seqlens_k,
                                         max_seqlen_q=max_seqlen_q, max_seqlen_k=max_seqlen_k)
     return [dq, dk, dv, torch.empty(0, dtype=torch.float32, device=q.device)]

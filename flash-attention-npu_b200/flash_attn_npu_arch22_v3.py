@@ -116,11 +116,10 @@ def bwd(dout, q, k, v, out, softmax_lse, dq_, dk_, dv_, cu_seqlens_q_, cu_seqlen
     """Backward of ``fwd`` for dense or packed-varlen q / k / v (argument order of the reference's pybind ``bwd``,
     flash_attn_npu_v3/interface_arch22.py:294-317).  Returns [dq, dk, dv, softmax_d]."""
     _reject(seqused_q_ is not None or seqused_k_ is not None, "the backward does not support seqused_q / seqused_k")
-    _reject(softcap != 0.0, "the backward does not support softcap")
     if softmax_scale is None:
         softmax_scale = q.shape[-1] ** (-0.5)
     dq, dk, dv = ops.attention_backward(dout, q, k, v, out, softmax_lse, dq=dq_, dk=dk_, dv=dv_,
                                         softmax_scale=softmax_scale, causal=is_causal, window_left=window_size_left,
-                                        window_right=window_size_right, cu_seqlens_q=cu_seqlens_q_,
+                                        window_right=window_size_right, softcap=softcap, cu_seqlens_q=cu_seqlens_q_,
                                         cu_seqlens_k=cu_seqlens_k_, max_seqlen_q=max_seqlen_q_, max_seqlen_k=max_seqlen_k_)
     return [dq, dk, dv, torch.empty(0, dtype=torch.float32, device=q.device)]

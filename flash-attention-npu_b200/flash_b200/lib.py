@@ -75,7 +75,7 @@ class BwdParams(C.Structure):
         + [("lse_batch_stride", _i64), ("lse_head_stride", _i64)]
         + [(n, _i32) for n in ("b", "seqlen_q", "seqlen_k", "h", "h_k", "d", "total_q", "dtype", "causal",
                                "window_left", "window_right")]
-        + [("softmax_scale", C.c_float)]
+        + [("softmax_scale", C.c_float), ("softcap", C.c_float)]
     )
 
 

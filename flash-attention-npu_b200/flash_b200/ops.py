@@ -223,10 +223,10 @@ def combine(o_partial: torch.Tensor, lse_partial: torch.Tensor, out: Optional[to
 
 
 def attention_backward(dout, q, k, v, out, lse, *, dq=None, dk=None, dv=None, softmax_scale=None, causal=False,
-                       window_left=-1, window_right=-1, cu_seqlens_q=None, cu_seqlens_k=None, max_seqlen_q=None,
-                       max_seqlen_k=None):
+                       window_left=-1, window_right=-1, softcap=0.0, cu_seqlens_q=None, cu_seqlens_k=None,
+                       max_seqlen_q=None, max_seqlen_k=None):
     """dQ, dK, dV of ``attention_forward`` (dense (b, s, h, d) or packed varlen (total, h, d) tensors) from
-    the forward's ``out`` and ``lse``.  Head dim a multiple of 8, at most 128; no dropout / softcap / alibi."""
+    the forward's ``out`` and ``lse``.  Head dim a multiple of 8, at most 128; no dropout / alibi."""
     lib = L.load()
     ts = (dout, q, k, v, out)
     if not all(t.is_cuda for t in ts) or not lse.is_cuda:
@@ -277,6 +277,7 @@ def attention_backward(dout, q, k, v, out, lse, *, dq=None, dk=None, dv=None, so
     p.dtype, p.causal = _dtype_code(q), int(bool(causal))
     p.window_left, p.window_right = int(window_left), int(window_right)
     p.softmax_scale = float(softmax_scale if softmax_scale is not None else d ** -0.5)
+    p.softcap = float(softcap)
     with torch.cuda.device(q.device):
         nbytes = lib.fa_b200_bwd_workspace_bytes(C.byref(p))
         ws = torch.empty(max(nbytes, 16), dtype=torch.uint8, device=q.device)

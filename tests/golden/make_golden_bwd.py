@@ -35,11 +35,12 @@ def rand(shape, dtype, g):
 
 
 CASES = [
-    # name, dtype, varlen lens (or None), b, s_q, s_k, h, h_k, d, causal, window
-    ("bsnd_causal_gqa_bf16", torch.bfloat16, None, 2, 96, 160, 4, 2, 64, True, (-1, -1)),
-    ("bsnd_full_fp16_d128", torch.float16, None, 1, 130, 70, 2, 2, 128, False, (-1, -1)),
-    ("bsnd_window_bf16", torch.bfloat16, None, 1, 128, 128, 2, 1, 64, False, (40, 10)),
-    ("tnd_causal_ragged_bf16", torch.bfloat16, ([70, 1, 130], [100, 33, 130]), 3, 130, 130, 4, 2, 64, True, (-1, -1)),
+    # name, dtype, varlen lens (or None), b, s_q, s_k, h, h_k, d, causal, window, softcap
+    ("bsnd_causal_gqa_bf16", torch.bfloat16, None, 2, 96, 160, 4, 2, 64, True, (-1, -1), 0.0),
+    ("bsnd_full_fp16_d128", torch.float16, None, 1, 130, 70, 2, 2, 128, False, (-1, -1), 0.0),
+    ("bsnd_window_bf16", torch.bfloat16, None, 1, 128, 128, 2, 1, 64, False, (40, 10), 0.0),
+    ("tnd_causal_ragged_bf16", torch.bfloat16, ([70, 1, 130], [100, 33, 130]), 3, 130, 130, 4, 2, 64, True, (-1, -1), 0.0),
+    ("bsnd_softcap_fp16", torch.float16, None, 1, 100, 100, 2, 1, 64, True, (-1, -1), 30.0),
 ]
 
 
@@ -49,14 +50,14 @@ def main(ref_root):
     spec.loader.exec_module(G)
     out_dir = os.path.join(HERE, "bwd")
     os.makedirs(out_dir, exist_ok=True)
-    for ci, (name, dtype, lens, b, s_q, s_k, h, h_k, d, causal, window) in enumerate(CASES):
+    for ci, (name, dtype, lens, b, s_q, s_k, h, h_k, d, causal, window, softcap) in enumerate(CASES):
         g = torch.Generator().manual_seed(42 + ci)
         scale = d ** -0.5
         if lens is None:
             q, k, v = rand((b, s_q, h, d), dtype, g), rand((b, s_k, h_k, d), dtype, g), rand((b, s_k, h_k, d), dtype, g)
             dout = rand((b, s_q, h, d), dtype, g)
-            out, lse = OA.flash_attn_func(q, k, v, softmax_scale=scale, causal=causal, window_size=window)
-            dq, dk, dv = G.golden_bsnd_bwd_from_fwd(q, k, v, dout, out, lse, h, h_k, scale, 0.0, 0.0, causal, window[0], window[1])
+            out, lse = OA.flash_attn_func(q, k, v, softmax_scale=scale, causal=causal, window_size=window, softcap=softcap)
+            dq, dk, dv = G.golden_bsnd_bwd_from_fwd(q, k, v, dout, out, lse, h, h_k, scale, softcap, 0.0, causal, window[0], window[1])
             extra = {}
         else:
             lq, lk = lens
@@ -65,14 +66,14 @@ def main(ref_root):
             q, k, v = rand((sum(lq), h, d), dtype, g), rand((sum(lk), h_k, d), dtype, g), rand((sum(lk), h_k, d), dtype, g)
             dout = rand((sum(lq), h, d), dtype, g)
             out, lse = OA.flash_attn_varlen_func(q, k, v, cq, ck, max(lq), max(lk), softmax_scale=scale, causal=causal,
-                                                 window_size=window)
-            dq, dk, dv = G.golden_tnd_bwd_from_fwd(q, k, v, dout, out, lse, h, h_k, lq, lk, scale, 0.0, 0.0, causal,
+                                                 window_size=window, softcap=softcap)
+            dq, dk, dv = G.golden_tnd_bwd_from_fwd(q, k, v, dout, out, lse, h, h_k, lq, lk, scale, softcap, 0.0, causal,
                                                    window[0], window[1])
             extra = {"cu_seqlens_q": cq, "cu_seqlens_k": ck}
         arrays, dtypes = {}, {}
         for key, t in dict(q=q, k=k, v=v, dout=dout, out=out, lse=lse, dq=dq, dk=dk, dv=dv, **extra).items():
             arrays[key], dtypes[key] = to_np(t)
-        meta = {"dtypes": dtypes, "scale": scale, "causal": causal, "window": list(window), "varlen": lens is not None,
+        meta = {"dtypes": dtypes, "scale": scale, "causal": causal, "window": list(window), "varlen": lens is not None, "softcap": softcap,
                 "source": "tests/fa_small_op_golden.py golden_bsnd_bwd_from_fwd / golden_tnd_bwd_from_fwd"}
         np.savez_compressed(os.path.join(out_dir, name + ".npz"), meta=json.dumps(meta), **arrays)
         print(name, "ok", {k_: tuple(v_.shape) for k_, v_ in arrays.items()})
