@@ -283,8 +283,9 @@ __global__ void __launch_bounds__(kBwdThreads) bwd_kernel(const __grid_constant_
             float* dst = p.dq_accum + (grow * p.h + head) * p.d_pad + half * DH * 8;
 #pragma unroll
             for (int dt = 0; dt < DH; ++dt) {
-              atomicAdd(dst + dt * 8 + 2 * t4, dq_acc[dt][hf * 2]);
-              atomicAdd(dst + dt * 8 + 2 * t4 + 1, dq_acc[dt][hf * 2 + 1]);
+              asm volatile("red.global.add.v2.f32 [%0], {%1, %2};\n" ::"l"(dst + dt * 8 + 2 * t4), "f"(dq_acc[dt][hf * 2]),
+                           "f"(dq_acc[dt][hf * 2 + 1])
+                           : "memory");
             }
           }
         }
