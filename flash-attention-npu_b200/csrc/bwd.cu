@@ -30,7 +30,7 @@ extern "C" {
 
 size_t fa_b200_bwd_workspace_bytes(const fa_bwd_params* a) {
   if (!a) return 0;
-  const int d_pad = a->d <= 64 ? 64 : 128;
+  const int d_pad = a->d <= 64 ? 64 : (a->d <= 128 ? 128 : 256);
   const int64_t rows = a->cu_seqlens_q ? a->total_q : (int64_t)a->b * a->seqlen_q;
   return fa::align16((size_t)rows * a->h * d_pad * sizeof(float)) + fa::align16((size_t)rows * a->h * sizeof(float));
 }
@@ -44,7 +44,7 @@ int fa_b200_bwd(const fa_bwd_params* a, void* workspace, size_t workspace_bytes,
   if (a->b <= 0 || a->h <= 0 || a->h_k <= 0 || a->h % a->h_k != 0)
     return fail_bwd(FA_ERR_INVALID, "Number of heads in key/value must divide number of heads in query");
   if (a->d <= 0 || a->d % 8 != 0) return fail_bwd(FA_ERR_INVALID, "head dimension must be a multiple of 8 (pad it on the caller side)");
-  if (a->d > 128) return fail_bwd(FA_ERR_UNSUPPORTED, "the backward covers head dimensions up to 128");
+  if (a->d > 256) return fail_bwd(FA_ERR_INVALID, "FlashAttention only supports head dimension at most 256");
   if (a->softcap < 0.f) return fail_bwd(FA_ERR_INVALID, "softcap must be non-negative (0.0 disables softcap)");
   if ((a->cu_seqlens_q != nullptr) != (a->cu_seqlens_k != nullptr))
     return fail_bwd(FA_ERR_INVALID, "cu_seqlens_q and cu_seqlens_k must be passed together");
@@ -84,7 +84,7 @@ int fa_b200_bwd(const fa_bwd_params* a, void* workspace, size_t workspace_bytes,
   p.dv_batch_stride = a->dv_batch_stride; p.dv_row_stride = a->dv_row_stride; p.dv_head_stride = a->dv_head_stride;
   p.lse_batch_stride = a->lse_batch_stride; p.lse_head_stride = a->lse_head_stride;
   p.b = a->b; p.seqlen_q = a->seqlen_q; p.seqlen_k = a->seqlen_k; p.h = a->h; p.h_k = a->h_k; p.d = a->d;
-  p.d_pad = a->d <= 64 ? 64 : 128;
+  p.d_pad = a->d <= 64 ? 64 : (a->d <= 128 ? 128 : 256);
   p.total_q = (int32_t)rows;
   // window normalisation of the golden (tests/fa_small_op_golden.py:21-33; the same rule as the forward's host code)
   int wl = a->window_left, wr = a->window_right;
@@ -111,7 +111,8 @@ int fa_b200_bwd(const fa_bwd_params* a, void* workspace, size_t workspace_bytes,
   if (e != cudaSuccess) return fail_bwd(FA_ERR_CUDA, std::string("backward (delta) launch: ") + cudaGetErrorString(e));
   const int n_kblocks = (a->seqlen_k + kBwdBN - 1) / kBwdBN;
   if (p.d_pad == 64) e = bf ? launch_bwd<64, __nv_bfloat16>(p, n_kblocks, cs) : launch_bwd<64, __half>(p, n_kblocks, cs);
-  else e = bf ? launch_bwd<128, __nv_bfloat16>(p, n_kblocks, cs) : launch_bwd<128, __half>(p, n_kblocks, cs);
+  else if (p.d_pad == 128) e = bf ? launch_bwd<128, __nv_bfloat16>(p, n_kblocks, cs) : launch_bwd<128, __half>(p, n_kblocks, cs);
+  else e = bf ? launch_bwd<256, __nv_bfloat16>(p, n_kblocks, cs) : launch_bwd<256, __half>(p, n_kblocks, cs);
   if (e != cudaSuccess) return fail_bwd(FA_ERR_CUDA, std::string("backward launch: ") + cudaGetErrorString(e));
   const int conv_grid = (int)std::min<int64_t>((rows * a->h * (p.d_pad / 4) + 255) / 256, 148 * 8);
   if (bf) bwd_convert_kernel<__nv_bfloat16><<<conv_grid, 256, 0, cs>>>(p);

@@ -115,7 +115,10 @@ __device__ __forceinline__ void bwd_load_tile(uint32_t dst, const T* src, int64_
 template <int HD, typename T>
 __global__ void __launch_bounds__(kBwdThreads) bwd_kernel(const __grid_constant__ BwdParams p) {
   using S = BwdSmem<HD>;
-  constexpr int DT = HD / 8, KS = HD / 16;
+  // dK / dV accumulators cover at most 128 columns of the head dim at a time (register budget): a head dim of 256
+  // takes two passes over the query blocks, each recomputing S, P, dP, dS; dQ is produced in the first pass only.
+  constexpr int KS = HD / 16, DW = HD > 128 ? 128 : HD, DT = DW / 8, NPASS = HD / DW;
+  constexpr int DQW = HD >= 128 ? 64 : 32, DH = DQW / 8, NQ = HD / DQW;  // dQ in slices of DQW columns
   extern __shared__ __align__(128) uint8_t smem[];
   const uint32_t sb = smem_u32(smem);
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -155,14 +158,16 @@ __global__ void __launch_bounds__(kBwdThreads) bwd_kernel(const __grid_constant_
   }
   const int m_lo = i_lo / kBwdBM, m_hi = i_hi > i_lo ? ceil_div(i_hi, kBwdBM) : m_lo;
 
+  float* lse_s = reinterpret_cast<float*>(smem + S::LSE_OFF);
+  float* delta_s = reinterpret_cast<float*>(smem + S::DELTA_OFF);
+
+#pragma unroll 1
+  for (int pass = 0; pass < NPASS; ++pass) {
   float dk_acc[DT][4], dv_acc[DT][4];
 #pragma unroll
   for (int dt = 0; dt < DT; ++dt)
 #pragma unroll
     for (int e = 0; e < 4; ++e) dk_acc[dt][e] = dv_acc[dt][e] = 0.f;
-
-  float* lse_s = reinterpret_cast<float*>(smem + S::LSE_OFF);
-  float* delta_s = reinterpret_cast<float*>(smem + S::DELTA_OFF);
 
   for (int hg = 0; hg < group; ++hg) {
     const int head = hk * group + hg;
@@ -249,10 +254,10 @@ __global__ void __launch_bounds__(kBwdThreads) bwd_kernel(const __grid_constant_
         }
       }
 
-      // ---- dQ (this warp's 16 rows) += dS K, in two halves of the head dim to bound the registers ----
+      // ---- dQ (this warp's 16 rows) += dS K, in slices of the head dim to bound the registers ----
+      if (pass == 0) {
 #pragma unroll
-      for (int half = 0; half < 2; ++half) {
-        constexpr int DH = DT / 2;
+      for (int half = 0; half < NQ; ++half) {
         float dq_acc[DH][4];
 #pragma unroll
         for (int dt = 0; dt < DH; ++dt)
@@ -290,6 +295,7 @@ __global__ void __launch_bounds__(kBwdThreads) bwd_kernel(const __grid_constant_
           }
         }
       }
+      }
       __syncthreads();  // P and dS of all four warps are in shared memory
 
       // ---- dV (this warp's 16 keys) += P^T dO,  dK += dS^T Q : contraction over the 64 rows ----
@@ -303,7 +309,7 @@ __global__ void __launch_bounds__(kBwdThreads) bwd_kernel(const __grid_constant_
 #pragma unroll
         for (int dp = 0; dp < DT / 2; ++dp) {
           const int brow = kk * 16 + (lm & 1) * 8 + lr;
-          const uint32_t boff = brow * S::PITCH + (dp * 2 + (lm >> 1)) * 16;
+          const uint32_t boff = brow * S::PITCH + (pass * (DW / 8) + dp * 2 + (lm >> 1)) * 16;
           uint32_t b0, b1, b2, b3;
           ldmatrix_x4_trans(b0, b1, b2, b3, sb + S::DO_OFF + boff);
           mma_16816<T>(dv_acc[2 * dp], ap, b0, b1);
@@ -316,7 +322,7 @@ __global__ void __launch_bounds__(kBwdThreads) bwd_kernel(const __grid_constant_
     }
   }
 
-  // ---- dK, dV of this warp's 16 keys ----
+  // ---- dK, dV of this warp's 16 keys (columns of this pass) ----
   cp_async_wait<0>();
 #pragma unroll
   for (int hf = 0; hf < 2; ++hf) {
@@ -328,13 +334,14 @@ __global__ void __launch_bounds__(kBwdThreads) bwd_kernel(const __grid_constant_
              (int64_t)hk * p.dv_head_stride;
 #pragma unroll
     for (int dt = 0; dt < DT; ++dt) {
-      const int c = dt * 8 + 2 * t4;
+      const int c = pass * DW + dt * 8 + 2 * t4;
       if (c < p.d) {
         *reinterpret_cast<uint32_t*>(dkg + c) = pack2<T>(dk_acc[dt][hf * 2], dk_acc[dt][hf * 2 + 1]);
         *reinterpret_cast<uint32_t*>(dvg + c) = pack2<T>(dv_acc[dt][hf * 2], dv_acc[dt][hf * 2 + 1]);
       }
     }
   }
+  }  // pass
 }
 
 }  // namespace fa

@@ -226,7 +226,7 @@ def attention_backward(dout, q, k, v, out, lse, *, dq=None, dk=None, dv=None, so
                        window_left=-1, window_right=-1, softcap=0.0, cu_seqlens_q=None, cu_seqlens_k=None,
                        max_seqlen_q=None, max_seqlen_k=None):
     """dQ, dK, dV of ``attention_forward`` (dense (b, s, h, d) or packed varlen (total, h, d) tensors) from
-    the forward's ``out`` and ``lse``.  Head dim a multiple of 8, at most 128; no dropout / alibi."""
+    the forward's ``out`` and ``lse``.  Head dim a multiple of 8, at most 256; no dropout / alibi."""
     lib = L.load()
     ts = (dout, q, k, v, out)
     if not all(t.is_cuda for t in ts) or not lse.is_cuda:

@@ -168,7 +168,7 @@ int fa_b200_fwd_plan(const fa_fwd_params* p, fa_fwd_plan* plan);
  * mha_varlen_bwd (pybind names bwd, varlen_bwd: csrc/arch22/flash_attn_npu_v2/flash_api.cpp:1301-1309;
  * called from flash_attn_npu_v2/interface_arch22.py:232-252); arithmetic of the reference's golden
   * tests/fa_small_op_golden.py:160-353.  No dropout or alibi (refused by the Python layer).
- * Head dims up to 128 (multiples of 8).  All tensors as in fa_fwd_params: device pointers, element
+ * Head dims up to 256 (multiples of 8).  All tensors as in fa_fwd_params: device pointers, element
  * strides, last dimension contiguous; dq / dk / dv are written completely.
  * ------------------------------------------------------------------------------------------------ */
 typedef struct fa_bwd_params {
