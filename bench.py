@@ -165,6 +165,54 @@ class Prefill:
         return done, t_total, f"{n} slices of (batch 1, 4 heads, seqlen {self.s}, d {self.d}) causal, bf16"
 
 
+class PrefillBackward(Prefill):
+    """c2 shape, backward: dQ, dK, dV of the causal prefill from its out and lse (5 matmuls: 2.5 x the forward's FLOPs)."""
+    name, metric = "c2_bwd_causal_b4_s4096_h32_d128", "attn_bwd_causal_tflops"
+
+    def setup(self, dev, rank, world):
+        Prefill.setup(self, dev, rank, world)
+        import flash_attn_npu_v2 as fa2
+        g = torch.Generator(device=dev).manual_seed(3 + 1000 * rank)
+        self.out, self.lse, _ = fa2.flash_attn_func(self.q, self.k, self.v, causal=True, return_attn_probs=True)
+        self.dout = (torch.randn(self.q.shape, generator=g, device=dev) / math.sqrt(2)).to(BF)
+        self.dq, self.dk, self.dv = [torch.empty_like(self.q) for _ in range(3)]
+        self.units *= 2.5
+
+    def setup_e2e(self):
+        self.host_in = [_pin(t) for t in (self.dout, self.q, self.k, self.v, self.out, self.lse)]
+        self.host_out = [torch.empty(self.q.shape, dtype=BF).pin_memory() for _ in range(3)]
+        self.h2d = sum(t.numel() * t.element_size() for t in self.host_in)
+        self.d2h = sum(t.numel() * t.element_size() for t in self.host_out)
+
+    def _bwd(self, dout, q, k, v, out, lse):
+        from flash_b200 import ops
+        return ops.attention_backward(dout, q, k, v, out, lse, dq=self.dq, dk=self.dk, dv=self.dv,
+                                      softmax_scale=self.d ** -0.5, causal=True)
+
+    def step(self):
+        return self._bwd(self.dout, self.q, self.k, self.v, self.out, self.lse)
+
+    def step_e2e(self):
+        grads = self._bwd(*[t.to("cuda", non_blocking=True) for t in self.host_in])
+        for h, g in zip(self.host_out, grads):
+            h.copy_(g, non_blocking=True)
+
+    def cpu_sample(self, budget_s):
+        from oracle import api as OA
+        from oracle import bwd as OB
+        g = torch.Generator().manual_seed(3)
+        done, t_total, n = 0.0, 0.0, 0
+        while t_total < budget_s and n < 128:
+            q, k, v, do = [(torch.randn((1, self.s, 4, self.d), generator=g) / math.sqrt(2)).to(BF) for _ in range(4)]
+            _, lse = OA.flash_attn_func(q, k, v, causal=True)
+            t0 = time.perf_counter()
+            OB.attention_backward(q, k, v, do, lse, softmax_scale=self.d ** -0.5, causal=True)
+            t_total += time.perf_counter() - t0
+            done += 2.5 * 4.0 * 1 * 4 * self.s * self.s * self.d / 2
+            n += 1
+        return done, t_total, f"{n} slices of (batch 1, 4 heads, seqlen {self.s}, d {self.d}) causal backward, bf16"
+
+
 class DecodeBase:
     metric, unit, bound = "kv_decode_hbm_gbs", "GB/s", "hbm"
     scale = 1e-9
@@ -346,7 +394,7 @@ class DecodeLongSharded(DecodeBase):
         return done, t_total, f"{n} passes over the first {n_tok} keys of sequence 0"
 
 
-WORKLOADS = {"c2": Prefill, "c3": DecodeContiguous, "c4": DecodePaged, "c5": DecodeLongSharded}
+WORKLOADS = {"c2": Prefill, "c2_bwd": PrefillBackward, "c3": DecodeContiguous, "c4": DecodePaged, "c5": DecodeLongSharded}
 
 
 # ------------------------------------------------------------------------------------------------
@@ -503,7 +551,7 @@ def main():
             "metric": wl.metric, "value": value, "unit": wl.unit, "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": total_ms / args.steps, "higher_is_better": True,
             "scaling": "strong" if strong else "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-            "config": {"workload": wl.name, "l2": "inputs larger than L2 (no flush needed)" if args.workload != "c2"
+            "config": {"workload": wl.name, "l2": "inputs larger than L2 (no flush needed)" if not args.workload.startswith("c2")
                        else "q+k+v+o = 537 MB per step, larger than the 126 MB L2", "median_ms_per_step": med_ms,
                        "per_gpu_units": wl.units, "cuda_graph": getattr(wl, "graph", None) is not None},
             "roofline": {"bound": wl.bound, "achieved": achieved, "peak": peak, "unit": runit,
