@@ -124,6 +124,7 @@ static int make_plan(const fa_fwd_params& a, Planned* out) {
   // ---- producer / consumer decode kernel: <= 32 packed rows, head dim <= 128 (> 64), rows that can
   //      be moved by 16-byte aligned bulk copies ----
   int kernel_id = FA_KERNEL_MMA;
+  bool decode_one_segment_only = false;  // the chosen decode configuration keeps its merge slab over the ring
   {
     auto al16 = [](const void* ptr) { return (reinterpret_cast<uintptr_t>(ptr) & 15) == 0; };
     const bool strides_ok = a.k_row_stride % 8 == 0 && a.k_head_stride % 8 == 0 && a.k_batch_stride % 8 == 0 &&
@@ -136,7 +137,19 @@ static int make_plan(const fa_fwd_params& a, Planned* out) {
     if (a.kernel == FA_KERNEL_DECODE && !eligible)
       return fail(FA_ERR_UNSUPPORTED, "the decode kernel does not cover this problem");
     if (eligible && (a.kernel == FA_KERNEL_DECODE || a.kernel == FA_KERNEL_AUTO)) {
-      int dcfg = rows_max <= 16 ? 3 : 5;  // measured best: two resident CTAs of 1x4 consumer warps / one CTA of 2x4
+      // Measured best.  Up to 16 rows: two resident CTAs of 1x4 consumer warps.  17-32 rows: one CTA of 2x4
+      // consumer warps for long key ranges and for launches that become persistent; for short ranges (a
+      // sliding window, short caches) two resident CTAs of 2x2 warps, so that one CTA's Q load, slice
+      // merge and store run under the other's streaming (paged window decode: 88 instead of 98 us).
+      int dcfg = 3;
+      if (rows_max > 16) {
+        long long keys = max_k_bound;
+        const bool windowed = is_local && wl >= 0 && (long long)wl + std::max(wr, 0) + 32 / gp + 2 < keys;
+        if (windowed) keys = (long long)wl + std::max(wr, 0) + 32 / gp + 2;
+        const bool may_persist = a.seqused_k && !windowed && a.num_splits == 0 && !a.cu_seqlens_q && a.kv_total == 0 &&
+                                 !a.partial_out;
+        dcfg = (!may_persist && keys <= 16384) ? 11 : 5;
+      }
       if (const char* e = std::getenv("FA_B200_DECODE_CONFIG")) {  // tuning override: decode tile configuration
         const int forced = std::atoi(e);
         DecodeConfigInfo t;
@@ -147,6 +160,7 @@ static int make_plan(const fa_fwd_params& a, Planned* out) {
         kernel_id = FA_KERNEL_DECODE;
         cfg = dcfg;
         ci = MmaConfigInfo{di.block_m, di.block_n, di.threads, di.smem_bytes};
+        decode_one_segment_only = di.slab_in_ring;
       }
     }
   }
@@ -212,9 +226,9 @@ static int make_plan(const fa_fwd_params& a, Planned* out) {
     persist_grid = (long long)num_sm * resident;
     const bool can_persist = (a.seqused_k != nullptr || window_bound) && base * max_blocks >= 4 * persist_grid &&
                              base * (max_blocks + 1) < 0x3fffffffLL;
-    persistent = can_persist && !window_bound;
+    persistent = can_persist && !window_bound && !decode_one_segment_only;
     if (const char* e = std::getenv("FA_B200_DECODE_PERSISTENT"))  // tuning override: 0 off, 1 default rule, 2 also window-bound
-      persistent = can_persist && (std::atoi(e) == 2 || (std::atoi(e) == 1 && !window_bound));
+      persistent = can_persist && !decode_one_segment_only && (std::atoi(e) == 2 || (std::atoi(e) == 1 && !window_bound));
     if (const char* e = std::getenv("FA_B200_DECODE_PERSISTENT_GRID")) persist_grid = std::max(1, std::atoi(e));  // tuning override
     if (persistent) { ns = kPersistSlots; bps = 0; }
   }

@@ -1,5 +1,6 @@
 // Tile configurations of the producer / consumer decode kernel (head dim padded to 128).
-//   X(index, MT, WM, WN, BN, STAGES)   rows per CTA = 16 * MT * WM, consumer warps = WM * WN
+//   X(index, MT, WM, WN, BN, STAGES, SR)   rows per CTA = 16 * MT * WM, consumer warps = WM * WN;
+//   SR = 1: the merge slab lies over the ring (never with persistent CTAs)
 #pragma once
 
 #include <cuda.h>
@@ -7,22 +8,23 @@
 #include "fwd_decode.cuh"
 
 #define FA_DECODE_CONFIGS_128(X) \
-  X(0, 1, 1, 4, 64, 5) X(1, 1, 1, 8, 128, 3) X(2, 1, 1, 4, 64, 2) X(3, 1, 1, 4, 64, 3) \
-  X(4, 2, 1, 4, 64, 3) X(5, 1, 2, 4, 128, 3) X(6, 1, 2, 4, 128, 2) X(7, 1, 2, 2, 64, 3) X(8, 2, 1, 8, 128, 2) \
-  X(9, 1, 2, 4, 64, 4) X(10, 1, 2, 4, 64, 3)
+  X(0, 1, 1, 4, 64, 5, 0) X(1, 1, 1, 8, 128, 3, 0) X(2, 1, 1, 4, 64, 2, 0) X(3, 1, 1, 4, 64, 3, 0) \
+  X(4, 2, 1, 4, 64, 3, 0) X(5, 1, 2, 4, 128, 3, 0) X(6, 1, 2, 4, 128, 2, 0) X(7, 1, 2, 2, 64, 3, 0) X(8, 2, 1, 8, 128, 2, 0) \
+  X(9, 1, 2, 4, 64, 4, 0) X(10, 1, 2, 4, 64, 3, 0) X(11, 1, 2, 2, 64, 3, 1)
 
 namespace fa {
 
 struct DecodeConfigInfo {
   int block_m, block_n, threads, smem_bytes;
+  bool slab_in_ring;
 };
 
 inline bool decode_config_info(int hd, int cfg, DecodeConfigInfo* out) {
   if (hd != 128) return false;
-#define FA_X(I_, MT_, WM_, WN_, BN_, ST_)                                                 \
+#define FA_X(I_, MT_, WM_, WN_, BN_, ST_, SR_)                                              \
   if (cfg == I_) {                                                                    \
-    using Tr = DecTraits<128, __nv_bfloat16, MT_, WM_, WN_, BN_, ST_>;                    \
-    *out = DecodeConfigInfo{Tr::BM, Tr::BN, Tr::NTHREADS, Tr::SMEM_BYTES};            \
+    using Tr = DecTraits<128, __nv_bfloat16, MT_, WM_, WN_, BN_, ST_, SR_>;                \
+    *out = DecodeConfigInfo{Tr::BM, Tr::BN, Tr::NTHREADS, Tr::SMEM_BYTES, Tr::SLAB_IN_RING}; \
     return true;                                                                      \
   }
   FA_DECODE_CONFIGS_128(FA_X)

@@ -22,7 +22,7 @@ namespace fa {
 
 // Consumer warps form a WM x WN grid: WM splits the packed query rows (16 * MT rows per warp), WN
 // splits the keys of a stage.
-template <int HD_, typename T_, int MT_, int WM_, int WN_, int BN_, int ST_>
+template <int HD_, typename T_, int MT_, int WM_, int WN_, int BN_, int ST_, int SR_ = 0>
 struct DecTraits {
   using T = T_;
   static constexpr int HD = HD_, MT = MT_, WM = WM_, WN = WN_, NCW = WM_ * WN_, BN = BN_, ST = ST_;
@@ -40,14 +40,22 @@ struct DecTraits {
   static constexpr int STAGE_BYTES = 2 * KV_BYTES;
   static constexpr int PIPE_BYTES = ST * STAGE_BYTES;
   static constexpr int SLAB_LD = HD + 4;
-  static constexpr int SLAB_BYTES = BM * SLAB_LD * 4;  // merged output rows of the tile (fp32), not part of the ring
-  static constexpr int MAIN_BYTES = PIPE_BYTES + SLAB_BYTES;
+  static constexpr int SLAB_BYTES = BM * SLAB_LD * 4;  // merged output rows of the tile (fp32)
+  // The slab normally lies behind the ring, so that the producer of a persistent CTA can fill the
+  // ring for the next segment while the consumers merge.  SR_ = 1 puts it over the first stages
+  // instead (one segment per CTA only: the ring is dead when the merge starts), which lets two
+  // CTAs of 32 rows share an SM.
+  static constexpr bool SLAB_IN_RING = SR_ != 0;
+  static_assert(!SLAB_IN_RING || SLAB_BYTES <= PIPE_BYTES, "the slab must fit into the ring");
+  static constexpr int SLAB_OFF = SLAB_IN_RING ? 0 : PIPE_BYTES;
+  static constexpr int MAIN_BYTES = SLAB_IN_RING ? PIPE_BYTES : PIPE_BYTES + SLAB_BYTES;
   static constexpr int Q_BYTES = BM * PITCH;
   static constexpr int ML_BYTES = WN * BM * 8;
   static constexpr int BAR_BYTES = 128 + 2 * ST * 8;
   // [pipeline | slab | Q | (m, l) | barriers], the pipeline at a 1024-byte aligned base
   static constexpr int SMEM_BYTES = 1024 + MAIN_BYTES + Q_BYTES + ML_BYTES + BAR_BYTES;
   static constexpr bool Q_IN_REGS = (MT == 1);
+  static constexpr int MIN_CTAS = SLAB_IN_RING ? 2 : 0;  // resident CTAs per SM the register count must allow (0: no constraint)
   static_assert(NW % 16 == 0, "each consumer warp needs a multiple of 16 keys");
 };
 

@@ -16,7 +16,7 @@ struct DecWalk {
 };
 
 template <class Tr>
-__global__ void __launch_bounds__(Tr::NTHREADS)
+__global__ void __launch_bounds__(Tr::NTHREADS, Tr::MIN_CTAS)
 fwd_decode_kernel(const __grid_constant__ KParams p, const __grid_constant__ CUtensorMap tm_k,
                   const __grid_constant__ CUtensorMap tm_v) {
   using T = typename Tr::T;
@@ -480,7 +480,7 @@ fwd_decode_kernel(const __grid_constant__ KParams p, const __grid_constant__ CUt
           it_base += (uint32_t)n_blocks;
 
           // ---- merge of the WN key slices and output (consumer warps only; the slab is not part of the ring) ----
-          float* slab = reinterpret_cast<float*>(smem_al + Tr::PIPE_BYTES);
+          float* slab = reinterpret_cast<float*>(smem_al + Tr::SLAB_OFF);
           float2* ml = reinterpret_cast<float2*>(smem_al + Tr::MAIN_BYTES + Tr::Q_BYTES);
 #pragma unroll
           for (int mt = 0; mt < MT; ++mt)

@@ -156,3 +156,25 @@ def test_plan_persistent_decode_for_ragged_lengths_only():
     assert rc == 0 and pl.num_splits == 2 and pl.grid == 64 * 8 * 2
     rc, pl = _plan(_params(window_left=1024, window_right=0, **kw))
     assert rc == 0 and pl.kernel == L.KERNEL_DECODE and pl.grid % (64 * 8) == 0  # plain grid: units x splits
+
+
+def test_plan_32_row_decode_configuration_follows_the_key_range():
+    """17-32 packed rows: short key ranges (a sliding window) run two resident CTAs of 2x2 consumer warps with
+    64-key blocks (one launch, no partials); long ranges and ragged launches that become persistent keep the
+    single CTA of 2x4 warps with 128-key blocks."""
+    kw = dict(b=32, seqlen_q=4, seqlen_k=32768, h=64, h_k=8, d=128, total_q=128, seqused_k=256,
+              block_table=256, page_size=256, block_table_batch_stride=128,
+              q_batch_stride=4 * 8192, q_row_stride=8192, q_head_stride=128,
+              k_batch_stride=256 * 1024, k_row_stride=1024, k_head_stride=128,
+              v_batch_stride=256 * 1024, v_row_stride=1024, v_head_stride=128,
+              o_batch_stride=4 * 8192, o_row_stride=8192, o_head_stride=128, lse_batch_stride=256, lse_head_stride=4, causal=1)
+    rc, pl = _plan(_params(window_left=4096, window_right=0, **kw))
+    assert rc == 0 and pl.kernel == L.KERNEL_DECODE and pl.block_m == 32
+    assert pl.config == 11 and pl.block_n == 64 and pl.threads == 160 and 2 * pl.smem_bytes <= 227 * 1024
+    assert pl.num_splits == 1 and pl.grid == 32 * 8 and pl.launches == 1
+    rc, pl = _plan(_params(**kw))  # ragged, no window: persistent, 128-key blocks
+    assert rc == 0 and pl.kernel == L.KERNEL_DECODE and pl.config == 5 and pl.block_n == 128 and pl.num_splits == 4
+    kw.pop("seqused_k"), kw.pop("block_table"), kw.pop("page_size"), kw.pop("block_table_batch_stride")
+    kw.update(k_batch_stride=32768 * 1024, v_batch_stride=32768 * 1024)
+    rc, pl = _plan(_params(**kw))  # uniform long range: 128-key blocks, split over the keys
+    assert rc == 0 and pl.kernel == L.KERNEL_DECODE and pl.config == 5 and pl.block_n == 128
