@@ -432,8 +432,8 @@ def run_reference(args, rank, world):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=20)
-    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--steps", type=int, default=None, help="default: 20 (c2), 10 (c2_bwd), 200 (decode workloads)")
+    ap.add_argument("--warmup", type=int, default=None, help="default: 5 (c2), 3 (c2_bwd), 50 (decode workloads)")
     ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS))
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
@@ -442,6 +442,10 @@ def main():
     ap.add_argument("--shrink", type=int, default=1,
                     help="divide the batch (c2-c4) or the key length (c5) by this factor: small cases for ncu captures")
     args = ap.parse_args()
+    # A decode step is ~0.1-0.6 ms: a handful of them ends before the clocks have risen, so those workloads run more.
+    d_steps, d_warm = {"c2": (20, 5), "c2_bwd": (10, 3)}.get(args.workload, (200, 50))
+    args.steps = d_steps if args.steps is None else args.steps
+    args.warmup = d_warm if args.warmup is None else args.warmup
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
