@@ -145,11 +145,11 @@ class Prefill:
         return fa2.flash_attn_func(self.q, self.k, self.v, causal=True, return_attn_probs=True)
 
     def step_e2e(self):
-        import flash_attn_npu_v2 as fa2
-        q, k, v = [t.to("cuda", non_blocking=True) for t in (self.hq, self.hk, self.hv)]
-        out, lse, _ = fa2.flash_attn_func(q, k, v, causal=True, return_attn_probs=True)
-        self.ho.copy_(out, non_blocking=True)
-        self.hl.copy_(lse, non_blocking=True)
+        # host-buffer entry point of the package: copy in, kernel and copy out of different batch chunks overlap
+        if getattr(self, "host_pipe", None) is None:
+            from flash_b200.host import HostPrefill
+            self.host_pipe = HostPrefill(self.q.shape, self.k.shape, BF, device=self.q.device, chunks=4)
+        self.host_pipe(self.hq, self.hk, self.hv, self.ho, self.hl, after_current_stream=False, softmax_scale=self.d ** -0.5, causal=True)
 
     def cpu_sample(self, budget_s):
         """Oracle on (1 batch, 4 heads) slices until the time budget is used; returns (units, seconds, text)."""

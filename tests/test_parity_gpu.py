@@ -224,3 +224,32 @@ def test_varlen_ragged_lengths_tcgen05():
         assert plan.kernel == L.KERNEL_TCGEN05
         assert L.load().fa_b200_check_status(torch.cuda.current_stream().cuda_stream) == 0
         U.check_rules(out, lse, gold_out, gold_lse, tag=f"tcgen05 ragged causal={causal} window={window}")
+
+
+@pytest.mark.gpu
+def test_host_buffer_pipeline_matches_the_device_call():
+    """flash_b200.host.HostPrefill (pinned host tensors in and out, batch chunks overlapped on three streams)
+    returns bit for bit what one call on device tensors returns, step after step."""
+    from flash_b200 import ops
+    from flash_b200.host import HostPrefill
+    g = torch.Generator().manual_seed(11)
+    b, s, h, hk, d = 5, 384, 4, 2, 128
+    q = (torch.randn((b, s, h, d), generator=g)).to(torch.bfloat16).pin_memory()
+    k = (torch.randn((b, s, hk, d), generator=g)).to(torch.bfloat16).pin_memory()
+    v = (torch.randn((b, s, hk, d), generator=g)).to(torch.bfloat16).pin_memory()
+    out = torch.empty_like(q).pin_memory()
+    lse = torch.empty((b, h, s), dtype=torch.float32).pin_memory()
+    pipe = HostPrefill(q.shape, k.shape, torch.bfloat16, chunks=3)
+    assert pipe.bounds == [(0, 1), (1, 3), (3, 5)]
+    ref_o, ref_l = ops.attention_forward(q.cuda(), k.cuda(), v.cuda(), softmax_scale=d ** -0.5, causal=True)
+    for _ in range(3):
+        out.zero_()
+        pipe(q, k, v, out, lse, softmax_scale=d ** -0.5, causal=True)
+        torch.cuda.synchronize()
+        assert torch.equal(out, ref_o.cpu()) and torch.equal(lse, ref_l.cpu())
+    for _ in range(3):  # steps streamed back to back: the next copies in run under the previous copies out
+        pipe(q, k, v, out, lse, after_current_stream=False, softmax_scale=d ** -0.5, causal=True)
+    torch.cuda.synchronize()
+    assert torch.equal(out, ref_o.cpu()) and torch.equal(lse, ref_l.cpu())
+    with pytest.raises(RuntimeError, match="host tensor"):
+        pipe(q.cuda(), k, v, out, lse, softmax_scale=d ** -0.5, causal=True)
