@@ -161,7 +161,10 @@ bool tc5_eligible(const fa_fwd_params& a, bool is_causal, bool is_local, int wl_
   // varlen: both sides packed, and the number of k / v rows known (TMA bound)
   if ((a.cu_seqlens_q != nullptr) != (a.cu_seqlens_k != nullptr)) return false;
   if (a.cu_seqlens_k && a.total_k <= 0) return false;
-  if (a.seqused_k || a.block_table || a.k_new || a.alibi_slopes || a.cache_batch_idx || a.rotary_cos) return false;
+  // KV cache without append: per-entry lengths, contiguous or paged with whole 128-key blocks per page
+  if ((a.seqused_k || a.block_table) && (a.cu_seqlens_q || !a.seqused_k)) return false;
+  if (a.block_table && (a.page_size <= 0 || a.page_size % tc5::kBlockN != 0)) return false;
+  if (a.k_new || a.alibi_slopes || a.cache_batch_idx || a.rotary_cos) return false;
   if (a.softcap > 0.f || a.partial_out || a.kv_total > 0 || wl_on_device) return false;
   // TMA: 16-byte aligned bases and strides
   auto al = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; };
@@ -232,6 +235,13 @@ int tc5_launch(const fa_fwd_params& a, const fa_fwd_plan& pl, cudaStream_t st, s
     ok = encode_map(&tq, a.q, a.dtype, a.d, a.h, a.total_q, 1, a.q_head_stride, a.q_row_stride, 0) &&
          encode_map(&tk, a.k, a.dtype, a.d, a.h_k, a.total_k, 1, a.k_head_stride, a.k_row_stride, 0) &&
          encode_map(&tv, a.v, a.dtype, a.d, a.h_k, a.total_k, 1, a.v_head_stride, a.v_row_stride, 0);
+  } else if (a.block_table) {
+    // (d, kv head, row in page, page); the page count is not part of the parameters and only bounds the
+    // TMA's out-of-range check, which the kernel never relies on in that dimension
+    const int64_t n_pages = int64_t(1) << 30;
+    ok = encode_map(&tq, a.q, a.dtype, a.d, a.h, a.seqlen_q, a.b, a.q_head_stride, a.q_row_stride, a.q_batch_stride) &&
+         encode_map(&tk, a.k, a.dtype, a.d, a.h_k, a.page_size, n_pages, a.k_head_stride, a.k_row_stride, a.k_batch_stride) &&
+         encode_map(&tv, a.v, a.dtype, a.d, a.h_k, a.page_size, n_pages, a.v_head_stride, a.v_row_stride, a.v_batch_stride);
   } else {
     ok = encode_map(&tq, a.q, a.dtype, a.d, a.h, a.seqlen_q, a.b, a.q_head_stride, a.q_row_stride, a.q_batch_stride) &&
          encode_map(&tk, a.k, a.dtype, a.d, a.h_k, a.seqlen_k, a.b, a.k_head_stride, a.k_row_stride, a.k_batch_stride) &&

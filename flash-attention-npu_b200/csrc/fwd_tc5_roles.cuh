@@ -21,7 +21,9 @@ struct RingPos {
 // ---------------------------------------------------------------------------------------------
 // TMA producer: Q sub-tiles once per CTA tile, then the K / V tiles into the ring.
 // Tensor maps are 4-D (d, head, row, batch); a [128 x 128] tile arrives as two 64-column boxes
-// (128-byte rows, 128-byte swizzle), each 16 KiB.
+// (128-byte rows, 128-byte swizzle), each 16 KiB.  A paged cache is (d, head, row in page, page):
+// pages hold whole 128-key blocks, the page of a block comes from the block table (the warp keeps
+// 32 consecutive entries in registers, one per lane).
 // ---------------------------------------------------------------------------------------------
 __device__ __forceinline__ void producer_loop(const Tc5Params& p, const CUtensorMap* tm_q, const CUtensorMap* tm_k,
                                               const CUtensorMap* tm_v, Barriers* bar, uint32_t q_smem, uint32_t kv_smem) {
@@ -30,6 +32,8 @@ __device__ __forceinline__ void producer_loop(const Tc5Params& p, const CUtensor
   Tracer tr(p, 5, (threadIdx.x & 31) == 0);
   uint32_t q_cnt[2] = {0, 0};
   const bool varlen_q = p.a.cu_seqlens_q != nullptr, varlen_k = p.a.cu_seqlens_k != nullptr;
+  const int lane = threadIdx.x & 31;
+  const int pages_per_seq = p.a.block_table ? ceil_div(p.a.seqlen_k, p.a.page_size) : 0;  // entries per block-table row
   TileSched sched(p);
   for (int n = sched.first(); n < p.total_tiles; n = sched.next()) {
     TileInfo ti;
@@ -52,16 +56,28 @@ __device__ __forceinline__ void producer_loop(const Tc5Params& p, const CUtensor
       FA_TR(tr, 40 + t);
     }
     const int bk = varlen_k ? 0 : ti.bi;
+    const int32_t* pages = p.a.block_table ? p.a.block_table + (int64_t)ti.bi * p.a.block_table_batch_stride : nullptr;
+    int pg_base = -1, pg_reg = 0;  // block-table entries pg_base .. pg_base + 31 of this batch entry, one per lane
     auto load = [&](const CUtensorMap* tm, int j) -> bool {
       uint32_t slot, par;
       ring.next(slot, par);
+      int row = ti.k_row0 + j * kBlockN, outer = bk;
+      if (pages) {
+        const int pg = (j * kBlockN) / p.a.page_size;
+        if (pg_base < 0 || pg < pg_base || pg >= pg_base + 32) {
+          pg_base = pg;
+          const int idx = pg + lane;
+          pg_reg = idx < pages_per_seq ? pages[idx] : 0;
+        }
+        outer = __shfl_sync(0xffffffffu, pg_reg, pg - pg_base);
+        row = j * kBlockN - pg * p.a.page_size;
+      }
       if (!mbar_wait(smem_addr(&bar->kv_empty[slot]), par ^ 1, abort_flag, 12)) return false;
       const uint32_t full = smem_addr(&bar->kv_full[slot]);
-      const int row = ti.k_row0 + j * kBlockN;
       if (elect_one()) {
         mbar_arrive_expect_tx(full, kTileBytes);
-        tma_load_4d(kv_smem + slot * kTileBytes, tm, full, 0, ti.hk, row, bk);
-        tma_load_4d(kv_smem + slot * kTileBytes + kHalfBytes, tm, full, 64, ti.hk, row, bk);
+        tma_load_4d(kv_smem + slot * kTileBytes, tm, full, 0, ti.hk, row, outer);
+        tma_load_4d(kv_smem + slot * kTileBytes + kHalfBytes, tm, full, 64, ti.hk, row, outer);
       }
       __syncwarp();
       FA_TR(tr, tm == tm_k ? 42 : 43);

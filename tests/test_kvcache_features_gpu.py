@@ -207,3 +207,37 @@ def test_persistent_decode_ragged(paged):
                                        causal=True, return_plan=True)
     assert plan.kernel == L.KERNEL_DECODE and plan.num_splits == 4 and plan.grid <= 2 * 160
     assert L.load().fa_b200_check_status(torch.cuda.current_stream().cuda_stream) == 0
+
+
+@pytest.mark.parametrize("page", [0, 128, 256])
+@pytest.mark.parametrize("dtype", [BF, FP])
+def test_chunked_prefill_against_cache_runs_on_tcgen05(page, dtype):
+    """Many query tokens against a KV cache with per-entry lengths (no append), contiguous (page 0) or paged: the
+    tcgen05 prefill kernel takes it (keys in use from cache_seqlens, pages from the block table).  Lengths below the
+    query count (rows without visible keys), an empty entry, lengths that end inside a block and inside a page."""
+    from flash_b200 import lib as L
+    from flash_b200 import ops
+    g = torch.Generator().manual_seed(500 + page)
+    b, s_q, h, hk, d, s_cache = 5, 200, 8, 2, 128, 1280
+    q = U.normal((b, s_q, h, d), dtype, g)
+    kc, vc = U.normal((b, s_cache, hk, d), dtype, g), U.normal((b, s_cache, hk, d), dtype, g)
+    lens = torch.tensor([333, 1280, 77, 0, 1025], dtype=torch.int32)
+    bt = None
+    if page:
+        nblk = b * s_cache // page + 3  # a few pages nobody owns
+        perm = torch.randperm(nblk, generator=g)[:b * s_cache // page]
+        bt = perm.view(b, s_cache // page).to(torch.int32)
+        pool_k, pool_v = U.normal((nblk, page, hk, d), dtype, g), U.normal((nblk, page, hk, d), dtype, g)
+        pool_k[perm] = kc.view(-1, page, hk, d)
+        pool_v[perm] = vc.view(-1, page, hk, d)
+        kc, vc = pool_k, pool_v
+    out, lse, go, gl = _run_both(q, kc, vc, None, None, lens, bt=bt, causal=True)
+    U.check_rules(out, lse, go, gl, tag=f"chunked prefill page={page}")
+    _, _, plan = ops.attention_forward(q.cuda(), kc.cuda(), vc.cuda(), seqused_k=lens.cuda(),
+                                       block_table=None if bt is None else bt.cuda(), softmax_scale=d ** -0.5,
+                                       causal=True, return_plan=True)
+    assert plan.kernel == L.KERNEL_TCGEN05
+    # a sliding window on top: the window rule needs the longest key length, which only the device knows here, so
+    # the general kernel takes this one
+    out, lse, go, gl = _run_both(q, kc, vc, None, None, lens, bt=bt, causal=True, window=(300, 0))
+    U.check_rules(out, lse, go, gl, tag=f"chunked prefill window page={page}")
