@@ -16,6 +16,7 @@
 #include "decode_configs.cuh"
 #include "mma_configs.cuh"
 #include "tc5_api.cuh"
+#include "kv_prologue.cuh"
 
 namespace fa {
 
@@ -307,7 +308,27 @@ static int run_fwd(const fa_fwd_params& a, void* workspace, size_t workspace_byt
   if (rc != FA_OK) return rc;
   if (a.total_q == 0 || a.seqlen_q == 0) return FA_OK;
   if (P.pl.kernel == FA_KERNEL_TCGEN05) {
-    rc = tc5_launch(a, P.pl, st, &g_err);
+    fa_fwd_params a2 = a;
+    if (a.k_new) {
+      // New tokens: a prologue launch appends them to the cache (k rotated) and leaves the rotated q in
+      // the workspace; the prefill kernel then sees a cache of cache_seqlens + s_new keys.
+      void* q_rot = nullptr;
+      if (a.rotary_cos) {
+        if (!workspace || workspace_bytes < P.pl.workspace_bytes) return fail(FA_ERR_WORKSPACE, "workspace missing or too small");
+        if ((reinterpret_cast<uintptr_t>(workspace) & 15) != 0) return fail(FA_ERR_WORKSPACE, "workspace must be 16-byte aligned");
+        q_rot = workspace;
+        a2.q = q_rot;
+        a2.q_head_stride = a.d;
+        a2.q_row_stride = (int64_t)a.h * a.d;
+        a2.q_batch_stride = (int64_t)a.seqlen_q * a.h * a.d;
+      }
+      cudaError_t e = launch_kv_prologue(P.kp, q_rot, P.pl.is_causal || P.pl.is_local, st);
+      if (e != cudaSuccess) return fail(FA_ERR_CUDA, std::string("append prologue launch: ") + cudaGetErrorString(e));
+      ++g_launches;
+      a2.k_new = a2.v_new = nullptr;  // seqlen_new stays: the kernel adds it to the cache lengths
+      a2.rotary_cos = a2.rotary_sin = nullptr;
+    }
+    rc = tc5_launch(a2, P.pl, st, &g_err);
     if (rc == FA_OK) ++g_launches;
     return rc;
   }

@@ -164,7 +164,9 @@ bool tc5_eligible(const fa_fwd_params& a, bool is_causal, bool is_local, int wl_
   // KV cache without append: per-entry lengths, contiguous or paged with whole 128-key blocks per page
   if ((a.seqused_k || a.block_table) && (a.cu_seqlens_q || !a.seqused_k)) return false;
   if (a.block_table && (a.page_size <= 0 || a.page_size % tc5::kBlockN != 0)) return false;
-  if (a.k_new || a.alibi_slopes || a.cache_batch_idx || a.rotary_cos) return false;
+  // new tokens (and rotary) are served by a prologue launch in front of the kernel; they need the cache lengths
+  if ((a.k_new || a.rotary_cos) && (!a.seqused_k || !a.k_new || !a.v_new)) return false;
+  if (a.alibi_slopes || a.cache_batch_idx) return false;
   if (a.softcap > 0.f || a.partial_out || a.kv_total > 0 || wl_on_device) return false;
   // TMA: 16-byte aligned bases and strides
   auto al = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; };
@@ -197,8 +199,8 @@ void tc5_fill_plan(const fa_fwd_params& a, fa_fwd_plan* pl) {
   pl->grid = (int)std::min<long long>(total, num_sm > 0 ? num_sm : 148);
   pl->threads = tc5::kThreads;
   pl->smem_bytes = tc5::kSmemBytes;
-  pl->launches = 1;
-  pl->workspace_bytes = 0;
+  pl->launches = a.k_new ? 2 : 1;  // + the append / rotary prologue
+  pl->workspace_bytes = a.rotary_cos ? (size_t)a.b * a.seqlen_q * a.h * a.d * 2 : 0;  // the rotated q
 }
 
 int tc5_launch(const fa_fwd_params& a, const fa_fwd_plan& pl, cudaStream_t st, std::string* err) {

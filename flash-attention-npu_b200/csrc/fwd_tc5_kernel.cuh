@@ -117,7 +117,8 @@ __device__ __forceinline__ void tile_info(const Tc5Params& p, int n, TileInfo& t
     ti.k_row0 = p.a.cu_seqlens_k[ti.bi];
     ti.k_len = p.a.cu_seqlens_k[ti.bi + 1] - ti.k_row0;
   }
-  if (p.a.seqused_k) ti.k_len = p.a.seqused_k[ti.bi];  // KV cache (contiguous or paged): keys in use per batch entry
+  // KV cache (contiguous or paged): keys in use per batch entry, plus the tokens the prologue appended
+  if (p.a.seqused_k) ti.k_len = p.a.seqused_k[ti.bi] + p.a.seqlen_new;
   ti.koff = ti.k_len - ti.q_len;
   ti.ulo = 0x7fffffff;
   ti.uhi = 0;

@@ -241,3 +241,39 @@ def test_chunked_prefill_against_cache_runs_on_tcgen05(page, dtype):
     # the general kernel takes this one
     out, lse, go, gl = _run_both(q, kc, vc, None, None, lens, bt=bt, causal=True, window=(300, 0))
     U.check_rules(out, lse, go, gl, tag=f"chunked prefill window page={page}")
+
+
+@pytest.mark.parametrize("page", [0, 128, 256])
+@pytest.mark.parametrize("rotary,interleaved", [(0, False), (64, False), (128, True)])
+def test_chunked_prefill_with_append_runs_on_tcgen05(page, rotary, interleaved):
+    """A chunk of new tokens (q, k, v of the same 160 positions) against a cache: the new k (rotated) and v are
+    written into the cache bit-exactly, q is rotated at its positions, and the attention runs on the tcgen05
+    kernel behind an append / rotary prologue launch."""
+    from flash_b200 import lib as L
+    from flash_b200 import ops
+    g = torch.Generator().manual_seed(900 + page + rotary)
+    b, s_q, h, hk, d, s_cache = 4, 160, 8, 2, 128, 1024
+    q = U.normal((b, s_q, h, d), BF, g)
+    k, v = U.normal((b, s_q, hk, d), BF, g), U.normal((b, s_q, hk, d), BF, g)
+    kc, vc = U.normal((b, s_cache, hk, d), BF, g), U.normal((b, s_cache, hk, d), BF, g)
+    lens = torch.tensor([0, 100, s_cache - s_q, 511], dtype=torch.int32)
+    cos = sin = None
+    if rotary:
+        cos, sin = U.rotary_tables(s_cache + 8, rotary, BF)
+    bt = None
+    if page:
+        nblk = b * s_cache // page + 2
+        perm = torch.randperm(nblk, generator=g)[:b * s_cache // page]
+        bt = perm.view(b, s_cache // page).to(torch.int32)
+        pool_k, pool_v = U.normal((nblk, page, hk, d), BF, g), U.normal((nblk, page, hk, d), BF, g)
+        pool_k[perm] = kc.view(-1, page, hk, d)
+        pool_v[perm] = vc.view(-1, page, hk, d)
+        kc, vc = pool_k, pool_v
+    out, lse, go, gl = _run_both(q, kc, vc, k, v, lens, cos=cos, sin=sin, interleaved=interleaved, bt=bt, causal=True)
+    U.check_rules(out, lse, go, gl, tag=f"chunked prefill + append page={page} rotary={rotary}")
+    c = lambda t: None if t is None else t.cuda()
+    _, _, plan = ops.attention_forward(c(q), c(kc), c(vc), k_new=c(k), v_new=c(v), seqused_k=c(lens), block_table=c(bt),
+                                       rotary_cos=c(cos), rotary_sin=c(sin), rotary_interleaved=interleaved,
+                                       softmax_scale=d ** -0.5, causal=True, return_plan=True)
+    assert plan.kernel == L.KERNEL_TCGEN05 and plan.launches == 2
+    assert plan.workspace_bytes == (b * s_q * h * d * 2 if rotary else 0)
