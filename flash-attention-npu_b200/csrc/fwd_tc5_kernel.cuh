@@ -63,7 +63,7 @@ struct Tc5Params {
   // 0 = always (P <= 1 and the row maximum has P = 1 exactly, like the golden); > 0 trades a few
   // ulps of P rounding on sharply peaked rows for fewer O rescales.
   float rescale_threshold;
-  int32_t tune_reserved;
+  int32_t chunk_bh;          // (batch, head) pairs per L2 chunk of the tile order (tile_info)
   int32_t tune_poly;         // experiment: exponentials evaluated by polynomial out of every 4 pairs
   int32_t* status;  // device word: 0 ok, otherwise the wait that gave up
 #ifdef FA_TC5_TRACE
@@ -98,10 +98,18 @@ struct TileInfo {
   int ulo, uhi;  // union of the block ranges
 };
 
+// Tile order: the (batch, head) pairs are cut into chunks whose K / V fit in L2 together; inside a
+// chunk all pairs run their last (heaviest, causal) query tile first, then the one before, and so
+// on, so the K / V prefixes a chunk re-reads tile after tile come from L2 and not from HBM.  The
+// chunk length makes a chunk a whole even number of rounds of the grid (TileSched), which keeps the
+// per-CTA sums as even as one chunk over everything would.
 __device__ __forceinline__ void tile_info(const Tc5Params& p, int n, TileInfo& ti) {
   const int per_m = p.a.b * p.a.h;
-  const int mt = p.m_tiles - 1 - n / per_m;  // heavy (late, causal) tiles first
-  const int rem = n % per_m;
+  const int per_chunk = p.chunk_bh * p.m_tiles;
+  const int ck = n / per_chunk, r = n - ck * per_chunk;
+  const int cnt = min(p.chunk_bh, per_m - ck * p.chunk_bh);  // pairs in this chunk (the last one may be short)
+  const int mt = p.m_tiles - 1 - r / cnt;  // heavy (late, causal) tiles first
+  const int rem = ck * p.chunk_bh + r % cnt;
   ti.bi = rem / p.a.h;
   ti.hh = rem % p.a.h;
   ti.hk = ti.hh / p.group;
