@@ -253,3 +253,20 @@ def test_host_buffer_pipeline_matches_the_device_call():
     assert torch.equal(out, ref_o.cpu()) and torch.equal(lse, ref_l.cpu())
     with pytest.raises(RuntimeError, match="host tensor"):
         pipe(q.cuda(), k, v, out, lse, softmax_scale=d ** -0.5, causal=True)
+
+
+@pytest.mark.gpu
+def test_tile_order_chunks_do_not_change_the_result(monkeypatch):
+    """The tcgen05 prefill kernel orders its tiles in chunks of (batch, head) pairs whose K / V stay in L2.  Any chunk
+    length (a tuning override here, incl. one that leaves a short last chunk) gives bit-identical O and LSE."""
+    from flash_b200 import ops
+    g = torch.Generator().manual_seed(21)
+    b, s, h, hk, d = 3, 700, 6, 2, 128  # 18 pairs x 3 query tiles
+    q, k, v = [U.normal((b, s, n, d), torch.bfloat16, g).cuda() for n in (h, hk, hk)]
+    monkeypatch.setenv("FA_B200_TC5_CHUNK", "0")
+    ref_o, ref_l = ops.attention_forward(q, k, v, softmax_scale=d ** -0.5, causal=True)
+    for chunk in ("1", "4", "5", "18", "100"):
+        monkeypatch.setenv("FA_B200_TC5_CHUNK", chunk)
+        o, l = ops.attention_forward(q, k, v, softmax_scale=d ** -0.5, causal=True)
+        torch.cuda.synchronize()
+        assert torch.equal(o, ref_o) and torch.equal(l, ref_l), f"chunk {chunk}"
