@@ -219,14 +219,15 @@ int tc5_launch(const fa_fwd_params& a, const fa_fwd_plan& pl, cudaStream_t st, s
   p.rescale_threshold = 0.f;
   {
     // L2 chunks of the tile order (tile_info).  A chunk is 2 * grid / gcd(2 * grid, m_tiles) pairs: a whole
-    // even number of grid rounds.  Used when all K / V together would not stay in L2 but a chunk's does.
+    // even number of grid rounds.  Used when all K / V together would not stay in L2 but a chunk's does (packed
+    // varlen input: judged by the longest sequence).
     const long long per_m = (long long)a.b * a.h;
     const long long kv_bytes_per_pair = 4LL * a.seqlen_k * a.d / std::max(1, a.h / a.h_k);  // K and V, shared by a group
     const long long l2_budget = 96LL << 20;
     auto gcd = [](long long x, long long y) { while (y) { const long long t = x % y; x = y; y = t; } return x; };
     long long chunk = 2LL * pl.grid / gcd(2LL * pl.grid, pl.m_blocks);
     if (const char* e = std::getenv("FA_B200_TC5_CHUNK")) chunk = std::atoll(e);  // tuning override (0: one chunk)
-    else if (a.cu_seqlens_q || per_m * kv_bytes_per_pair <= l2_budget || chunk * kv_bytes_per_pair > l2_budget) chunk = per_m;
+    else if (per_m * kv_bytes_per_pair <= l2_budget || chunk * kv_bytes_per_pair > l2_budget) chunk = per_m;
     if (chunk <= 0 || chunk > per_m) chunk = per_m;
     p.chunk_bh = (int)chunk;
   }

@@ -270,3 +270,16 @@ def test_tile_order_chunks_do_not_change_the_result(monkeypatch):
         o, l = ops.attention_forward(q, k, v, softmax_scale=d ** -0.5, causal=True)
         torch.cuda.synchronize()
         assert torch.equal(o, ref_o) and torch.equal(l, ref_l), f"chunk {chunk}"
+    # packed varlen input with ragged lengths (an empty sequence among them)
+    lens = [300, 0, 700, 129, 512]
+    cu = torch.tensor([0] + list(itertools.accumulate(lens)), dtype=torch.int32).cuda()
+    tot = sum(lens)
+    q, k, v = [U.normal((tot, n, d), torch.bfloat16, g).cuda() for n in (h, hk, hk)]
+    kw = dict(cu_seqlens_q=cu, cu_seqlens_k=cu, max_seqlen_q=max(lens), max_seqlen_k=max(lens), softmax_scale=d ** -0.5, causal=True)
+    monkeypatch.setenv("FA_B200_TC5_CHUNK", "0")
+    ref_o, ref_l = ops.attention_forward(q, k, v, **kw)
+    for chunk in ("1", "7", "29"):
+        monkeypatch.setenv("FA_B200_TC5_CHUNK", chunk)
+        o, l = ops.attention_forward(q, k, v, **kw)
+        torch.cuda.synchronize()
+        assert torch.equal(o, ref_o) and torch.equal(l, ref_l), f"varlen chunk {chunk}"
