@@ -178,3 +178,33 @@ def test_plan_32_row_decode_configuration_follows_the_key_range():
     kw.update(k_batch_stride=32768 * 1024, v_batch_stride=32768 * 1024)
     rc, pl = _plan(_params(**kw))  # uniform long range: 128-key blocks, split over the keys
     assert rc == 0 and pl.kernel == L.KERNEL_DECODE and pl.config == 5 and pl.block_n == 128
+
+
+def test_plan_prefill_against_a_cache_goes_to_the_tcgen05_kernel():
+    """Many query tokens against a KV cache with per-entry lengths: tcgen05 kernel for contiguous caches and for
+    pages that hold whole 128-key blocks; new tokens add a prologue launch and, with rotary, a workspace for the
+    rotated q; cache_batch_idx and small pages stay on the general kernel."""
+    kw = dict(b=4, seqlen_q=512, seqlen_k=8192, h=32, h_k=8, d=128, total_q=2048, seqused_k=256,
+              q_batch_stride=512 * 4096, q_row_stride=4096, q_head_stride=128,
+              k_batch_stride=8192 * 1024, k_row_stride=1024, k_head_stride=128,
+              v_batch_stride=8192 * 1024, v_row_stride=1024, v_head_stride=128,
+              o_batch_stride=512 * 4096, o_row_stride=4096, o_head_stride=128, lse_batch_stride=32 * 512, lse_head_stride=512,
+              causal=1)
+    rc, pl = _plan(_params(**kw))
+    assert rc == 0 and pl.kernel == L.KERNEL_TCGEN05 and pl.launches == 1 and pl.workspace_bytes == 0
+    paged = dict(kw, block_table=256, page_size=256, block_table_batch_stride=32,
+                 k_batch_stride=256 * 1024, v_batch_stride=256 * 1024)
+    rc, pl = _plan(_params(**paged))
+    assert rc == 0 and pl.kernel == L.KERNEL_TCGEN05 and pl.launches == 1
+    rc, pl = _plan(_params(**dict(paged, page_size=64, k_batch_stride=64 * 1024, v_batch_stride=64 * 1024,
+                                  block_table_batch_stride=128)))
+    assert rc == 0 and pl.kernel == L.KERNEL_MMA
+    new = dict(k_new=256, v_new=256, seqlen_new=512, knew_batch_stride=512 * 1024, knew_row_stride=1024, knew_head_stride=128,
+               vnew_batch_stride=512 * 1024, vnew_row_stride=1024, vnew_head_stride=128)
+    rc, pl = _plan(_params(**dict(paged, **new)))
+    assert rc == 0 and pl.kernel == L.KERNEL_TCGEN05 and pl.launches == 2 and pl.workspace_bytes == 0
+    rc, pl = _plan(_params(**dict(paged, rotary_cos=256, rotary_sin=256, rotary_dim=128, rotary_seqlen=9000, **new)))
+    assert rc == 0 and pl.kernel == L.KERNEL_TCGEN05 and pl.launches == 2
+    assert pl.workspace_bytes == 4 * 512 * 32 * 128 * 2
+    rc, pl = _plan(_params(**dict(kw, cache_batch_idx=256)))
+    assert rc == 0 and pl.kernel == L.KERNEL_MMA
