@@ -166,7 +166,7 @@ bool tc5_eligible(const fa_fwd_params& a, bool is_causal, bool is_local, int wl_
   if (a.block_table && (a.page_size <= 0 || a.page_size % tc5::kBlockN != 0)) return false;
   // new tokens (and rotary) are served by a prologue launch in front of the kernel; they need the cache lengths
   if ((a.k_new || a.rotary_cos) && (!a.seqused_k || !a.k_new || !a.v_new)) return false;
-  if (a.alibi_slopes || a.cache_batch_idx) return false;
+  if (a.alibi_slopes || (a.cache_batch_idx && !a.seqused_k)) return false;
   if (a.softcap > 0.f || a.partial_out || a.kv_total > 0 || wl_on_device) return false;
   // TMA: 16-byte aligned bases and strides
   auto al = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; };
@@ -259,9 +259,11 @@ int tc5_launch(const fa_fwd_params& a, const fa_fwd_plan& pl, cudaStream_t st, s
          encode_map(&tk, a.k, a.dtype, a.d, a.h_k, a.page_size, n_pages, a.k_head_stride, a.k_row_stride, a.k_batch_stride) &&
          encode_map(&tv, a.v, a.dtype, a.d, a.h_k, a.page_size, n_pages, a.v_head_stride, a.v_row_stride, a.v_batch_stride);
   } else {
+    // with cache_batch_idx the cache has more rows than the batch: their number is not part of the parameters
+    const int64_t kv_batch = a.cache_batch_idx ? (int64_t(1) << 30) : a.b;
     ok = encode_map(&tq, a.q, a.dtype, a.d, a.h, a.seqlen_q, a.b, a.q_head_stride, a.q_row_stride, a.q_batch_stride) &&
-         encode_map(&tk, a.k, a.dtype, a.d, a.h_k, a.seqlen_k, a.b, a.k_head_stride, a.k_row_stride, a.k_batch_stride) &&
-         encode_map(&tv, a.v, a.dtype, a.d, a.h_k, a.seqlen_k, a.b, a.v_head_stride, a.v_row_stride, a.v_batch_stride);
+         encode_map(&tk, a.k, a.dtype, a.d, a.h_k, a.seqlen_k, kv_batch, a.k_head_stride, a.k_row_stride, a.k_batch_stride) &&
+         encode_map(&tv, a.v, a.dtype, a.d, a.h_k, a.seqlen_k, kv_batch, a.v_head_stride, a.v_row_stride, a.v_batch_stride);
   }
   if (!ok) { *err = "cuTensorMapEncodeTiled failed"; return FA_ERR_CUDA; }
   cudaError_t e = cudaErrorInvalidValue;

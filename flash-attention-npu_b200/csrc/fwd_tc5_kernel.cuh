@@ -92,6 +92,7 @@ struct Tracer {
 
 struct TileInfo {
   int bi, hh, hk, q_row0, q_len, k_row0, k_len, koff;
+  int bk;  // batch row of K / V (cache_batch_idx for a contiguous cache)
   int row0[2];  // first row (within the sequence) of each sub-tile
   int jlo[2], jhi[2];
   bool has[2];
@@ -125,6 +126,7 @@ __device__ __forceinline__ void tile_info(const Tc5Params& p, int n, TileInfo& t
     ti.k_row0 = p.a.cu_seqlens_k[ti.bi];
     ti.k_len = p.a.cu_seqlens_k[ti.bi + 1] - ti.k_row0;
   }
+  ti.bk = (p.a.cache_batch_idx && !p.a.block_table) ? p.a.cache_batch_idx[ti.bi] : ti.bi;
   // KV cache (contiguous or paged): keys in use per batch entry, plus the tokens the prologue appended
   if (p.a.seqused_k) ti.k_len = p.a.seqused_k[ti.bi] + p.a.seqlen_new;
   ti.koff = ti.k_len - ti.q_len;

@@ -55,7 +55,7 @@ __device__ __forceinline__ void producer_loop(const Tc5Params& p, const CUtensor
       __syncwarp();
       FA_TR(tr, 40 + t);
     }
-    const int bk = varlen_k ? 0 : ti.bi;
+    const int bk = varlen_k ? 0 : ti.bk;
     const int32_t* pages = p.a.block_table ? p.a.block_table + (int64_t)ti.bi * p.a.block_table_batch_stride : nullptr;
     int pg_base = -1, pg_reg = 0;  // block-table entries pg_base .. pg_base + 31 of this batch entry, one per lane
     auto load = [&](const CUtensorMap* tm, int j) -> bool {

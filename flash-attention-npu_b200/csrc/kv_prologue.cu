@@ -35,8 +35,9 @@ __global__ void __launch_bounds__(256) kv_prologue_kernel(const __grid_constant_
     if (p.a.block_table) {
       sv.pages = p.a.block_table + (int64_t)bi * p.a.block_table_batch_stride;
     } else {
-      kb += (int64_t)bi * p.a.k_batch_stride;
-      vb += (int64_t)bi * p.a.v_batch_stride;
+      const int batch_row = p.a.cache_batch_idx ? p.a.cache_batch_idx[bi] : bi;
+      kb += (int64_t)batch_row * p.a.k_batch_stride;
+      vb += (int64_t)batch_row * p.a.v_batch_stride;
     }
     sv.k = kb;
     sv.v = vb;

@@ -183,7 +183,7 @@ def test_plan_32_row_decode_configuration_follows_the_key_range():
 def test_plan_prefill_against_a_cache_goes_to_the_tcgen05_kernel():
     """Many query tokens against a KV cache with per-entry lengths: tcgen05 kernel for contiguous caches and for
     pages that hold whole 128-key blocks; new tokens add a prologue launch and, with rotary, a workspace for the
-    rotated q; cache_batch_idx and small pages stay on the general kernel."""
+    rotated q; alibi and small pages stay on the general kernel."""
     kw = dict(b=4, seqlen_q=512, seqlen_k=8192, h=32, h_k=8, d=128, total_q=2048, seqused_k=256,
               q_batch_stride=512 * 4096, q_row_stride=4096, q_head_stride=128,
               k_batch_stride=8192 * 1024, k_row_stride=1024, k_head_stride=128,
@@ -207,4 +207,6 @@ def test_plan_prefill_against_a_cache_goes_to_the_tcgen05_kernel():
     assert rc == 0 and pl.kernel == L.KERNEL_TCGEN05 and pl.launches == 2
     assert pl.workspace_bytes == 4 * 512 * 32 * 128 * 2
     rc, pl = _plan(_params(**dict(kw, cache_batch_idx=256)))
+    assert rc == 0 and pl.kernel == L.KERNEL_TCGEN05
+    rc, pl = _plan(_params(**dict(kw, alibi_slopes=256)))
     assert rc == 0 and pl.kernel == L.KERNEL_MMA

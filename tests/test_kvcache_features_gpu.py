@@ -237,6 +237,18 @@ def test_chunked_prefill_against_cache_runs_on_tcgen05(page, dtype):
                                        block_table=None if bt is None else bt.cuda(), softmax_scale=d ** -0.5,
                                        causal=True, return_plan=True)
     assert plan.kernel == L.KERNEL_TCGEN05
+    if not page:  # the cache rows of the batch entries picked by cache_batch_idx (a cache with more rows than the batch)
+        idx = torch.tensor([6, 0, 3, 5, 1], dtype=torch.int32)
+        big_k, big_v = U.normal((7, s_cache, hk, d), dtype, g), U.normal((7, s_cache, hk, d), dtype, g)
+        out, lse, go, gl = _run_both(q, big_k, big_v, None, None, lens, idx=idx, causal=True)
+        U.check_rules(out, lse, go, gl, tag="chunked prefill cache_batch_idx")
+        kn, vn = U.normal((b, s_q, hk, d), dtype, g), U.normal((b, s_q, hk, d), dtype, g)
+        lens2 = torch.tensor([333, 1000, 77, 0, 1025], dtype=torch.int32)
+        out, lse, go, gl = _run_both(q, big_k, big_v, kn, vn, lens2, idx=idx, causal=True)  # + append (bit-exact cache check inside)
+        U.check_rules(out, lse, go, gl, tag="chunked prefill cache_batch_idx + append")
+        _, _, plan = ops.attention_forward(q.cuda(), big_k.cuda(), big_v.cuda(), seqused_k=lens.cuda(), cache_batch_idx=idx.cuda(),
+                                           softmax_scale=d ** -0.5, causal=True, return_plan=True)
+        assert plan.kernel == L.KERNEL_TCGEN05
     # a sliding window on top: the window rule needs the longest key length, which only the device knows here, so
     # the general kernel takes this one
     out, lse, go, gl = _run_both(q, kc, vc, None, None, lens, bt=bt, causal=True, window=(300, 0))
