@@ -167,7 +167,10 @@ bool tc5_eligible(const fa_fwd_params& a, bool is_causal, bool is_local, int wl_
   // new tokens (and rotary) are served by a prologue launch in front of the kernel; they need the cache lengths
   if ((a.k_new || a.rotary_cos) && (!a.seqused_k || !a.k_new || !a.v_new)) return false;
   if (a.alibi_slopes || (a.cache_batch_idx && !a.seqused_k)) return false;
-  if (a.softcap > 0.f || a.partial_out || a.kv_total > 0 || wl_on_device) return false;
+  // A left window that may cover every key of the batch (the rule that turns it into "causal" needs the longest
+  // cache length, known on the device only) is simply kept as a window here: the mask is the same either way.
+  (void)wl_on_device;
+  if (a.softcap > 0.f || a.partial_out || a.kv_total > 0) return false;
   // TMA: 16-byte aligned bases and strides
   auto al = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; };
   if (!al(a.q) || !al(a.k) || !al(a.v) || !al(a.o)) return false;

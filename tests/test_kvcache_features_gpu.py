@@ -249,10 +249,15 @@ def test_chunked_prefill_against_cache_runs_on_tcgen05(page, dtype):
         _, _, plan = ops.attention_forward(q.cuda(), big_k.cuda(), big_v.cuda(), seqused_k=lens.cuda(), cache_batch_idx=idx.cuda(),
                                            softmax_scale=d ** -0.5, causal=True, return_plan=True)
         assert plan.kernel == L.KERNEL_TCGEN05
-    # a sliding window on top: the window rule needs the longest key length, which only the device knows here, so
-    # the general kernel takes this one
-    out, lse, go, gl = _run_both(q, kc, vc, None, None, lens, bt=bt, causal=True, window=(300, 0))
-    U.check_rules(out, lse, go, gl, tag=f"chunked prefill window page={page}")
+    # a sliding window on top, narrower and wider than every cache length (the rule that turns a window covering all
+    # keys into "causal" needs the longest length, which only the device knows: the kernel keeps the window)
+    for wl in (300, 5000):
+        out, lse, go, gl = _run_both(q, kc, vc, None, None, lens, bt=bt, causal=True, window=(wl, 0))
+        U.check_rules(out, lse, go, gl, tag=f"chunked prefill window {wl} page={page}")
+    _, _, plan = ops.attention_forward(q.cuda(), kc.cuda(), vc.cuda(), seqused_k=lens.cuda(),
+                                       block_table=None if bt is None else bt.cuda(), softmax_scale=d ** -0.5,
+                                       causal=True, window_left=300, window_right=0, return_plan=True)
+    assert plan.kernel == L.KERNEL_TCGEN05 and plan.is_local == 1
 
 
 @pytest.mark.parametrize("page", [0, 128, 256])
