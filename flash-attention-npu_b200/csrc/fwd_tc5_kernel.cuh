@@ -2,7 +2,8 @@
 // streamed by TMA through a shared-memory ring, online softmax in registers (one thread per
 // query row), persistent CTAs.
 //
-// It replaces, for dense / varlen prefill, the cube+vector pipeline of the reference kernel
+// It replaces, for prefill (dense, packed varlen, or many query tokens against a KV cache, paged or
+// not), the cube+vector pipeline of the reference kernel
 // (csrc/arch22/flash_attn_npu_v2/mha_fwd_kvcache.cpp:632-965: QK -> online softmax -> PV ->
 // rescale O, with S / P / O_tmp round-tripping through a global workspace).  Here S, P and O never
 // leave the SM: S and O live in TMEM, P goes through shared memory (16-bit, the layout of an MMA
