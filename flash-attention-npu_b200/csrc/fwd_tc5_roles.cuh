@@ -33,6 +33,7 @@ __device__ __forceinline__ void producer_loop(const Tc5Params& p, const CUtensor
   uint32_t q_cnt[2] = {0, 0};
   const bool varlen_q = p.a.cu_seqlens_q != nullptr, varlen_k = p.a.cu_seqlens_k != nullptr;
   const int lane = threadIdx.x & 31;
+  const uint64_t q_policy = l2_policy_evict_first();  // Q is read once
   const int pages_per_seq = p.a.block_table ? ceil_div(p.a.seqlen_k, p.a.page_size) : 0;  // entries per block-table row
   TileSched sched(p);
   for (int n = sched.first(); n < p.total_tiles; n = sched.next()) {
@@ -49,8 +50,8 @@ __device__ __forceinline__ void producer_loop(const Tc5Params& p, const CUtensor
       const int bq = varlen_q ? 0 : ti.bi;
       if (elect_one()) {
         mbar_arrive_expect_tx(full, kTileBytes);
-        tma_load_4d(q_smem + t * kTileBytes, tm_q, full, 0, ti.hh, row, bq);
-        tma_load_4d(q_smem + t * kTileBytes + kHalfBytes, tm_q, full, 64, ti.hh, row, bq);
+        tma_load_4d_hint(q_smem + t * kTileBytes, tm_q, full, 0, ti.hh, row, bq, q_policy);
+        tma_load_4d_hint(q_smem + t * kTileBytes + kHalfBytes, tm_q, full, 64, ti.hh, row, bq, q_policy);
       }
       __syncwarp();
       FA_TR(tr, 40 + t);

@@ -339,7 +339,7 @@ __device__ __forceinline__ void correction_loop(const Tc5Params& p, Barriers* ba
             w.y = pack2<T>(__uint_as_float(a[e + 2]) * inv, __uint_as_float(a[e + 3]) * inv);
             w.z = pack2<T>(__uint_as_float(a[e + 4]) * inv, __uint_as_float(a[e + 5]) * inv);
             w.w = pack2<T>(__uint_as_float(a[e + 6]) * inv, __uint_as_float(a[e + 7]) * inv);
-            *reinterpret_cast<uint4*>(o_ptr + half * 64 + e) = w;
+            __stcs(reinterpret_cast<uint4*>(o_ptr + half * 64 + e), w);  // written once, read by nobody here: streaming
           }
 #pragma unroll
           for (int e = 0; e < 32; e += 8) {
@@ -348,7 +348,7 @@ __device__ __forceinline__ void correction_loop(const Tc5Params& p, Barriers* ba
             w.y = pack2<T>(__uint_as_float(b[e + 2]) * inv, __uint_as_float(b[e + 3]) * inv);
             w.z = pack2<T>(__uint_as_float(b[e + 4]) * inv, __uint_as_float(b[e + 5]) * inv);
             w.w = pack2<T>(__uint_as_float(b[e + 6]) * inv, __uint_as_float(b[e + 7]) * inv);
-            *reinterpret_cast<uint4*>(o_ptr + half * 64 + 32 + e) = w;
+            __stcs(reinterpret_cast<uint4*>(o_ptr + half * 64 + 32 + e), w);
           }
         }
         if (half == 0) {
