@@ -3,9 +3,11 @@
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--workload c2|c3|c4|c5] [--impl reference]
 
-Prints ONE JSON line (rank 0).  Default workload: the causal-prefill configuration the headline
-metric is quoted on (bf16, batch 4, seqlen 4096, 32 heads, head dim 128).  A "step" is one forward
-over one batch of seeded synthetic inputs.
+Prints ONE JSON line (rank 0).  The headline (metric, value, ...) is the causal-prefill configuration the
+metric's TFLOP/s half is quoted on (c2: bf16, batch 4, seqlen 4096, 32 heads, head dim 128); the decode half of
+the metric (HBM GB/s on c3 contiguous decode, c4 paged windowed decode and c5 long-context sequence-sharded
+decode) is measured in the same run and reported, entry by entry with the same keys, under "workloads".
+--workload X measures X alone.  A "step" is one forward over one batch of seeded synthetic inputs.
 
 * value        whole-job throughput with inputs resident in HBM, timed with CUDA events on the
                launching stream (barrier + synchronize on both sides, max over ranks).
@@ -121,7 +123,15 @@ def _pin(t):
     return t.cpu().pin_memory()
 
 
-class Prefill:
+class Workload:
+    def release(self):
+        """Drops what must not outlive the measurement (captured graphs and the tensors they own)."""
+        for name in ("graph", "g_out", "host_pipe"):
+            if getattr(self, name, None) is not None:
+                setattr(self, name, None)
+
+
+class Prefill(Workload):
     """c2: causal prefill, bf16, batch 4, seqlen 4096, 32 heads (MHA), head dim 128."""
     name, metric, unit, bound = "c2_causal_prefill_b4_s4096_h32_d128", "attn_fwd_causal_prefill_tflops", "TFLOP/s", "tensor"
     b, s, h, d = 4, 4096, 32, 128
@@ -214,7 +224,7 @@ class PrefillBackward(Prefill):
         return done, t_total, f"{n} slices of (batch 1, 4 heads, seqlen {self.s}, d {self.d}) causal backward, bf16"
 
 
-class DecodeBase:
+class DecodeBase(Workload):
     metric, unit, bound = "kv_decode_hbm_gbs", "GB/s", "hbm"
     scale = 1e-9
 
@@ -306,20 +316,27 @@ class DecodeContiguous(DecodeBase):
         self.hl.copy_(lse, non_blocking=True)
 
     def cpu_sample(self, budget_s):
+        """Oracle on sequences of this configuration generated on the host (same shapes, distributions and length
+        range as setup(); the device is not touched)."""
         from oracle import api as OA
+        g = torch.Generator().manual_seed(3)
+        inv = 10000.0 ** (-torch.arange(0, 128, 2, dtype=torch.float32) / 128)
+        ang = torch.arange(8192, dtype=torch.float32).view(-1, 1) * inv.view(1, -1)
+        cos, sin = torch.cos(ang).to(BF), torch.sin(ang).to(BF)
         done, t_total, n = 0.0, 0.0, 0
-        lens = self.lens.cpu()
-        cos, sin = self.cos.cpu(), self.sin.cpu()
         while t_total < budget_s and n < self.b:
-            kc, vc = self.kc[n:n + 1].cpu(), self.vc[n:n + 1].cpu()
-            q, kn, vn = self.q[n:n + 1].cpu(), self.kn[n:n + 1].cpu(), self.vn[n:n + 1].cpu()
+            kc = torch.randn((1, self.s_cache, self.hk, self.d), generator=g).to(BF)
+            vc = torch.randn((1, self.s_cache, self.hk, self.d), generator=g).to(BF)
+            q = torch.randn((1, 1, self.h, self.d), generator=g).to(BF)
+            kn, vn = [torch.randn((1, 1, self.hk, self.d), generator=g).to(BF) for _ in range(2)]
+            lens = torch.randint(1024, 8192, (1,), generator=g, dtype=torch.int32)
             t0 = time.perf_counter()
-            OA.flash_attn_with_kvcache(q, kc, vc, kn, vn, rotary_cos=cos, rotary_sin=sin, cache_seqlens=lens[n:n + 1],
+            OA.flash_attn_with_kvcache(q, kc, vc, kn, vn, rotary_cos=cos, rotary_sin=sin, cache_seqlens=lens,
                                        causal=True, rotary_interleaved=False)
             t_total += time.perf_counter() - t0
-            done += (int(lens[n]) + 1) * self.hk * self.d * 4
+            done += (int(lens[0]) + 1) * self.hk * self.d * 4
             n += 1
-        return done, t_total, f"first {n} of {self.b} sequences (K/V bytes attended)"
+        return done, t_total, f"{n} sequences of the configuration, one at a time (K/V bytes attended)"
 
 
 class DecodePaged(DecodeBase):
@@ -343,18 +360,23 @@ class DecodePaged(DecodeBase):
                                            causal=True, window_size=(4096, 0), return_softmax_lse=True)
 
     def cpu_sample(self, budget_s):
+        """Oracle on sequences of this configuration generated on the host: each with its own 128 pages in a
+        permuted block table (the device is not touched)."""
         from oracle import api as OA
+        g = torch.Generator().manual_seed(4)
         done, t_total, n = 0.0, 0.0, 0
-        kp, vp, bt, lens = self.kp.cpu(), self.vp.cpu(), self.bt.cpu(), self.lens.cpu()
         while t_total < budget_s and n < self.b:
-            q = self.q[n:n + 1].cpu()
+            kp = torch.randn((128, self.page, self.hk, self.d), generator=g).to(BF)
+            vp = torch.randn((128, self.page, self.hk, self.d), generator=g).to(BF)
+            bt = torch.randperm(128, generator=g).view(1, 128).to(torch.int32)
+            lens = torch.randint(512, 32769, (1,), generator=g, dtype=torch.int32)
+            q = torch.randn((1, self.s_q, self.h, self.d), generator=g).to(BF)
             t0 = time.perf_counter()
-            OA.flash_attn_with_kvcache(q, kp, vp, cache_seqlens=lens[n:n + 1], block_table=bt[n:n + 1], causal=True,
-                                       window_size=(4096, 0))
+            OA.flash_attn_with_kvcache(q, kp, vp, cache_seqlens=lens, block_table=bt, causal=True, window_size=(4096, 0))
             t_total += time.perf_counter() - t0
-            done += min(int(lens[n]), 4096 + self.s_q) * self.hk * self.d * 4
+            done += min(int(lens[0]), 4096 + self.s_q) * self.hk * self.d * 4
             n += 1
-        return done, t_total, f"first {n} of {self.b} sequences (in-window K/V bytes; the golden reads whole sequences)"
+        return done, t_total, f"{n} sequences of the configuration, one at a time (in-window K/V bytes; the golden reads whole sequences)"
 
 
 class DecodeLongSharded(DecodeBase):
@@ -382,9 +404,13 @@ class DecodeLongSharded(DecodeBase):
         return D.sharded_decode(q, self.kc, self.vc, kv_pos_offset=self.lo, kv_total=self.L, causal=True)
 
     def cpu_sample(self, budget_s):
+        """Oracle on the first 16384 keys of one sequence of this configuration, generated on the host."""
         from oracle import api as OA
         n_tok = 16384
-        kc, vc, q = self.kc[:1, :n_tok].cpu(), self.vc[:1, :n_tok].cpu(), self.q[:1].cpu()
+        g = torch.Generator().manual_seed(5)
+        kc = torch.randn((1, n_tok, self.hk, self.d), generator=g).to(BF)
+        vc = torch.randn((1, n_tok, self.hk, self.d), generator=g).to(BF)
+        q = torch.randn((1, 1, self.h, self.d), generator=g).to(BF)
         done, t_total, n = 0.0, 0.0, 0
         while t_total < budget_s and n < 8:
             t0 = time.perf_counter()
@@ -392,7 +418,7 @@ class DecodeLongSharded(DecodeBase):
             t_total += time.perf_counter() - t0
             done += n_tok * self.hk * self.d * 4
             n += 1
-        return done, t_total, f"{n} passes over the first {n_tok} keys of sequence 0"
+        return done, t_total, f"{n} passes over {n_tok} keys of one sequence"
 
 
 WORKLOADS = {"c2": Prefill, "c2_bwd": PrefillBackward, "c3": DecodeContiguous, "c4": DecodePaged, "c5": DecodeLongSharded}
@@ -401,112 +427,98 @@ WORKLOADS = {"c2": Prefill, "c2_bwd": PrefillBackward, "c3": DecodeContiguous, "
 # ------------------------------------------------------------------------------------------------
 # driver
 # ------------------------------------------------------------------------------------------------
+HEADLINE = "c2"
+DECODE_HALF = ("c3", "c4", "c5")  # the decode half of the metric: entries of the default line's "workloads" object
+DEFAULT_STEPS = {"c2": (20, 5), "c2_bwd": (10, 3)}  # (steps, warm-up); decode steps are 0.1-0.6 ms, so they run (200, 50)
+
+
+def _cpu_entry(wl, budget, repeats=1, warm=False):
+    """The CPU oracle (a port of the reference's PyTorch golden) on all host cores, on a bounded sample."""
+    torch.set_num_threads(os.cpu_count() or 1)
+    if warm:
+        wl.cpu_sample(min(0.5, budget))
+    done, secs, sample = 0.0, 0.0, ""
+    for _ in range(repeats):
+        d, t, sample = wl.cpu_sample(budget)
+        done += d
+        secs += t
+    val = done / secs * wl.scale
+    return {"value": val, "unit": wl.unit, "cores": torch.get_num_threads(), "kind": "port",
+            "sample": sample + (f", x{repeats} steps" if repeats > 1 else ""), "seconds": secs}
+
+
 def run_reference(args, rank, world):
     """--impl reference: the reference's CPU implementation of the path (its PyTorch golden, here the
-    oracle port -- the reference's native code needs the Ascend toolchain) on the host cores."""
+    oracle port -- the reference's native code needs the Ascend toolchain) on the host cores, on the same
+    workloads as the default arm: the prefill configuration as the headline, the decode configurations under
+    "workloads".  Every step is a bounded sample of its workload; nothing here touches a GPU."""
     if rank != 0:
         return
-    torch.set_num_threads(os.cpu_count() or 1)
-    # The CPU arm always times the prefill configuration (the headline metric); the decode workloads
-    # build multi-GiB caches on the device and have their own cpu_baseline leg in the default arm.
-    target = Prefill()
-    budget = 2.0
-    if args.warmup > 0:
-        target.cpu_sample(0.5)
-    done, secs, sample = 0.0, 0.0, ""
-    for _ in range(args.steps):
-        d, s, sample = target.cpu_sample(budget)
-        done += d
-        secs += s
-    val = done / secs * target.scale
-    line = {"impl": "reference", "metric": target.metric, "value": val, "unit": target.unit, "n_gpus": args.gpus,
-            "steps": args.steps, "warmup": args.warmup, "ms_per_step": secs / args.steps * 1e3,
-            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-            "config": {"workload": target.name, "note": "CPU golden (oracle port) on host cores; each step a bounded sample"},
-            "cpu_baseline": {"value": val, "unit": target.unit, "cores": torch.get_num_threads(), "kind": "port",
-                             "sample": sample + f", x{args.steps} steps"},
-            "e2e": {"value": val, "unit": target.unit, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
-            "gpu_launches": 0}
+    keys = [args.workload] if args.workload else [HEADLINE] + list(DECODE_HALF)
+    entries = {}
+    for key in keys:
+        wl = WORKLOADS[key]()
+        budget = 2.0 if key == keys[0] else max(1.0, 8.0 / max(args.steps, 1))
+        cb = _cpu_entry(wl, budget, repeats=args.steps, warm=args.warmup > 0)
+        entries[key] = {"impl": "reference", "metric": wl.metric, "value": cb["value"], "unit": wl.unit,
+                        "steps": args.steps, "warmup": args.warmup, "ms_per_step": cb["seconds"] / args.steps * 1e3,
+                        "config": {"workload": wl.name}, "cpu_baseline": cb,
+                        "e2e": {"value": cb["value"], "unit": wl.unit, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+                        "gpu_launches": 0}
+    first = entries[keys[0]]
+    line = dict(first)
+    line.update({"n_gpus": args.gpus, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+                 "data": "synthetic"})
+    line["config"] = {"workload": first["config"]["workload"],
+                      "note": "CPU golden (oracle port) on host cores; each step a bounded sample"}
+    if len(keys) > 1:
+        line["workloads"] = {k: entries[k] for k in keys[1:]}
     print(json.dumps(line))
 
 
-def main():
-    ap = argparse.ArgumentParser()
-    ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=None, help="default: 20 (c2), 10 (c2_bwd), 200 (decode workloads)")
-    ap.add_argument("--warmup", type=int, default=None, help="default: 5 (c2), 3 (c2_bwd), 50 (decode workloads)")
-    ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS))
-    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
-    ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--cpu-budget", type=float, default=12.0)
-    ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (profiling runs)")
-    ap.add_argument("--shrink", type=int, default=1,
-                    help="divide the batch (c2-c4) or the key length (c5) by this factor: small cases for ncu captures")
-    args = ap.parse_args()
-    # A decode step is ~0.1-0.6 ms: a handful of them ends before the clocks have risen, so those workloads run more.
-    d_steps, d_warm = {"c2": (20, 5), "c2_bwd": (10, 3)}.get(args.workload, (200, 50))
-    args.steps = d_steps if args.steps is None else args.steps
-    args.warmup = d_warm if args.warmup is None else args.warmup
-    rank = int(os.environ.get("RANK", "0"))
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
-    if args.impl == "reference":
-        run_reference(args, rank, world)
-        return
-    if not torch.cuda.is_available():
-        raise SystemExit("bench.py needs a CUDA device (there is no CPU implementation of the product path)")
-    args.warmup = max(args.warmup, 3)
-    torch.cuda.set_device(local_rank)
-    dev = torch.device("cuda", local_rank)
+def measure(key, args, steps, warmup, dev, rank, world, local_rank, peaks, barrier, cpu_budget):
+    """Sets one workload up, times it (device-resident and end to end) and returns its result object (rank 0)
+    or None (other ranks).  Every rank runs the same sequence of steps: c5 has a collective in each."""
     import torch.distributed as dist
-    if world > 1:
-        dist.init_process_group("nccl", device_id=dev)
-
-    def barrier():
-        if world > 1:
-            dist.barrier()
-        torch.cuda.synchronize()
-
-    wl = WORKLOADS[args.workload]()
+    from flash_b200 import lib as _L
+    wl = WORKLOADS[key]()
     if args.shrink > 1:
-        if args.workload == "c5":
+        if key == "c5":
             wl.L //= args.shrink
         else:
             wl.b = max(1, wl.b // args.shrink)
-        if args.workload == "c4":
+        if key == "c4":
             wl.nblk = wl.b * 128
         wl.name += f"_shrunk{args.shrink}"
     wl.setup(dev, rank, world)
-    peaks = load_peaks()
 
     # ---- device-resident timing ----
-    for _ in range(args.warmup):
+    for _ in range(warmup):
         wl.step()
     barrier()
     sampler = ClockSampler(local_rank)
     if rank == 0:
         sampler.start()
     stream = torch.cuda.current_stream()
-    ev = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps + 1)]
+    ev = [torch.cuda.Event(enable_timing=True) for _ in range(steps + 1)]
     barrier()
-    from flash_b200 import lib as _L
     launches0 = _L.load().fa_b200_launch_count() + getattr(wl, "replayed_launches", 0)
     ev[0].record(stream)
-    for i in range(args.steps):
+    for i in range(steps):
         wl.step()
         ev[i + 1].record(stream)
     # counted by the library (eager calls) or during the capture of the replayed graph, not assumed
     gpu_launches = int(_L.load().fa_b200_launch_count() + getattr(wl, "replayed_launches", 0) - launches0)
     barrier()
     total_ms = ev[0].elapsed_time(ev[-1])
-    per = sorted(ev[i].elapsed_time(ev[i + 1]) for i in range(args.steps))
+    per = sorted(ev[i].elapsed_time(ev[i + 1]) for i in range(steps))
     # Keep the GPU busy a little longer so the clock sampler sees load even for short runs.  The
     # number of extra steps is derived from the rank-reduced time, so every rank runs the same count
     # (a workload with a collective would deadlock otherwise).
     t0 = torch.tensor([total_ms], dtype=torch.float64, device=dev)
     if world > 1:
         dist.all_reduce(t0, op=dist.ReduceOp.MAX)
-    n_extra = int(min(2000, 600.0 / max(float(t0[0]) / args.steps, 1e-3))) if args.steps > 2 else 0
+    n_extra = int(min(2000, 600.0 / max(float(t0[0]) / steps, 1e-3))) if steps > 2 else 0
     for _ in range(n_extra):
         wl.step()
     barrier()
@@ -522,7 +534,7 @@ def main():
         barrier()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record(stream)
-        for _ in range(args.steps):
+        for _ in range(steps):
             wl.step_e2e()
         e1.record(stream)
         barrier()
@@ -537,52 +549,119 @@ def main():
         total_ms, e2e_ms, units_all = float(tmax[0]), float(tmax[1]), float(tsum[2])
     else:
         units_all = wl.units
+    used_graph = getattr(wl, "graph", None) is not None
+    entry = None
     if rank == 0:
-        value = units_all * args.steps / (total_ms * 1e-3) * wl.scale
-        e2e = units_all * args.steps / (e2e_ms * 1e-3) * wl.scale
-        med_ms = per[len(per) // 2]
-        achieved = wl.units / (total_ms / args.steps * 1e-3) * wl.scale
+        value = units_all * steps / (total_ms * 1e-3) * wl.scale
+        e2e = units_all * steps / (e2e_ms * 1e-3) * wl.scale
+        achieved = wl.units / (total_ms / steps * 1e-3) * wl.scale
         if wl.bound == "tensor":
             peak = peaks["bf16_tflops"] if total_ms < 1000 else peaks.get("bf16_tflops_sustained", peaks["bf16_tflops"])
             runit = "TFLOP/s"
         else:
             peak, runit = peaks["hbm_gbs"], "GB/s"
-        strong = getattr(wl, "strong", False)
         traffic, traffic_src = None, None
-        if args.workload in NCU_TRAFFIC:
-            t_bytes, t_units, traffic_src = NCU_TRAFFIC[args.workload]
+        if key in NCU_TRAFFIC:
+            t_bytes, t_units, traffic_src = NCU_TRAFFIC[key]
             traffic = t_bytes * wl.units / t_units
-        line = {
-            "metric": wl.metric, "value": value, "unit": wl.unit, "n_gpus": world, "steps": args.steps,
-            "warmup": args.warmup, "ms_per_step": total_ms / args.steps, "higher_is_better": True,
-            "scaling": "strong" if strong else "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-            "config": {"workload": wl.name, "l2": "inputs larger than L2 (no flush needed)" if not args.workload.startswith("c2")
-                       else "q+k+v+o = 537 MB per step, larger than the 126 MB L2", "median_ms_per_step": med_ms,
-                       "per_gpu_units": wl.units, "cuda_graph": getattr(wl, "graph", None) is not None},
+        entry = {
+            "metric": wl.metric, "value": value, "unit": wl.unit, "n_gpus": world, "steps": steps,
+            "warmup": warmup, "ms_per_step": total_ms / steps, "higher_is_better": True,
+            "scaling": "strong" if getattr(wl, "strong", False) else "weak", "vs_baseline": None, "dtype": "bf16",
+            "data": "synthetic",
+            "config": {"workload": wl.name, "l2": "inputs larger than L2 (no flush needed)" if not key.startswith("c2")
+                       else "q+k+v+o = 537 MB per step, larger than the 126 MB L2", "median_ms_per_step": per[len(per) // 2],
+                       "per_gpu_units": wl.units, "cuda_graph": used_graph},
             "roofline": {"bound": wl.bound, "achieved": achieved, "peak": peak, "unit": runit,
                          "frac": achieved / peak, "traffic": traffic, "traffic_unit": "bytes per launch",
                          "traffic_source": traffic_src, "peak_source": peaks["_source"],
-                         "per_launch": "one attention launch per step" + (" (+ merge)" if gpu_launches > args.steps else "")},
+                         "per_launch": "one attention launch per step" + (" (+ merge)" if gpu_launches > steps else "")},
             "e2e": {"value": e2e, "unit": wl.unit, "h2d_bytes_per_step": wl.h2d, "d2h_bytes_per_step": wl.d2h},
             "gpu_launches": gpu_launches,
             "clocks": clocks,
         }
+        if wl.bound == "hbm":  # the north star quotes the decode target against the nominal 8 TB/s too
+            entry["roofline"]["frac_of_nominal_8tbs"] = achieved / 8000.0
         if not args.no_cpu_baseline and world == 1:
-            torch.set_num_threads(os.cpu_count() or 1)
-            done, secs, sample = wl.cpu_sample(args.cpu_budget)
-            line["cpu_baseline"] = {"value": done / secs * wl.scale, "unit": wl.unit, "cores": torch.get_num_threads(),
-                                    "kind": "port", "sample": sample, "seconds": secs}
+            entry["cpu_baseline"] = _cpu_entry(wl, cpu_budget)
+    # A captured graph holds NCCL kernels, and the communicator cannot be torn down while such a graph is alive:
+    # release it (and the tensors captured with it) here, with the stream idle.
+    wl.release()
+    del wl
+    torch.cuda.synchronize()
+    torch.cuda.empty_cache()
+    return entry
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=None, help="default: 20 (c2), 10 (c2_bwd), 200 (decode workloads)")
+    ap.add_argument("--warmup", type=int, default=None, help="default: 5 (c2), 3 (c2_bwd), 50 (decode workloads)")
+    ap.add_argument("--workload", default=None, choices=sorted(WORKLOADS),
+                    help="one workload only; default: c2 as the headline plus c3, c4, c5 under \"workloads\"")
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--cpu-budget", type=float, default=12.0)
+    ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (profiling runs)")
+    ap.add_argument("--shrink", type=int, default=1,
+                    help="divide the batch (c2-c4) or the key length (c5) by this factor: small cases for ncu captures")
+    args = ap.parse_args()
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    head_key = args.workload or HEADLINE
+    if args.impl == "reference":
+        d_steps, d_warm = DEFAULT_STEPS.get(head_key, (20, 5))
+        args.steps = min(d_steps, 20) if args.steps is None else args.steps
+        args.warmup = d_warm if args.warmup is None else args.warmup
+        run_reference(args, rank, world)
+        return
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device (there is no CPU implementation of the product path)")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    import torch.distributed as dist
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    peaks = load_peaks()
+
+    def counts(key, is_head):
+        d_steps, d_warm = DEFAULT_STEPS.get(key, (200, 50))
+        # --steps / --warmup are the headline's; a decode step is so short that fewer than its default count would
+        # end before the clocks have risen, so the entries under "workloads" keep their own counts
+        steps = args.steps if (is_head and args.steps is not None) else d_steps
+        warm = args.warmup if (is_head and args.warmup is not None) else d_warm
+        return steps, max(warm, 3)
+
+    steps, warm = counts(head_key, True)
+    line = measure(head_key, args, steps, warm, dev, rank, world, local_rank, peaks, barrier, args.cpu_budget)
+    if args.workload is None:
+        extra = {}
+        for key in DECODE_HALF:
+            steps, warm = counts(key, False)
+            extra[key] = measure(key, args, steps, warm, dev, rank, world, local_rank, peaks, barrier,
+                                 min(args.cpu_budget, 4.0))
+        if rank == 0:
+            line["workloads"] = extra
+    if rank == 0:
         print(json.dumps(line))
+        sys.stdout.flush()
     if world > 1:
         dist.barrier()
         torch.cuda.synchronize()
-        if getattr(wl, "graph", None) is not None:
-            # A captured graph holds NCCL kernels; tearing the communicator down under it did not return (measured:
-            # the ranks sat in destroy_process_group until killed).  Everything is done and synchronised: leave.
-            sys.stdout.flush()
-            sys.stderr.flush()
-            os._exit(0)
+        # Every captured graph was released in measure(); should the teardown still not return (it once sat in
+        # destroy_process_group until killed, with a graph of NCCL kernels alive), leave after a grace period:
+        # everything is done, printed and synchronised.
+        threading.Timer(30.0, lambda: os._exit(0)).start()
         dist.destroy_process_group()
+        os._exit(0)
 
 
 if __name__ == "__main__":

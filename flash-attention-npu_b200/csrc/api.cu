@@ -10,6 +10,7 @@
 #include <cstdio>
 #include <cstdlib>
 #include <cstring>
+#include <mutex>
 #include <string>
 
 #include "combine.cuh"
@@ -53,6 +54,8 @@ static void normalize_window(int seqlen_q, int max_k, bool causal, int& wl, int&
   is_local = (wl >= 0 || wr >= 0) && !is_causal;
 }
 
+static bool s_new_too_long(const fa_fwd_params& a) { return a.seqlen_new > a.seqlen_k; }
+
 struct Planned {
   fa_fwd_plan pl;
   KParams kp;
@@ -84,6 +87,11 @@ static int make_plan(const fa_fwd_params& a, Planned* out) {
       return fail(FA_ERR_INVALID, "rotary_dim must be divisible by 16 and at most the head dimension");
   }
   if (a.kv_total < 0 || a.kv_pos_offset < 0) return fail(FA_ERR_INVALID, "negative kv shard position");
+  if (a.kv_outer < 0) return fail(FA_ERR_INVALID, "negative kv_outer");
+  if (a.block_table && a.kv_outer <= 0) return fail(FA_ERR_INVALID, "paged KV cache needs kv_outer = the number of pages");
+  if (a.cache_batch_idx && !a.block_table && a.kv_outer <= 0)
+    return fail(FA_ERR_INVALID, "cache_batch_idx needs kv_outer = the number of cache rows");
+  if (a.seqused_k && s_new_too_long(a)) return fail(FA_ERR_INVALID, "the new tokens do not fit into the KV cache");
 
   const int s_new = a.seqlen_new;
   const int max_k_bound = a.seqlen_k + s_new;
@@ -322,6 +330,7 @@ static int run_fwd(const fa_fwd_params& a, void* workspace, size_t workspace_byt
         a2.q_row_stride = (int64_t)a.h * a.d;
         a2.q_batch_stride = (int64_t)a.seqlen_q * a.h * a.d;
       }
+      P.kp.status = device_status_word();
       cudaError_t e = launch_kv_prologue(P.kp, q_rot, P.pl.is_causal || P.pl.is_local, st);
       if (e != cudaSuccess) return fail(FA_ERR_CUDA, std::string("append prologue launch: ") + cudaGetErrorString(e));
       ++g_launches;
@@ -334,6 +343,8 @@ static int run_fwd(const fa_fwd_params& a, void* workspace, size_t workspace_byt
   }
 
   KParams& kp = P.kp;
+  kp.status = device_status_word();
+  if (!kp.status) return fail(FA_ERR_CUDA, "cannot look up the device status word");
   if (P.pl.num_splits > 1) {
     if (!workspace || workspace_bytes < P.pl.workspace_bytes) return fail(FA_ERR_WORKSPACE, "workspace missing or too small");
     if ((reinterpret_cast<uintptr_t>(workspace) & 15) != 0) return fail(FA_ERR_WORKSPACE, "workspace must be 16-byte aligned");
@@ -345,12 +356,10 @@ static int run_fwd(const fa_fwd_params& a, void* workspace, size_t workspace_byt
   cudaError_t e = cudaErrorInvalidValue;
   const bool bf = a.dtype == FA_BF16;
   if (P.pl.kernel == FA_KERNEL_DECODE) {
-    kp.status = device_status_word();
     CUtensorMap tm_k, tm_v;
     const bool paged = a.block_table != nullptr;
-    // the outer extent (cache rows / pages) is not part of the parameters; it only bounds the TMA's
-    // out-of-range check, which the kernel never relies on in that dimension
-    const int64_t rows = paged ? a.page_size : a.seqlen_k, outer = int64_t(1) << 30;
+    // true outer extent (pages / cache rows): an index outside it makes the TMA return zeros, never a wild read
+    const int64_t rows = paged ? a.page_size : a.seqlen_k, outer = a.kv_outer > 0 ? a.kv_outer : a.b;
     if (!tma_encode_rows(&tm_k, a.k, a.dtype, a.d, a.h_k, rows, outer, a.k_head_stride, a.k_row_stride, a.k_batch_stride, P.pl.block_n) ||
         !tma_encode_rows(&tm_v, a.v, a.dtype, a.d, a.h_k, rows, outer, a.v_head_stride, a.v_row_stride, a.v_batch_stride, P.pl.block_n))
       return fail(FA_ERR_CUDA, "cuTensorMapEncodeTiled failed for the KV cache");
@@ -416,8 +425,10 @@ static __device__ __align__(256) unsigned char g_noalloc_scratch[kNoAllocScratch
 
 static int noalloc_scratch_ptr(void** out) {
   static void* ptrs[64] = {nullptr};
+  static std::mutex mu;  // calls may come from several host threads
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return fail(FA_ERR_CUDA, "cannot query the current device");
+  std::lock_guard<std::mutex> lock(mu);
   if (!ptrs[dev]) {
     void* ptr = nullptr;
     cudaError_t e = cudaGetSymbolAddress(&ptr, g_noalloc_scratch);
@@ -495,6 +506,9 @@ int fa_b200_check_status(void* stream) {
   const int v = fa::tc5_read_status(reinterpret_cast<cudaStream_t>(stream));
   if (v == 0) return FA_OK;
   if (v < 0) return fa::fail(FA_ERR_CUDA, "cannot read the device status word");
+  if (v & fa::kStatusBadIndex)
+    return fa::fail(FA_ERR_INVALID, "a block_table / cache_batch_idx entry or a cache length was out of range "
+                                    "(the kernels read zeros instead; results of that launch are invalid)");
   if (v & 0x40000000)
     return fa::fail(FA_ERR_CUDA, "a bounded device-side wait gave up in CTA " + std::to_string(v & 0xffffff) +
                                      " of the decode kernel (results of that launch are invalid)");

@@ -34,6 +34,42 @@ struct KParams {
 
 __host__ __device__ inline int ceil_div(int a, int b) { return (a + b - 1) / b; }
 
+// ---- index tensors are never trusted ----
+// A stale block_table / cache_batch_idx entry or a cache length beyond the cache's capacity must not become a wild
+// access: the value is clamped (plain loads / stores) or handed to the TMA unit, whose tensor maps carry the true
+// extents and return zeros outside them, and this bit is raised in the device status word for
+// fa_b200_check_status.  The reference validates these on the host after a device-to-host copy
+// (csrc/arch22/flash_attn_npu_v2/flash_api.cpp:459); here the lengths stay on the device.
+constexpr int kStatusBadIndex = 0x10000000;
+__device__ __forceinline__ void raise_bad_index(int32_t* status) {
+  if (status) atomicOr(status, kStatusBadIndex);
+}
+// Keys already held by batch entry bi of a KV cache, clamped to [0, capacity - s_new].
+__device__ __forceinline__ int cache_len(const fa_fwd_params& a, int bi, int32_t* status) {
+  int l = a.seqused_k[bi];
+  const int cap = max(a.seqlen_k - a.seqlen_new, 0);
+  if (l < 0 || l > cap) {
+    raise_bad_index(status);
+    l = min(max(l, 0), cap);
+  }
+  return l;
+}
+// Outermost k / v index (page or cache row) clamped into [0, kv_outer) for code that forms addresses from it.
+__device__ __forceinline__ int outer_index(const fa_fwd_params& a, int idx, int32_t* status) {
+  const int n = a.kv_outer > 0 ? a.kv_outer : a.b;
+  if ((unsigned)idx >= (unsigned)n) {
+    raise_bad_index(status);
+    idx = min(max(idx, 0), n - 1);
+  }
+  return idx;
+}
+// Same check for an index that goes into a TMA coordinate: out-of-range values are kept (the copy then
+// returns zeros), only the status bit is raised.
+__device__ __forceinline__ void check_outer_index(const fa_fwd_params& a, int idx, int32_t* status) {
+  const int n = a.kv_outer > 0 ? a.kv_outer : a.b;
+  if ((unsigned)idx >= (unsigned)n) raise_bad_index(status);
+}
+
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
   return static_cast<uint32_t>(__cvta_generic_to_shared(p));
 }

@@ -117,6 +117,7 @@ __device__ __forceinline__ bool decode_producer(const KParams& p, const SeqView<
       const int pg = t0 / p.a.page_size;
       row = t0 - pg * p.a.page_size;
       outer = __ldg(sv.pages + pg);
+      check_outer_index(p.a, outer, p.status);  // out of range: the TMA returns zeros, the status word says so
     }
     if (tc5::elect_one()) {
       tc5::mbar_arrive_expect_tx(full, Tr::STAGE_BYTES);

@@ -47,7 +47,7 @@ fwd_decode_kernel(const __grid_constant__ KParams p, const __grid_constant__ CUt
 
   // KV block range [nb_lo, nb_hi) that the queries of batch entry bi can see (all heads alike).
   auto batch_range = [&](int bi, int q_len, int& nb_lo, int& nb_hi) {
-    const int l_cache = p.a.seqused_k ? p.a.seqused_k[bi] : p.a.seqlen_k;
+    const int l_cache = p.a.seqused_k ? cache_len(p.a, bi, p.status) : p.a.seqlen_k;
     const int k_len = l_cache + p.a.seqlen_new;
     const int koff = (p.a.kv_total > 0 ? p.a.kv_total - p.a.kv_pos_offset : k_len) - q_len;
     const int i_max = q_len - 1;
@@ -203,7 +203,7 @@ fwd_decode_kernel(const __grid_constant__ KParams p, const __grid_constant__ CUt
     }
     sv.q_row0 = q_row0;
     sv.q = reinterpret_cast<const T*>(p.a.q) + (int64_t)bi * p.a.q_batch_stride + (int64_t)q_row0 * p.a.q_row_stride;
-    sv.l_cache = p.a.seqused_k ? p.a.seqused_k[bi] : p.a.seqlen_k;
+    sv.l_cache = p.a.seqused_k ? cache_len(p.a, bi, p.status) : p.a.seqlen_k;
     sv.k_len = sv.l_cache + p.a.seqlen_new;
     const T* kb = reinterpret_cast<const T*>(p.a.k) + (int64_t)hk * p.a.k_head_stride;
     const T* vb = reinterpret_cast<const T*>(p.a.v) + (int64_t)hk * p.a.v_head_stride;
@@ -211,7 +211,7 @@ fwd_decode_kernel(const __grid_constant__ KParams p, const __grid_constant__ CUt
     if (p.a.block_table) {
       sv.pages = p.a.block_table + (int64_t)bi * p.a.block_table_batch_stride;
     } else {
-      batch_row = p.a.cache_batch_idx ? p.a.cache_batch_idx[bi] : bi;
+      batch_row = p.a.cache_batch_idx ? outer_index(p.a, p.a.cache_batch_idx[bi], p.status) : bi;
       kb += (int64_t)batch_row * p.a.k_batch_stride;
       vb += (int64_t)batch_row * p.a.v_batch_stride;
     }

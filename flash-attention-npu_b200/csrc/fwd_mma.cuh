@@ -69,7 +69,7 @@ __device__ __forceinline__ const typename Tr::T* kv_row_ptr(const KParams& p, co
   if (pages) {
     int pg = t / p.a.page_size;
     int in = t - pg * p.a.page_size;
-    return base + (int64_t)__ldg(pages + pg) * page_stride + (int64_t)in * row_stride;
+    return base + (int64_t)outer_index(p.a, __ldg(pages + pg), p.status) * page_stride + (int64_t)in * row_stride;
   }
   return base + (int64_t)t * row_stride;
 }

@@ -46,7 +46,7 @@ __global__ void __launch_bounds__(Tr::NTHREADS) fwd_mma_kernel(const __grid_cons
       k_row0 = p.a.cu_seqlens_k[bi];
       sv.l_cache = p.a.cu_seqlens_k[bi + 1] - k_row0;
     }
-    if (p.a.seqused_k) sv.l_cache = p.a.seqused_k[bi];
+    if (p.a.seqused_k) sv.l_cache = cache_len(p.a, bi, p.status);
     sv.k_len = sv.l_cache + p.a.seqlen_new;
     const T* kb = reinterpret_cast<const T*>(p.a.k) + (int64_t)hk * p.a.k_head_stride;
     const T* vb = reinterpret_cast<const T*>(p.a.v) + (int64_t)hk * p.a.v_head_stride;
@@ -54,7 +54,7 @@ __global__ void __launch_bounds__(Tr::NTHREADS) fwd_mma_kernel(const __grid_cons
     if (p.a.block_table) {
       sv.pages = p.a.block_table + (int64_t)bi * p.a.block_table_batch_stride;
     } else {
-      const int64_t row = p.a.cache_batch_idx ? p.a.cache_batch_idx[bi] : bi;
+      const int64_t row = p.a.cache_batch_idx ? outer_index(p.a, p.a.cache_batch_idx[bi], p.status) : bi;
       kb += row * p.a.k_batch_stride + (int64_t)k_row0 * p.a.k_row_stride;
       vb += row * p.a.v_batch_stride + (int64_t)k_row0 * p.a.v_row_stride;
     }

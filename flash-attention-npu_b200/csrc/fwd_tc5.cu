@@ -16,7 +16,7 @@
 namespace fa {
 namespace tc5 {
 
-template <typename T, uint32_t AB_FMT, int POLY>
+template <typename T, uint32_t AB_FMT>
 __global__ void __launch_bounds__(kThreads, 1)
 fwd_tc5_kernel(const __grid_constant__ Tc5Params p, const __grid_constant__ CUtensorMap tm_q,
                const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v) {
@@ -56,7 +56,11 @@ fwd_tc5_kernel(const __grid_constant__ Tc5Params p, const __grid_constant__ CUte
       mbar_init(smem_addr(&bar->kv_full[s]), 1);
       mbar_init(smem_addr(&bar->kv_empty[s]), 2);
     }
+    mbar_init(smem_addr(&bar->fix_req), 2);
+    mbar_init(smem_addr(&bar->v_fixed), 1);
     bar->abort_flag = 0;
+    bar->fix_seen[0] = bar->fix_seen[1] = 0;
+    for (int i = 0; i < 8; ++i) (&bar->exp_busy[0][0])[i] = 0;
     fence_barrier_init();
   }
   if (warp == kMmaWarp) {
@@ -77,7 +81,7 @@ fwd_tc5_kernel(const __grid_constant__ Tc5Params p, const __grid_constant__ CUte
   // scores of a row plus working set, the other roles need far fewer.
   if (warp < 8) {
     asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;\n" ::"n"(kRegsSoftmax));
-    softmax_loop<T, POLY>(p, bar, tmem, p_smem, warp >> 2, warp & 3, lane);
+    softmax_loop<T>(p, bar, tmem, p_smem, warp >> 2, warp & 3, lane);
   } else if (warp < 12) {
     asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;\n" ::"n"(kRegsCorr));
     correction_loop<T>(p, bar, tmem, warp & 3, lane);
@@ -86,6 +90,7 @@ fwd_tc5_kernel(const __grid_constant__ Tc5Params p, const __grid_constant__ CUte
     // warp-uniform role code; one elected lane issues
     if (warp == kMmaWarp || warp == kMmaWarp + 1) mma_loop<AB_FMT>(p, bar, q_smem, p_smem, kv_smem, tmem, warp - kMmaWarp);
     else if (warp == kTmaWarp) producer_loop(p, &tm_q, &tm_k, &tm_v, bar, q_smem, kv_smem);
+    else tail_fix_loop(p, bar, kv_smem, lane);
   }
 
   tc_fence_before();
@@ -139,6 +144,11 @@ static bool encode_map(CUtensorMap* m, const void* ptr, int dtype, int d, int he
   return r == CUDA_SUCCESS;
 }
 
+// The status word of the bounded waits and index checks: one per device, part of the library image (no
+// allocation; 0 when the module is loaded).  In host code the symbol is only a handle; its device address is
+// looked up once per device, with that device current.
+static __device__ int32_t g_status_word;
+
 static int32_t* status_word() {
   static int32_t* words[64] = {nullptr};
   static std::mutex mu;
@@ -146,8 +156,9 @@ static int32_t* status_word() {
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
   std::lock_guard<std::mutex> lock(mu);
   if (!words[dev]) {
-    if (cudaMalloc(&words[dev], sizeof(int32_t)) != cudaSuccess) return nullptr;
-    cudaMemset(words[dev], 0, sizeof(int32_t));
+    void* ptr = nullptr;
+    if (cudaGetSymbolAddress(&ptr, g_status_word) != cudaSuccess) return nullptr;
+    words[dev] = static_cast<int32_t*>(ptr);
   }
   return words[dev];
 }
@@ -169,7 +180,9 @@ bool tc5_eligible(const fa_fwd_params& a, bool is_causal, bool is_local, int wl_
   if (a.alibi_slopes || (a.cache_batch_idx && !a.seqused_k)) return false;
   // A left window that may cover every key of the batch (the rule that turns it into "causal" needs the longest
   // cache length, known on the device only) is simply kept as a window here: the mask is the same either way.
-  (void)wl_on_device;
+  // With rotary tables the mode also decides where q is rotated (per token or all at the cache length), and the
+  // other kernels decide that on the device: such calls are left to them so that every kernel gives one answer.
+  if (wl_on_device && a.rotary_cos) return false;
   if (a.softcap > 0.f || a.partial_out || a.kv_total > 0) return false;
   // TMA: 16-byte aligned bases and strides
   auto al = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; };
@@ -219,7 +232,7 @@ int tc5_launch(const fa_fwd_params& a, const fa_fwd_plan& pl, cudaStream_t st, s
   p.m_tiles = pl.m_blocks;
   p.total_tiles = pl.m_blocks * a.b * a.h;
   p.scale_log2 = a.softmax_scale * kLog2e;
-  p.rescale_threshold = 0.f;
+  p.fix_tail = (a.seqused_k || a.cu_seqlens_k) ? 1 : 0;
   {
     // L2 chunks of the tile order (tile_info).  A chunk is 2 * grid / gcd(2 * grid, m_tiles) pairs: a whole
     // even number of grid rounds.  Used when all K / V together would not stay in L2 but a chunk's does (packed
@@ -234,16 +247,8 @@ int tc5_launch(const fa_fwd_params& a, const fa_fwd_plan& pl, cudaStream_t st, s
     if (chunk <= 0 || chunk > per_m) chunk = per_m;
     p.chunk_bh = (int)chunk;
   }
-  if (const char* e = std::getenv("FA_B200_RESCALE_THRESHOLD")) p.rescale_threshold = (float)std::atof(e);  // tuning override
-  if (const char* e = std::getenv("FA_B200_TC5_POLY")) p.tune_poly = std::atoi(e);
   p.status = status_word();
-  if (!p.status) { *err = "cannot allocate the device status word"; return FA_ERR_CUDA; }
-#ifdef FA_TC5_TRACE
-  static long long* trace_buf = nullptr;
-  if (!trace_buf) cudaMalloc(&trace_buf, sizeof(long long) * kTraceSlots * kTraceLen);
-  cudaMemsetAsync(trace_buf, 0, sizeof(long long) * kTraceSlots * kTraceLen, st);
-  p.trace = trace_buf;
-#endif
+  if (!p.status) { *err = "cannot look up the device status word"; return FA_ERR_CUDA; }
   const bool varlen = a.cu_seqlens_q != nullptr;
   CUtensorMap tq, tk, tv;
   bool ok = true;
@@ -255,15 +260,14 @@ int tc5_launch(const fa_fwd_params& a, const fa_fwd_plan& pl, cudaStream_t st, s
          encode_map(&tk, a.k, a.dtype, a.d, a.h_k, a.total_k, 1, a.k_head_stride, a.k_row_stride, 0) &&
          encode_map(&tv, a.v, a.dtype, a.d, a.h_k, a.total_k, 1, a.v_head_stride, a.v_row_stride, 0);
   } else if (a.block_table) {
-    // (d, kv head, row in page, page); the page count is not part of the parameters and only bounds the
-    // TMA's out-of-range check, which the kernel never relies on in that dimension
-    const int64_t n_pages = int64_t(1) << 30;
+    // (d, kv head, row in page, page): a block-table entry outside the pool reads zeros, not memory
+    const int64_t n_pages = a.kv_outer;
     ok = encode_map(&tq, a.q, a.dtype, a.d, a.h, a.seqlen_q, a.b, a.q_head_stride, a.q_row_stride, a.q_batch_stride) &&
          encode_map(&tk, a.k, a.dtype, a.d, a.h_k, a.page_size, n_pages, a.k_head_stride, a.k_row_stride, a.k_batch_stride) &&
          encode_map(&tv, a.v, a.dtype, a.d, a.h_k, a.page_size, n_pages, a.v_head_stride, a.v_row_stride, a.v_batch_stride);
   } else {
-    // with cache_batch_idx the cache has more rows than the batch: their number is not part of the parameters
-    const int64_t kv_batch = a.cache_batch_idx ? (int64_t(1) << 30) : a.b;
+    // with cache_batch_idx the cache may have more rows than the batch; an index outside it reads zeros
+    const int64_t kv_batch = a.cache_batch_idx ? a.kv_outer : a.b;
     ok = encode_map(&tq, a.q, a.dtype, a.d, a.h, a.seqlen_q, a.b, a.q_head_stride, a.q_row_stride, a.q_batch_stride) &&
          encode_map(&tk, a.k, a.dtype, a.d, a.h_k, a.seqlen_k, kv_batch, a.k_head_stride, a.k_row_stride, a.k_batch_stride) &&
          encode_map(&tv, a.v, a.dtype, a.d, a.h_k, a.seqlen_k, kv_batch, a.v_head_stride, a.v_row_stride, a.v_batch_stride);
@@ -278,26 +282,9 @@ int tc5_launch(const fa_fwd_params& a, const fa_fwd_plan& pl, cudaStream_t st, s
     }
   };
   const bool bf = a.dtype == FA_BF16;
-  switch (p.tune_poly) {
-    case 0: bf ? launch(fwd_tc5_kernel<__nv_bfloat16, 1, 0>) : launch(fwd_tc5_kernel<__half, 0, 0>); break;
-    case 1: bf ? launch(fwd_tc5_kernel<__nv_bfloat16, 1, 1>) : launch(fwd_tc5_kernel<__half, 0, 1>); break;
-    case 2: bf ? launch(fwd_tc5_kernel<__nv_bfloat16, 1, 2>) : launch(fwd_tc5_kernel<__half, 0, 2>); break;
-    default: bf ? launch(fwd_tc5_kernel<__nv_bfloat16, 1, 3>) : launch(fwd_tc5_kernel<__half, 0, 3>); break;
-  }
+  if (bf) launch(fwd_tc5_kernel<__nv_bfloat16, 1>);
+  else launch(fwd_tc5_kernel<__half, 0>);
   if (e != cudaSuccess) { *err = std::string("tcgen05 kernel launch: ") + cudaGetErrorString(e); return FA_ERR_CUDA; }
-#ifdef FA_TC5_TRACE
-  if (const char* path = std::getenv("FA_B200_TC5_TRACE_FILE")) {
-    static long long host[kTraceSlots * kTraceLen];
-    cudaStreamSynchronize(st);
-    cudaMemcpy(host, trace_buf, sizeof(host), cudaMemcpyDeviceToHost);
-    if (FILE* f = std::fopen(path, "w")) {
-      for (int s = 0; s < kTraceSlots; ++s)
-        for (int i = 0; i < kTraceLen; ++i)
-          if (host[s * kTraceLen + i]) std::fprintf(f, "%d %lld %lld\n", s, host[s * kTraceLen + i] >> 8, host[s * kTraceLen + i] & 255);
-      std::fclose(f);
-    }
-  }
-#endif
   return FA_OK;
 }
 

@@ -14,7 +14,8 @@
 //                  warps 8-11   correction (rescale of O in TMEM when a row maximum moved) and
 //                               epilogue (O / l -> global) for both sub-tiles
 //                  warps 12-13  MMA issuers, one per sub-tile (one elected lane each)
-//                  warp  14     TMA producer (one elected lane)      warp 15 idle
+//                  warp  14     TMA producer (one elected lane)
+//                  warp  15     clears the V rows past the end of a sequence (KV caches, packed input)
 // TMEM (512 columns): S0 [0,128)  S1 [128,256)  O0 [256,384)  O1 [384,512).
 // Shared memory: Q0 Q1 | P0 P1 | ring of K / V tiles (32 KiB each).
 // Dependency chain per sub-tile: a softmax thread copies its row of S into registers and frees the
@@ -60,36 +61,14 @@ struct Tc5Params {
   int32_t m_tiles;  // ceil(max seqlen_q / 256)
   int32_t total_tiles;
   float scale_log2;
-  // log2 units: the running max is only advanced (and O rescaled) when it grew by more than this.
-  // 0 = always (P <= 1 and the row maximum has P = 1 exactly, like the golden); > 0 trades a few
-  // ulps of P rounding on sharply peaked rows for fewer O rescales.
-  float rescale_threshold;
   int32_t chunk_bh;          // (batch, head) pairs per L2 chunk of the tile order (tile_info)
-  int32_t tune_poly;         // experiment: exponentials evaluated by polynomial out of every 4 pairs
+  // 1: the rows behind the last key of a sequence hold foreign data (the unused tail of a KV cache or of a page,
+  // the next sequence of a packed tensor) and must be cleared in V before P.V: P is 0 there, but 0 x NaN is NaN.
+  // 0: dense input, those rows lie outside the tensor and the TMA unit already returns zeros for them.
+  int32_t fix_tail;
   int32_t* status;  // device word: 0 ok, otherwise the wait that gave up
-#ifdef FA_TC5_TRACE
-  long long* trace;  // [slot][kTraceLen] (clock << 8 | tag), CTA 0 only (debug builds)
-#endif
 };
 
-#ifdef FA_TC5_TRACE
-constexpr int kTraceLen = 2048;
-constexpr int kTraceSlots = 8;
-struct Tracer {
-  long long* buf;
-  int n;
-  __device__ Tracer(const Tc5Params& p, int slot, bool on) : buf(on && blockIdx.x == 0 ? p.trace + slot * kTraceLen : nullptr), n(0) {}
-  __device__ void operator()(int tag) {
-    if (buf && n < kTraceLen) buf[n++] = (clock64() << 8) | (long long)(tag & 255);
-  }
-};
-#define FA_TR(tr, tag) (tr)(tag)
-#else
-struct Tracer {
-  __device__ Tracer(const Tc5Params&, int, bool) {}
-};
-#define FA_TR(tr, tag) ((void)0)
-#endif
 
 struct TileInfo {
   int bi, hh, hk, q_row0, q_len, k_row0, k_len, koff;
@@ -129,7 +108,7 @@ __device__ __forceinline__ void tile_info(const Tc5Params& p, int n, TileInfo& t
   }
   ti.bk = (p.a.cache_batch_idx && !p.a.block_table) ? p.a.cache_batch_idx[ti.bi] : ti.bi;
   // KV cache (contiguous or paged): keys in use per batch entry, plus the tokens the prologue appended
-  if (p.a.seqused_k) ti.k_len = p.a.seqused_k[ti.bi] + p.a.seqlen_new;
+  if (p.a.seqused_k) ti.k_len = cache_len(p.a, ti.bi, nullptr) + p.a.seqlen_new;  // clamped; the producer reports it
   ti.koff = ti.k_len - ti.q_len;
   ti.ulo = 0x7fffffff;
   ti.uhi = 0;
@@ -190,8 +169,13 @@ struct Barriers {
   uint64_t o_done[2];      // MMA -> correction, softmax: P.V of a block has completed (O_t updated, P_t read)
   uint64_t stats_ready[2]; // softmax -> correction: 1 / l of the tile's rows is in shared memory
   uint64_t o_free[2];      // correction -> MMA: the epilogue has read O_t
+  uint64_t fix_req;        // MMA (both warps) -> warp 15: the last V tile of the CTA tile has landed and needs its tail cleared
+  uint64_t v_fixed;        // warp 15 -> MMA (both warps): done
   uint32_t tmem_base;
   int abort_flag;
+  uint32_t fix_seen[2];    // tail repairs each issuing warp has been through (phase of fix_req / v_fixed)
+  uint32_t fix_slot;       // ring slot of the V tile to repair
+  int exp_busy[2][4];      // softmax warp [sub-tile][warp] is in its exponentials (a hint, see softmax_loop)
   float corr[2][kBlockM];
   float row_inv[2][kBlockM];
 };

@@ -71,6 +71,20 @@ __device__ __forceinline__ void poly_exp2_x2(uint64_t x2, float& p0, float& p1) 
   p1 = __uint_as_float(__float_as_uint(r1) + (__float_as_uint(n1) << 23));
 }
 
+// Build-time tuning constants of the softmax role.
+#ifndef FA_TC5_POLY
+#define FA_TC5_POLY 0
+#endif
+#ifndef FA_TC5_RESCALE_THRESHOLD
+#define FA_TC5_RESCALE_THRESHOLD 0.f
+#endif
+#ifndef FA_TC5_EXP_TURNS
+#define FA_TC5_EXP_TURNS 0
+#endif
+constexpr int kExpTurns = FA_TC5_EXP_TURNS;  // polls a softmax warp spends waiting for its scheduler's other softmax warp to leave its exponentials (0: none)
+constexpr int kPolyPairs = FA_TC5_POLY;  // of every 4 pairs of exponentials, how many use the polynomial
+constexpr float kRescaleThreshold = FA_TC5_RESCALE_THRESHOLD;
+
 // 32 scores -> 16 packed 16-bit pairs of P, accumulating the fp32 row sum (two partial sums).
 // POLY of every 4 pairs use the polynomial, the others the special-function unit.
 template <typename T, int POLY>
@@ -85,13 +99,8 @@ __device__ __forceinline__ void chunk_exp(const uint32_t (&a)[32], uint64_t scal
     } else {
       float x0, x1;
       unpack_f32x2(x2, x0, x1);
-#if defined(FA_TC5_EXPERIMENT) && (FA_TC5_EXPERIMENT & 1)
-      p0 = x0 * 0.001f;  // what-if build: no special-function work (results are wrong)
-      p1 = x1 * 0.001f;
-#else
       p0 = fast_exp2(x0);
       p1 = fast_exp2(x1);
-#endif
     }
     sum2[(e >> 1) & 3] = add_f32x2(sum2[(e >> 1) & 3], pack_f32x2(p0, p1));  // four independent chains
     pk[e >> 1] = pack2<T>(p0, p1);
@@ -110,7 +119,7 @@ __device__ __forceinline__ void store_p_chunk(uint32_t p_row, uint32_t p_xor, in
   }
 }
 
-template <typename T, int POLY>
+template <typename T>
 __device__ __forceinline__ void softmax_loop(const Tc5Params& p, Barriers* bar, uint32_t tmem, uint32_t p_smem, int t,
                                              int warp_in_wg, int lane) {
   volatile int* abort_flag = &bar->abort_flag;
@@ -123,7 +132,6 @@ __device__ __forceinline__ void softmax_loop(const Tc5Params& p, Barriers* bar, 
   const uint32_t p_xor = (uint32_t)(row & 7);
   const uint32_t bar_sfree = smem_addr(&bar->s_free[t]), bar_odone = smem_addr(&bar->o_done[t]);
   const uint32_t bar_oready = smem_addr(&bar->o_ready[t]), bar_ofree = smem_addr(&bar->o_free[t]);
-  Tracer tr(p, t, warp_in_wg == 0 && lane == 0);
   const float scale_log2 = p.scale_log2;
   const uint64_t scale2 = pack_f32x2(scale_log2, scale_log2);
 
@@ -160,7 +168,6 @@ __device__ __forceinline__ void softmax_loop(const Tc5Params& p, Barriers* bar, 
       if (!mbar_wait(smem_addr(&bar->s_full[t]), s_cnt & 1, abort_flag, 41)) return;
       const uint32_t blk = s_cnt;  // running number of this block (all tiles of this CTA)
       ++s_cnt;
-      FA_TR(tr, 1);
       tc_fence_after();
       // ---- all 128 scores of the row into registers (one TMEM round trip) ----
       uint32_t sc[4][32];
@@ -171,24 +178,19 @@ __device__ __forceinline__ void softmax_loop(const Tc5Params& p, Barriers* bar, 
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(bar_sfree);
-#if defined(FA_TC5_EXPERIMENT) && (FA_TC5_EXPERIMENT & 4)
-      need_mask = false;  // what-if build: no masking (results are wrong)
-#endif
       if (need_mask) {
 #pragma unroll
         for (int c = 0; c < 4; ++c) chunk_mask(sc[c], col0 + c * 32, lo, hi);
       }
-#if defined(FA_TC5_EXPERIMENT) && (FA_TC5_EXPERIMENT & 2)
-      float blk_max = __uint_as_float(sc[0][0]) + 8.f;  // what-if build: no row maximum (results are wrong)
-#else
       float blk_max = chunk_max(sc[0], -INFINITY);
 #pragma unroll
       for (int c = 1; c < 4; ++c) blk_max = chunk_max(sc[c], blk_max);
-#endif
 
       float m_new = fmaxf(m_run, blk_max);
-      // optional lazy update: keep the old reference max while the true max is within the threshold
-      if (m_run != -INFINITY && (m_new - m_run) * scale_log2 <= p.rescale_threshold) m_new = m_run;
+      // The running maximum follows every increase (P <= 1, and the row maximum has P = 1 exactly, like the
+      // reference's golden).  kRescaleThreshold > 0 (log2 units) would keep the old maximum while the new one is
+      // within the threshold: fewer O rescales for a few ulps of P rounding on sharply peaked rows.
+      if (kRescaleThreshold > 0.f && m_run != -INFINITY && (m_new - m_run) * scale_log2 <= kRescaleThreshold) m_new = m_run;
       const float m_use = (m_new == -INFINITY) ? 0.f : m_new;
       const float corr = fast_exp2((m_run - m_use) * scale_log2);  // 0 when m_run = -inf
       if (j > ti.jlo[t]) {
@@ -200,35 +202,44 @@ __device__ __forceinline__ void softmax_loop(const Tc5Params& p, Barriers* bar, 
         __syncwarp();
         if (lane == 0) mbar_arrive(smem_addr(&bar->corr_ready[t]));
       }
-      FA_TR(tr, 2);
       m_run = m_new;
       const float neg_ms = -m_use * scale_log2;
       const uint64_t negms2 = pack_f32x2(neg_ms, neg_ms);
 
       // ---- exponentials, P -> shared memory ----
+      // The two softmax warps of a scheduler (one per sub-tile) share its special-function unit.  When both are in
+      // their exponentials at once each runs at half speed and the unit then idles while both look for their next
+      // row maximum; taking turns keeps it busy.  The turn is only a hint (a flag and a bounded number of polls):
+      // it cannot block, whatever the other warp does.
+      if (kExpTurns > 0) {
+        if (lane == 0) {
+          volatile int* other = &bar->exp_busy[1 - t][warp_in_wg];
+          for (int w = 0; w < kExpTurns && *other; ++w) __nanosleep(40);
+          bar->exp_busy[t][warp_in_wg] = 1;
+        }
+        __syncwarp();
+      }
       uint64_t sum2[4];
 #pragma unroll
       for (int q = 0; q < 4; ++q) sum2[q] = pack_f32x2(0.f, 0.f);
       uint32_t pk[16];
-      chunk_exp<T, POLY>(sc[0], scale2, negms2, sum2, pk);
+      chunk_exp<T, kPolyPairs>(sc[0], scale2, negms2, sum2, pk);
       // P.V of the previous block must have read P_t before it is overwritten
       if (blk > 0 && !mbar_wait(bar_odone, (blk - 1) & 1, abort_flag, 42)) return;
-      FA_TR(tr, 5);
       store_p_chunk(p_row, p_xor, 0, pk);
-      chunk_exp<T, POLY>(sc[1], scale2, negms2, sum2, pk);
+      chunk_exp<T, kPolyPairs>(sc[1], scale2, negms2, sum2, pk);
       store_p_chunk(p_row, p_xor, 1, pk);
       fence_proxy_async();  // generic-proxy stores -> visible to the MMA (async proxy)
       __syncwarp();
       if (lane == 0) mbar_arrive(smem_addr(&bar->p_full[t][0]));  // first 64 keys of P are ready
-      FA_TR(tr, 3);
-      chunk_exp<T, POLY>(sc[2], scale2, negms2, sum2, pk);
+      chunk_exp<T, kPolyPairs>(sc[2], scale2, negms2, sum2, pk);
       store_p_chunk(p_row, p_xor, 2, pk);
-      chunk_exp<T, POLY>(sc[3], scale2, negms2, sum2, pk);
+      chunk_exp<T, kPolyPairs>(sc[3], scale2, negms2, sum2, pk);
+      if (kExpTurns > 0 && lane == 0) *(volatile int*)&bar->exp_busy[t][warp_in_wg] = 0;
       store_p_chunk(p_row, p_xor, 3, pk);
       fence_proxy_async();
       __syncwarp();
       if (lane == 0) mbar_arrive(smem_addr(&bar->p_full[t][1]));  // last 64 keys
-      FA_TR(tr, 4);
       float s0, s1;
       unpack_f32x2(add_f32x2(add_f32x2(sum2[0], sum2[1]), add_f32x2(sum2[2], sum2[3])), s0, s1);
       l_run = l_run * corr + (s0 + s1);
@@ -283,7 +294,6 @@ __device__ __forceinline__ void correction_loop(const Tc5Params& p, Barriers* ba
   const int row = warp_in_wg * 32 + lane;
   const uint32_t lane_addr = (uint32_t)(warp_in_wg * 32) << 16;
   uint32_t cr_cnt[2] = {0, 0}, od_cnt[2] = {0, 0}, st_cnt[2] = {0, 0};
-  Tracer tr(p, 2, warp_in_wg == 0 && lane == 0);
 
   TileSched sched(p);
   for (int n = sched.first(); n < p.total_tiles; n = sched.next()) {
@@ -296,7 +306,6 @@ __device__ __forceinline__ void correction_loop(const Tc5Params& p, Barriers* ba
         if (!(ti.has[t] && j > ti.jlo[t] && j < ti.jhi[t])) continue;
         if (!mbar_wait(smem_addr(&bar->corr_ready[t]), cr_cnt[t] & 1, abort_flag, 43)) return;
         ++cr_cnt[t];
-        FA_TR(tr, 10 + t);
         const float f = bar->corr[t][row];
         if (!mbar_wait(smem_addr(&bar->o_done[t]), od_cnt[t] & 1, abort_flag, 44)) return;  // P.V of block j-1 done
         ++od_cnt[t];
@@ -307,7 +316,6 @@ __device__ __forceinline__ void correction_loop(const Tc5Params& p, Barriers* ba
         }
         __syncwarp();
         if (lane == 0) mbar_arrive(smem_addr(&bar->o_ready[t]));
-        FA_TR(tr, 12 + t);
       }
     }
     // ---- epilogue of both sub-tiles ----

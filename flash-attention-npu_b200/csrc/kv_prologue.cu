@@ -20,7 +20,7 @@ template <typename T>
 __global__ void __launch_bounds__(256) kv_prologue_kernel(const __grid_constant__ KParams p, T* q_rot, int rot_per_token) {
   using Tr = PrologueTraits<T>;
   const int bi = blockIdx.y, unit = blockIdx.x, tid = threadIdx.x;
-  const int l_cache = p.a.seqused_k[bi];
+  const int l_cache = cache_len(p.a, bi, p.status);
   if (unit < p.a.h_k) {
     const int hk = unit;
     SeqView<T> sv;
@@ -35,7 +35,7 @@ __global__ void __launch_bounds__(256) kv_prologue_kernel(const __grid_constant_
     if (p.a.block_table) {
       sv.pages = p.a.block_table + (int64_t)bi * p.a.block_table_batch_stride;
     } else {
-      const int batch_row = p.a.cache_batch_idx ? p.a.cache_batch_idx[bi] : bi;
+      const int batch_row = p.a.cache_batch_idx ? outer_index(p.a, p.a.cache_batch_idx[bi], p.status) : bi;
       kb += (int64_t)batch_row * p.a.k_batch_stride;
       vb += (int64_t)batch_row * p.a.v_batch_stride;
     }

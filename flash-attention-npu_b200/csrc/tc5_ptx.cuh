@@ -56,6 +56,17 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
   if (*abort_flag == 0) *abort_flag = id;
   return false;
 }
+// Wait of a role that is idle for long stretches by design (it may be needed once per launch): many rounds of
+// the bounded wait with a pause between polls; only the sum of all rounds expiring is reported.
+__device__ __forceinline__ bool mbar_wait_patient(uint32_t bar, uint32_t parity, volatile int* abort_flag, int id) {
+  for (uint32_t i = 0; i < (kSpinLimit << 4); ++i) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if (*abort_flag) return false;
+    __nanosleep(256);
+  }
+  if (*abort_flag == 0) *abort_flag = id;
+  return false;
+}
 __device__ __forceinline__ void fence_barrier_init() {
   asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
 }

@@ -80,7 +80,7 @@ def get_scheduler_metadata(batch_size, max_seqlen_q, max_seqlen_k, num_heads_q, 
     else:
         p.lse_batch_stride, p.lse_head_stride = num_heads_q * max_seqlen_q, max_seqlen_q
     if page_size is not None:
-        p.block_table, p.page_size = dummy, int(page_size)
+        p.block_table, p.page_size, p.kv_outer = dummy, int(page_size), 1
     if max_seqlen_k_new:
         p.k_new = p.v_new = dummy
         p.seqlen_new = int(max_seqlen_k_new)

@@ -41,7 +41,7 @@ class FwdParams(C.Structure):
             "rotary_dim", "rotary_seqlen", "rotary_interleaved", "dtype",
             "causal", "window_left", "window_right", "max_seqlen_k_known",
             "kv_pos_offset", "kv_total", "partial_out",
-            "num_splits", "kernel", "num_sm", "total_k")]
+            "num_splits", "kernel", "num_sm", "total_k", "kv_outer")]
         + [("softmax_scale", C.c_float), ("softcap", C.c_float)]
     )
 
@@ -120,7 +120,7 @@ def load() -> C.CDLL:
     lib.fa_b200_abi_version.restype = C.c_int
     lib.fa_b200_launch_count.restype = C.c_longlong
     lib.fa_b200_launch_count.argtypes = []
-    if lib.fa_b200_abi_version() != 1:
+    if lib.fa_b200_abi_version() != 2:
         raise ImportError("libfa_b200.so ABI version mismatch")
     _lib = lib
     return lib

@@ -87,6 +87,8 @@ def build_params(q, k, v, out, lse, *, k_new=None, v_new=None, cu_seqlens_q=None
         h_k = k.shape[2]
         p.k_batch_stride, p.k_row_stride, p.k_head_stride = k.stride(0), k.stride(1), k.stride(2)
         p.v_batch_stride, p.v_row_stride, p.v_head_stride = v.stride(0), v.stride(1), v.stride(2)
+        if paged or cache_batch_idx is not None:
+            p.kv_outer = k.shape[0]  # pages / cache rows: bounds every block_table / cache_batch_idx entry
         if paged:
             p.page_size = k.shape[1]
             p.seqlen_k = block_table.shape[1] * k.shape[1]
@@ -116,6 +118,61 @@ def build_params(q, k, v, out, lse, *, k_new=None, v_new=None, cu_seqlens_q=None
     return p
 
 
+def _lse_shape(q, varlen_q):
+    return (q.shape[1], q.shape[0]) if varlen_q else (q.shape[0], q.shape[2], q.shape[1])
+
+
+def validate_forward(q, k, v, out, lse, kw) -> None:
+    """Every check that must hold before a parameter block is built from these tensors; allocates nothing.
+    ``out`` / ``lse`` may be None (the caller allocates them afterwards).  The C side only sees raw pointers and
+    strides, so a wrong dtype, device, shape or layout here would become an out-of-bounds access on the GPU."""
+    if not (q.is_cuda and k.is_cuda and v.is_cuda):
+        raise RuntimeError("flash_b200 runs on CUDA tensors only (there is no CPU implementation)")
+    if k.dtype != q.dtype or v.dtype != q.dtype:
+        raise RuntimeError("query and key/value must have the same dtype")
+    if k.device != q.device or v.device != q.device:
+        raise RuntimeError("query and key/value must be on the same device")
+    for name, t in (("q", q), ("k", k), ("v", v), ("k_new", kw.get("k_new")), ("v_new", kw.get("v_new"))):
+        if t is not None and t.stride(-1) != 1:
+            raise RuntimeError(f"Input tensor {name} must have contiguous last dimension")
+    for name in ("k_new", "v_new"):
+        t = kw.get(name)
+        if t is not None and (t.dtype != q.dtype or t.device != q.device):
+            raise RuntimeError(f"{name} must have the dtype and device of q")
+    for name in ("cu_seqlens_q", "cu_seqlens_k", "seqused_k", "cache_batch_idx", "block_table"):
+        _check_i32(kw.get(name), name)
+    b = (kw["cu_seqlens_q"].numel() - 1) if kw.get("cu_seqlens_q") is not None else q.shape[0]
+    for name in ("seqused_k", "cache_batch_idx"):
+        t = kw.get(name)
+        if t is not None and (t.dim() != 1 or t.numel() != b or not t.is_contiguous()):
+            raise RuntimeError(f"{name} must be a contiguous int32 tensor of shape (batch_size,)")
+    if kw.get("cu_seqlens_k") is not None and kw["cu_seqlens_k"].numel() != b + 1:
+        raise RuntimeError("cu_seqlens_k must have shape (batch_size + 1,)")
+    bt = kw.get("block_table")
+    if bt is not None and (bt.dim() != 2 or bt.shape[0] != b):
+        raise RuntimeError("block_table must have shape (batch_size, max_num_blocks_per_seq)")
+    if kw.get("alibi_slopes") is not None:
+        a = kw["alibi_slopes"]
+        if a.dtype != torch.float32 or not a.is_cuda or a.stride(-1) != 1:
+            raise RuntimeError("alibi_slopes must be a contiguous fp32 CUDA tensor")
+        if tuple(a.shape) not in ((q.shape[-2],), (b, q.shape[-2])):
+            raise RuntimeError("alibi_slopes must have shape (nheads,) or (batch_size, nheads)")
+    for name in ("rotary_cos", "rotary_sin"):
+        r = kw.get(name)
+        if r is not None and (r.dtype != q.dtype or not r.is_contiguous() or r.device != q.device or r.dim() != 2):
+            raise RuntimeError(f"{name} must be a contiguous 2-D tensor with the dtype and device of q")
+    partial = bool(kw.get("partial_out", False))
+    if out is not None:
+        if out.shape != q.shape or out.stride(-1) != 1 or out.device != q.device:
+            raise RuntimeError("out must have the shape and device of q and a contiguous last dimension")
+        if out.dtype != (torch.float32 if partial else q.dtype):
+            raise RuntimeError("out has the wrong dtype")
+    if lse is not None:
+        shape = _lse_shape(q, kw.get("cu_seqlens_q") is not None)
+        if tuple(lse.shape) != shape or lse.dtype != torch.float32 or lse.device != q.device or not lse.is_contiguous():
+            raise RuntimeError("lse must be a contiguous fp32 tensor of shape (b, h, s_q) / (h, total_q) on q's device")
+
+
 def attention_forward(q, k, v, *, out=None, lse=None, return_plan=False, **kw) -> Tuple[torch.Tensor, torch.Tensor]:
     """Runs the forward on the current CUDA stream.  Returns (out, lse[, plan]).
 
@@ -124,37 +181,12 @@ def attention_forward(q, k, v, *, out=None, lse=None, return_plan=False, **kw) -
     ``out`` / ``lse`` may be given (e.g. views of one message buffer); they are allocated otherwise.
     """
     lib = L.load()
-    if not (q.is_cuda and k.is_cuda and v.is_cuda):
-        raise RuntimeError("flash_b200 runs on CUDA tensors only (there is no CPU implementation)")
-    if k.dtype != q.dtype or v.dtype != q.dtype:
-        raise RuntimeError("query and key/value must have the same dtype")
-    for name, t in (("q", q), ("k", k), ("v", v), ("k_new", kw.get("k_new")), ("v_new", kw.get("v_new"))):
-        if t is not None and t.stride(-1) != 1:
-            raise RuntimeError(f"Input tensor {name} must have contiguous last dimension")
-    for name in ("cu_seqlens_q", "cu_seqlens_k", "seqused_k", "cache_batch_idx", "block_table"):
-        _check_i32(kw.get(name), name)
-    if kw.get("alibi_slopes") is not None:
-        a = kw["alibi_slopes"]
-        if a.dtype != torch.float32 or not a.is_cuda or a.stride(-1) != 1:
-            raise RuntimeError("alibi_slopes must be a contiguous fp32 CUDA tensor")
-    for name in ("rotary_cos", "rotary_sin"):
-        r = kw.get(name)
-        if r is not None and (r.dtype != q.dtype or not r.is_contiguous()):
-            raise RuntimeError(f"{name} must be contiguous and have the dtype of q")
+    validate_forward(q, k, v, out, lse, kw)
     partial = bool(kw.get("partial_out", False))
-    varlen_q = kw.get("cu_seqlens_q") is not None
     if out is None:
         out = torch.empty(q.shape, dtype=torch.float32 if partial else q.dtype, device=q.device)
-    else:
-        if out.shape != q.shape or out.stride(-1) != 1 or out.device != q.device:
-            raise RuntimeError("out must have the shape and device of q and a contiguous last dimension")
-        if out.dtype != (torch.float32 if partial else q.dtype):
-            raise RuntimeError("out has the wrong dtype")
-    lse_shape = (q.shape[1], q.shape[0]) if varlen_q else (q.shape[0], q.shape[2], q.shape[1])
     if lse is None:
-        lse = torch.empty(lse_shape, dtype=torch.float32, device=q.device)
-    elif tuple(lse.shape) != lse_shape or lse.dtype != torch.float32 or lse.device != q.device or not lse.is_contiguous():
-        raise RuntimeError("lse must be a contiguous fp32 tensor of shape (b, h, s_q) / (h, total_q) on q's device")
+        lse = torch.empty(_lse_shape(q, kw.get("cu_seqlens_q") is not None), dtype=torch.float32, device=q.device)
     with torch.cuda.device(q.device):
         p = build_params(q, k, v, out, lse, num_sm=_num_sm(q.device), **kw)
         plan = L.FwdPlan()
@@ -173,11 +205,15 @@ def attention_forward_noalloc(q, k, v, out, lse, **kw) -> None:
     """Same forward as ``attention_forward`` through ``fa_b200_fwd_noalloc``: the caller passes the
     output tensors (``out`` like q, ``lse`` fp32 (b, h, s_q) or (h, total_q)) and the library
     allocates nothing -- the split-KV scratch is a fixed 32 MiB array inside the library.  Meant
-    for hosts that may not touch an allocator while serving.  Calls that overlap on the GPU share
-    that scratch and race; the first call on a device should not be made under stream capture."""
+    for hosts that may not touch an allocator while serving.  The tensors go through the same checks as in
+    ``attention_forward`` before anything is launched.  Calls that overlap on the GPU share that scratch and
+    race.  The first call on a device loads the library's device image (which holds the array) and looks up the
+    array's address: make it once at start-up, outside any stream capture, before the phase in which nothing may
+    be allocated."""
     lib = L.load()
-    if not (q.is_cuda and k.is_cuda and v.is_cuda and out.is_cuda and lse.is_cuda):
-        raise RuntimeError("flash_b200 runs on CUDA tensors only (there is no CPU implementation)")
+    if out is None or lse is None:
+        raise RuntimeError("the allocation-free entry point needs caller-provided out and lse tensors")
+    validate_forward(q, k, v, out, lse, kw)
     with torch.cuda.device(q.device):
         p = build_params(q, k, v, out, lse, num_sm=_num_sm(q.device), **kw)
         L.check(lib.fa_b200_fwd_noalloc(C.byref(p), torch.cuda.current_stream(q.device).cuda_stream))

@@ -37,7 +37,7 @@
 extern "C" {
 #endif
 
-#define FA_B200_ABI_VERSION 1
+#define FA_B200_ABI_VERSION 2
 
 enum fa_status {
   FA_OK = 0,
@@ -109,6 +109,10 @@ typedef struct fa_fwd_params {
   int32_t num_sm;     /* 0 = query the current device */
   int32_t total_k;    /* rows of k / v when cu_seqlens_k is set (0 = not given: the tcgen05 kernel, which needs
                          the bound for its TMA descriptors, is then not used for varlen input) */
+  int32_t kv_outer;   /* extent of the outermost dimension of k / v: the number of pages when block_table is set,
+                         the number of cache rows when cache_batch_idx is set (required in both cases), else 0 = b.
+                         Entries of block_table / cache_batch_idx outside [0, kv_outer) are never dereferenced:
+                         the kernels read zeros instead and raise the status word (fa_b200_check_status) */
   float softmax_scale;
   float softcap; /* 0 = off */
 } fa_fwd_params;
@@ -152,9 +156,11 @@ int fa_b200_fwd(const fa_fwd_params* p, void* workspace, size_t workspace_bytes,
  * call makes no cudaMalloc / cudaFree or any other allocating call.  It always uses the
  * register-accumulator kernel.  A problem whose plan needs more than 32 MiB of scratch is
  * refused with FA_ERR_WORKSPACE (pass a smaller num_splits, or use fa_b200_fwd).
- * The first call on a device looks up the array's device address; make that first call outside
- * any stream capture.  All calls share the one array, which keeps the previous call's contents
- * (nothing in it needs clearing: every slot that is read is written first), so two calls that
+ * The first call on a device makes the driver load the library's device image (which holds the
+ * 32 MiB array) and looks up the array's device address: the free memory the driver reports drops
+ * by about that much at that moment.  Make that first call once at start-up, outside any stream
+ * capture, before the phase in which nothing may be allocated.  All calls share the one array,
+ * which keeps the previous call's contents (nothing in it needs clearing: every slot that is read is written first), so two calls that
  * overlap on the GPU -- different streams or threads -- race on it.
  * This entry point has no counterpart in the reference. */
 int fa_b200_fwd_noalloc(const fa_fwd_params* p, void* stream);

@@ -20,13 +20,13 @@ def test_library_exports_every_declared_symbol():
     assert declared == set(L.EXPORTS)
     for name in declared:
         assert hasattr(lib, name), name
-    assert lib.fa_b200_abi_version() == 1
+    assert lib.fa_b200_abi_version() == 2
     assert lib.fa_b200_status_string(-4).decode().startswith("workspace")
 
 
 def test_struct_layout_matches_header():
     # sizes produced by gcc for include/fa_b200.h (x86-64 LP64)
-    assert C.sizeof(L.FwdParams) == 400
+    assert C.sizeof(L.FwdParams) == 408
     assert C.sizeof(L.FwdPlan) == 72
     assert C.sizeof(L.CombineParams) == 176
 
@@ -72,7 +72,7 @@ def test_plan_decode_packs_gqa_and_splits():
 
 
 def test_plan_window_bounds_the_kv_range():
-    p = _params(seqused_k=256, block_table=256, page_size=256, seqlen_k=32768, seqlen_q=4, total_q=8,
+    p = _params(seqused_k=256, block_table=256, page_size=256, kv_outer=4096, seqlen_k=32768, seqlen_q=4, total_q=8,
                 lse_head_stride=4, lse_batch_stride=128, causal=1, window_left=4096, window_right=0, h=64)
     rc, pl = _plan(p)
     assert rc == 0 and pl.is_local == 1 and pl.window_left == 4096 and pl.window_right == 0
@@ -84,7 +84,11 @@ def test_plan_window_bounds_the_kv_range():
     (dict(h=30), "Number of heads"), (dict(d=264), "at most 256"), (dict(d=100), "multiple of 8"),
     (dict(dtype=7), "FP16 and BF16"), (dict(b=0), "batch size"), (dict(softcap=-1.0), "softcap"),
     (dict(k_new=256), "together"), (dict(k_new=256, v_new=256, seqlen_new=1), "cache_seqlens"),
-    (dict(block_table=256, page_size=16), "key lengths"),
+    (dict(block_table=256, page_size=16, kv_outer=8), "key lengths"),
+    (dict(block_table=256, page_size=128, seqused_k=256), "kv_outer"),            # paged: the page count is required
+    (dict(cache_batch_idx=256, seqused_k=256), "kv_outer"),                       # ... and the cache rows with an index
+    (dict(block_table=256, page_size=128, seqused_k=256, kv_outer=-3), "kv_outer"),
+    (dict(seqused_k=256, k_new=256, v_new=256, seqlen_new=5000), "do not fit"),   # more new tokens than the cache holds
     (dict(rotary_cos=256, rotary_sin=256, rotary_dim=64), "together with new k"),
     (dict(kernel=L.KERNEL_TCGEN05, seqused_k=256), "tcgen05"),
 ])
@@ -163,7 +167,7 @@ def test_plan_32_row_decode_configuration_follows_the_key_range():
     64-key blocks (one launch, no partials); long ranges and ragged launches that become persistent keep the
     single CTA of 2x4 warps with 128-key blocks."""
     kw = dict(b=32, seqlen_q=4, seqlen_k=32768, h=64, h_k=8, d=128, total_q=128, seqused_k=256,
-              block_table=256, page_size=256, block_table_batch_stride=128,
+              block_table=256, page_size=256, kv_outer=4096, block_table_batch_stride=128,
               q_batch_stride=4 * 8192, q_row_stride=8192, q_head_stride=128,
               k_batch_stride=256 * 1024, k_row_stride=1024, k_head_stride=128,
               v_batch_stride=256 * 1024, v_row_stride=1024, v_head_stride=128,
@@ -192,7 +196,7 @@ def test_plan_prefill_against_a_cache_goes_to_the_tcgen05_kernel():
               causal=1)
     rc, pl = _plan(_params(**kw))
     assert rc == 0 and pl.kernel == L.KERNEL_TCGEN05 and pl.launches == 1 and pl.workspace_bytes == 0
-    paged = dict(kw, block_table=256, page_size=256, block_table_batch_stride=32,
+    paged = dict(kw, block_table=256, page_size=256, kv_outer=64, block_table_batch_stride=32,
                  k_batch_stride=256 * 1024, v_batch_stride=256 * 1024)
     rc, pl = _plan(_params(**paged))
     assert rc == 0 and pl.kernel == L.KERNEL_TCGEN05 and pl.launches == 1
@@ -206,7 +210,7 @@ def test_plan_prefill_against_a_cache_goes_to_the_tcgen05_kernel():
     rc, pl = _plan(_params(**dict(paged, rotary_cos=256, rotary_sin=256, rotary_dim=128, rotary_seqlen=9000, **new)))
     assert rc == 0 and pl.kernel == L.KERNEL_TCGEN05 and pl.launches == 2
     assert pl.workspace_bytes == 4 * 512 * 32 * 128 * 2
-    rc, pl = _plan(_params(**dict(kw, cache_batch_idx=256)))
+    rc, pl = _plan(_params(**dict(kw, cache_batch_idx=256, kv_outer=7)))
     assert rc == 0 and pl.kernel == L.KERNEL_TCGEN05
     rc, pl = _plan(_params(**dict(kw, alibi_slopes=256)))
     assert rc == 0 and pl.kernel == L.KERNEL_MMA
