@@ -62,8 +62,12 @@ struct Planned {
   int hd_pad;
 };
 
-static int make_plan(const fa_fwd_params& a, Planned* out) {
+// `forced`: a plan made earlier for the same problem (fa_b200_plan_encode): its kernel family, tile configuration
+// and KV splits are taken over instead of being decided again; FA_ERR_UNSUPPORTED when they do not fit this call.
+static int make_plan(const fa_fwd_params& a_in, Planned* out, const fa_fwd_plan* forced = nullptr) {
   std::memset(out, 0, sizeof(*out));
+  fa_fwd_params a = a_in;
+  if (forced) a.kernel = forced->kernel;
   if (a.b <= 0) return fail(FA_ERR_INVALID, "batch size must be positive");
   if (a.dtype != FA_FP16 && a.dtype != FA_BF16) return fail(FA_ERR_INVALID, "FlashAttention only supports FP16 and BF16 data types");
   if (a.d <= 0 || a.d > 256) return fail(FA_ERR_INVALID, "FlashAttention only supports head dimension at most 256");
@@ -128,6 +132,12 @@ static int make_plan(const fa_fwd_params& a, Planned* out) {
     MmaConfigInfo t;
     if (mma_config_info(hd_pad, forced, &t) && t.block_m >= std::min(rows_max, 16)) cfg = forced;
   }
+  if (forced && forced->kernel == FA_KERNEL_MMA) {
+    MmaConfigInfo t;
+    if (!mma_config_info(hd_pad, forced->config, &t) || t.block_m < std::min(rows_max, 16))
+      return fail(FA_ERR_UNSUPPORTED, "the plan's tile configuration does not fit this problem");
+    cfg = forced->config;
+  }
   MmaConfigInfo ci;
   if (!mma_config_info(hd_pad, cfg, &ci)) return fail(FA_ERR_UNSUPPORTED, "no tile configuration");
   // ---- producer / consumer decode kernel: <= 32 packed rows, head dim <= 128 (> 64), rows that can
@@ -163,6 +173,12 @@ static int make_plan(const fa_fwd_params& a, Planned* out) {
         const int forced = std::atoi(e);
         DecodeConfigInfo t;
         if (decode_config_info(hd_pad, forced, &t) && t.block_m >= rows_max) dcfg = forced;
+      }
+      if (forced && forced->kernel == FA_KERNEL_DECODE) {
+        DecodeConfigInfo t;
+        if (!decode_config_info(hd_pad, forced->config, &t) || t.block_m < rows_max)
+          return fail(FA_ERR_UNSUPPORTED, "the plan's tile configuration does not fit this problem");
+        dcfg = forced->config;
       }
       DecodeConfigInfo di;
       if (decode_config_info(hd_pad, dcfg, &di)) {
@@ -240,6 +256,23 @@ static int make_plan(const fa_fwd_params& a, Planned* out) {
       persistent = can_persist && !decode_one_segment_only && (std::atoi(e) == 2 || (std::atoi(e) == 1 && !window_bound));
     if (const char* e = std::getenv("FA_B200_DECODE_PERSISTENT_GRID")) persist_grid = std::max(1, std::atoi(e));  // tuning override
     if (persistent) { ns = kPersistSlots; bps = 0; }
+    if (forced && forced->kernel == FA_KERNEL_DECODE && forced->num_splits > 1 && forced->blocks_per_split == 0) {
+      if (!can_persist || decode_one_segment_only || forced->grid <= 0 || forced->num_splits != kPersistSlots)
+        return fail(FA_ERR_UNSUPPORTED, "the plan's persistent decode schedule does not fit this problem");
+      persistent = true;
+      persist_grid = forced->grid;
+      ns = kPersistSlots;
+      bps = 0;
+    } else if (forced) {
+      persistent = false;
+    }
+  }
+  if (forced && forced->kernel != FA_KERNEL_TCGEN05 && !persistent) {
+    if (forced->num_splits < 1 || forced->blocks_per_split < 1 ||
+        (long long)forced->num_splits * forced->blocks_per_split < max_blocks)
+      return fail(FA_ERR_UNSUPPORTED, "the plan's KV splits do not cover this problem's key range");
+    ns = forced->num_splits;
+    bps = forced->blocks_per_split;
   }
 
   const bool varlen_q = a.cu_seqlens_q != nullptr;
@@ -309,10 +342,11 @@ static int launch_combine(const fa_combine_params& c, cudaStream_t st) {
   return FA_OK;
 }
 
-static int run_fwd(const fa_fwd_params& a, void* workspace, size_t workspace_bytes, cudaStream_t st) {
+static int run_fwd(const fa_fwd_params& a, void* workspace, size_t workspace_bytes, cudaStream_t st,
+                   const fa_fwd_plan* forced = nullptr) {
   if (!a.q || !a.k || !a.v || !a.o || !a.lse) return fail(FA_ERR_INVALID, "q, k, v, o and lse must be non-null");
   Planned P;
-  int rc = make_plan(a, &P);
+  int rc = make_plan(a, &P, forced);
   if (rc != FA_OK) return rc;
   if (a.total_q == 0 || a.seqlen_q == 0) return FA_OK;
   if (P.pl.kernel == FA_KERNEL_TCGEN05) {
@@ -456,6 +490,95 @@ static int run_fwd_noalloc(const fa_fwd_params& a_in, cudaStream_t st) {
   return run_fwd(a, scratch, kNoAllocScratchBytes, st);
 }
 
+// ------------------------------------------------------------------------------------------------
+// Plans as bytes: what get_scheduler_metadata of the reference returns as an opaque tensor
+// (csrc/arch22/flash_attn_npu_v3/flash_api.cpp:493-558: [causal mask | FAInferTilingData], filled by an AICPU
+// kernel).  Here the bytes are a header that names the problem they were made for and the fa_fwd_plan itself; the
+// forward that receives them checks the header against its own arguments and takes the plan over.
+// ------------------------------------------------------------------------------------------------
+constexpr uint32_t kPlanMagic = 0x0FA5B200u;
+struct PlanBlob {
+  uint32_t magic, abi, bytes, kind;
+  int32_t b, seqlen_q, seqlen_k, h, h_k, d, dtype, causal, window_left, window_right, page_size, seqlen_new, num_splits;
+  int32_t reserved[3];
+  fa_fwd_plan plan;
+};
+static_assert(sizeof(PlanBlob) <= FA_B200_PLAN_BYTES, "FA_B200_PLAN_BYTES is too small");
+
+// Which optional parts a call has: a plan only carries over between calls of the same kind.
+static uint32_t plan_kind(const fa_fwd_params& a) {
+  return (a.seqused_k ? 1u : 0u) | (a.block_table ? 2u : 0u) | (a.cu_seqlens_q ? 4u : 0u) | (a.cu_seqlens_k ? 8u : 0u) |
+         (a.softcap > 0.f ? 16u : 0u) | (a.k_new ? 32u : 0u) | (a.alibi_slopes ? 64u : 0u) | (a.cache_batch_idx ? 128u : 0u) |
+         (a.kv_total > 0 ? 256u : 0u) | (a.partial_out ? 512u : 0u);
+}
+
+static int plan_encode(const fa_fwd_params& a, void* buf, size_t n) {
+  if (!buf || n < sizeof(PlanBlob)) return fail(FA_ERR_INVALID, "plan buffer too small (FA_B200_PLAN_BYTES)");
+  Planned P;
+  const int rc = make_plan(a, &P);
+  if (rc != FA_OK) return rc;
+  PlanBlob blob;
+  std::memset(&blob, 0, sizeof(blob));
+  blob.magic = kPlanMagic;
+  blob.abi = FA_B200_ABI_VERSION;
+  blob.bytes = sizeof(PlanBlob);
+  blob.kind = plan_kind(a);
+  blob.b = a.b; blob.seqlen_q = a.seqlen_q; blob.seqlen_k = a.seqlen_k; blob.h = a.h; blob.h_k = a.h_k; blob.d = a.d;
+  blob.dtype = a.dtype; blob.causal = a.causal; blob.window_left = a.window_left; blob.window_right = a.window_right;
+  blob.page_size = a.page_size; blob.seqlen_new = a.seqlen_new; blob.num_splits = a.num_splits;
+  blob.plan = P.pl;
+  std::memset(buf, 0, n);
+  std::memcpy(buf, &blob, sizeof(blob));
+  return FA_OK;
+}
+
+static int plan_decode(const void* buf, size_t n, PlanBlob* out) {
+  if (!buf || n < sizeof(PlanBlob)) return fail(FA_ERR_INVALID, "scheduler metadata is too short to be a plan of this library");
+  std::memcpy(out, buf, sizeof(PlanBlob));
+  if (out->magic != kPlanMagic) return fail(FA_ERR_INVALID, "scheduler metadata was not made by get_scheduler_metadata of this library");
+  if (out->abi != FA_B200_ABI_VERSION || out->bytes != sizeof(PlanBlob))
+    return fail(FA_ERR_INVALID, "scheduler metadata was made by another version of this library");
+  return FA_OK;
+}
+
+static int run_fwd_planned(const fa_fwd_params& a, const void* buf, size_t n, void* workspace, size_t workspace_bytes,
+                           cudaStream_t st) {
+  PlanBlob blob;
+  int rc = plan_decode(buf, n, &blob);
+  if (rc != FA_OK) return rc;
+  // The problem the plan names must be the one at hand: a plan for other shapes is a caller's mistake.
+  struct { const char* name; int32_t planned, given; } key[] = {
+      {"batch size", blob.b, a.b}, {"max_seqlen_q", blob.seqlen_q, a.seqlen_q}, {"num_heads_q", blob.h, a.h},
+      {"num_heads_kv", blob.h_k, a.h_k}, {"head dim", blob.d, a.d}, {"dtype", blob.dtype, a.dtype},
+      {"causal", blob.causal, a.causal}, {"window_size_left", blob.window_left, a.window_left},
+      {"window_size_right", blob.window_right, a.window_right}};
+  for (const auto& f : key)
+    if (f.planned != f.given)
+      return fail(FA_ERR_INVALID, std::string("scheduler metadata was computed for a different problem: ") + f.name + " " +
+                                      std::to_string(f.planned) + " there, " + std::to_string(f.given) + " here");
+  const bool cache = a.seqused_k != nullptr;
+  if (!cache && blob.seqlen_k != a.seqlen_k)
+    return fail(FA_ERR_INVALID, "scheduler metadata was computed for a different problem: max_seqlen_k " +
+                                    std::to_string(blob.seqlen_k) + " there, " + std::to_string(a.seqlen_k) + " here");
+  // The tile configuration and KV splits only carry over to a call with the same optional parts; otherwise the
+  // call is planned afresh (the reference's tests hand a plan made from cache lengths to the dense entry points).
+  if (blob.kind == plan_kind(a) && blob.page_size == a.page_size && blob.seqlen_new == a.seqlen_new &&
+      blob.num_splits == a.num_splits) {
+    fa_fwd_params a2 = a;
+    // A cache may be larger than the longest sequence the plan was made for.  The plan's splits cover
+    // max_seqlen_k keys, so that becomes the bound: a longer cache_seqlens entry is clamped and reported through
+    // the status word instead of being attended to in part.
+    if (cache && blob.seqlen_k < a2.seqlen_k) {
+      a2.seqlen_k = blob.seqlen_k;
+      if (a2.block_table) a2.seqlen_k = ceil_div(a2.seqlen_k, a2.page_size) * a2.page_size;
+      if (a2.max_seqlen_k_known > blob.seqlen_k) a2.max_seqlen_k_known = blob.seqlen_k;
+    }
+    rc = run_fwd(a2, workspace, workspace_bytes, st, &blob.plan);
+    if (rc != FA_ERR_UNSUPPORTED) return rc;
+  }
+  return run_fwd(a, workspace, workspace_bytes, st);
+}
+
 }  // namespace fa
 
 extern "C" {
@@ -470,6 +593,28 @@ int fa_b200_fwd(const fa_fwd_params* p, void* workspace, size_t workspace_bytes,
   if (!p) return fa::fail(FA_ERR_INVALID, "null params");
   fa::g_err.clear();
   return fa::run_fwd(*p, workspace, workspace_bytes, reinterpret_cast<cudaStream_t>(stream));
+}
+
+int fa_b200_fwd_planned(const fa_fwd_params* p, const void* plan, size_t plan_bytes, void* workspace, size_t workspace_bytes,
+                        void* stream) {
+  if (!p) return fa::fail(FA_ERR_INVALID, "null params");
+  fa::g_err.clear();
+  return fa::run_fwd_planned(*p, plan, plan_bytes, workspace, workspace_bytes, reinterpret_cast<cudaStream_t>(stream));
+}
+
+int fa_b200_plan_encode(const fa_fwd_params* p, void* buf, size_t buf_bytes) {
+  if (!p) return fa::fail(FA_ERR_INVALID, "null params");
+  fa::g_err.clear();
+  return fa::plan_encode(*p, buf, buf_bytes);
+}
+
+int fa_b200_plan_decode(const void* buf, size_t buf_bytes, fa_fwd_plan* plan) {
+  if (!plan) return fa::fail(FA_ERR_INVALID, "null argument");
+  fa::g_err.clear();
+  fa::PlanBlob blob;
+  const int rc = fa::plan_decode(buf, buf_bytes, &blob);
+  if (rc == FA_OK) *plan = blob.plan;
+  return rc;
 }
 
 int fa_b200_fwd_plan(const fa_fwd_params* p, fa_fwd_plan* plan) {

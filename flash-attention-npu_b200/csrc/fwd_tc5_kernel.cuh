@@ -175,7 +175,6 @@ struct Barriers {
   int abort_flag;
   uint32_t fix_seen[2];    // tail repairs each issuing warp has been through (phase of fix_req / v_fixed)
   uint32_t fix_slot;       // ring slot of the V tile to repair
-  int exp_busy[2][4];      // softmax warp [sub-tile][warp] is in its exponentials (a hint, see softmax_loop)
   float corr[2][kBlockM];
   float row_inv[2][kBlockM];
 };

@@ -6,13 +6,12 @@
 namespace fa {
 namespace tc5 {
 
-// The CTA's work is one stream of units u = (CTA tile, KV block), tile after tile.  The tensor pipe gets
-//   Q.K^T(u+1) before P.V(u)
-// across tile boundaries too: Q.K^T of the next tile's first block is issued before P.V of this tile's last one,
-// so the softmax threads go from the last block of a tile to the first block of the next without waiting for the
-// tensor pipe, and a sub-tile that finishes its tile a block early (causal: the upper half of the rows) starts the
-// next tile while the other sub-tile is still on its last block.  K / V tiles go through the ring in the same
-// order,  K(0) | K(1) V(0) | K(2) V(1) | ... | V(last);  ring slot and parity follow from a running count.
+// Both single-thread roles walk the K / V tiles of a CTA tile in the order the tensor pipe needs them:
+//   K_lo | K_lo+1 V_lo | K_lo+2 V_lo+1 | ... | V_hi-1
+// (Q.K^T of block j+1 is issued before P.V of block j).  Ring slot and parity follow from a running count.
+// (Carrying the order across tile boundaries -- Q.K^T of the next tile's first block before P.V of this tile's last
+// one -- lets one sub-tile run a block ahead of the other, and then the two need four K / V tiles at a time where the
+// ring has three: measured 8 % slower on causal 4K.)
 struct RingPos {
   uint32_t cnt = 0;
   __device__ __forceinline__ void next(uint32_t& slot, uint32_t& par) {
@@ -29,6 +28,7 @@ struct RingPos {
 // pages hold whole 128-key blocks, the page of a block comes from the block table (the warp keeps
 // 32 consecutive entries in registers, one per lane).
 // ---------------------------------------------------------------------------------------------
+template <bool FIX>
 __device__ __forceinline__ void producer_loop(const Tc5Params& p, const CUtensorMap* tm_q, const CUtensorMap* tm_k,
                                               const CUtensorMap* tm_v, Barriers* bar, uint32_t q_smem, uint32_t kv_smem) {
   volatile int* abort_flag = &bar->abort_flag;
@@ -38,21 +38,6 @@ __device__ __forceinline__ void producer_loop(const Tc5Params& p, const CUtensor
   const int lane = threadIdx.x & 31;
   const uint64_t q_policy = l2_policy_evict_first();  // Q is read once
   const int pages_per_seq = p.a.block_table ? ceil_div(p.a.seqlen_k, p.a.page_size) : 0;  // entries per block-table row
-  auto load = [&](const CUtensorMap* tm, int hk, int row, int outer) -> bool {
-    uint32_t slot, par;
-    ring.next(slot, par);
-    if (!mbar_wait(smem_addr(&bar->kv_empty[slot]), par ^ 1, abort_flag, 12)) return false;
-    const uint32_t full = smem_addr(&bar->kv_full[slot]);
-    if (elect_one()) {
-      mbar_arrive_expect_tx(full, kTileBytes);
-      tma_load_4d(kv_smem + slot * kTileBytes, tm, full, 0, hk, row, outer);
-      tma_load_4d(kv_smem + slot * kTileBytes + kHalfBytes, tm, full, 64, hk, row, outer);
-    }
-    __syncwarp();
-    return true;
-  };
-  bool have_prev = false;         // V of the previous unit is still to be loaded (same coordinates as its K)
-  int v_hk = 0, v_row = 0, v_outer = 0;
   TileSched sched(p);
   for (int n = sched.first(); n < p.total_tiles; n = sched.next()) {
     TileInfo ti;
@@ -74,13 +59,15 @@ __device__ __forceinline__ void producer_loop(const Tc5Params& p, const CUtensor
       __syncwarp();
     }
     const int bk = varlen_k ? 0 : ti.bk;
-    if (lane == 0 && p.a.seqused_k) {  // every role clamps these silently (tile_info); this one reports them
+    if (FIX && lane == 0 && p.a.seqused_k) {  // every role clamps these silently (tile_info); this one reports them
       cache_len(p.a, ti.bi, p.status);
       if (p.a.cache_batch_idx && !p.a.block_table) check_outer_index(p.a, bk, p.status);
     }
     const int32_t* pages = p.a.block_table ? p.a.block_table + (int64_t)ti.bi * p.a.block_table_batch_stride : nullptr;
     int pg_base = -1, pg_reg = 0;  // block-table entries pg_base .. pg_base + 31 of this batch entry, one per lane
-    for (int j = ti.ulo; j < ti.uhi; ++j) {
+    auto load = [&](const CUtensorMap* tm, int j) -> bool {
+      uint32_t slot, par;
+      ring.next(slot, par);
       int row = ti.k_row0 + j * kBlockN, outer = bk;
       if (pages) {
         const int pg = (j * kBlockN) / p.a.page_size;
@@ -90,18 +77,25 @@ __device__ __forceinline__ void producer_loop(const Tc5Params& p, const CUtensor
           pg_reg = idx < pages_per_seq ? pages[idx] : 0;
         }
         outer = __shfl_sync(0xffffffffu, pg_reg, pg - pg_base);
-        if (lane == 0) check_outer_index(p.a, outer, p.status);  // out of range: the TMA returns zeros
+        if (FIX && lane == 0) check_outer_index(p.a, outer, p.status);  // out of range: the TMA returns zeros
         row = j * kBlockN - pg * p.a.page_size;
       }
-      if (!load(tm_k, ti.hk, row, outer)) return;
-      if (have_prev && !load(tm_v, v_hk, v_row, v_outer)) return;
-      have_prev = true;
-      v_hk = ti.hk;
-      v_row = row;
-      v_outer = outer;
+      if (!mbar_wait(smem_addr(&bar->kv_empty[slot]), par ^ 1, abort_flag, 12)) return false;
+      const uint32_t full = smem_addr(&bar->kv_full[slot]);
+      if (elect_one()) {
+        mbar_arrive_expect_tx(full, kTileBytes);
+        tma_load_4d(kv_smem + slot * kTileBytes, tm, full, 0, ti.hk, row, outer);
+        tma_load_4d(kv_smem + slot * kTileBytes + kHalfBytes, tm, full, 64, ti.hk, row, outer);
+      }
+      __syncwarp();
+      return true;
+    };
+    if (!load(tm_k, ti.ulo)) return;
+    for (int j = ti.ulo; j < ti.uhi; ++j) {
+      if (j + 1 < ti.uhi && !load(tm_k, j + 1)) return;
+      if (!load(tm_v, j)) return;
     }
   }
-  if (have_prev) load(tm_v, v_hk, v_row, v_outer);
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -145,15 +139,14 @@ __device__ __forceinline__ void tail_fix_loop(const Tc5Params& p, Barriers* bar,
 }
 
 // ---------------------------------------------------------------------------------------------
-// MMA issuer of sub-tile t (one warp per sub-tile, one elected lane each).  Per unit u = (tile, KV block j):
+// MMA issuer of sub-tile t (one warp per sub-tile, one elected lane each).  Per KV block j:
 //   S_t = Q_t K_j^T (both operands in shared memory),
 //   O_t += P_t V_j  (P_t from shared memory, V_j as an N-contiguous operand).
-// Issue order  QK(u0) | QK(u+1) PV(u) | ... over the whole stream of the CTA: Q.K^T of the next unit only waits
-// for the softmax threads to have copied S_t into registers (and, on the first block of a tile, for Q_t), so it
-// runs under this unit's exponentials.  What P.V of the previous unit needs to know travels in `prev`.
+// Issue order  QK(j0) | QK(j+1) PV(j) | ... : Q.K^T of the next block only waits for the softmax
+// threads to have copied S_t into registers, so it runs under this block's exponentials.
 // A K / V slot is released by two arrivals: one per sub-tile, or both from the only user.
 // ---------------------------------------------------------------------------------------------
-template <uint32_t AB_FMT>
+template <uint32_t AB_FMT, bool FIX>
 __device__ __forceinline__ void mma_loop(const Tc5Params& p, Barriers* bar, uint32_t q_smem, uint32_t p_smem,
                                          uint32_t kv_smem, uint32_t tmem, const int t) {
   volatile int* abort_flag = &bar->abort_flag;
@@ -177,15 +170,9 @@ __device__ __forceinline__ void mma_loop(const Tc5Params& p, Barriers* bar, uint
   const uint32_t bar_kvfull0 = smem_addr(&bar->kv_full[0]), bar_kvempty0 = smem_addr(&bar->kv_empty[0]);
   const int o = 1 - t;
 
-  // The previous unit, whose P.V is still to be issued: bit 0 this sub-tile uses it, bit 1 it is this sub-tile's
-  // first block of its tile (O_t starts from zero), bit 2 the other sub-tile uses it too, bit 3 its V tile needs
-  // the rows behind the last key cleared (tail_fix_loop), bit 4 there is a previous unit at all.
-  enum : uint32_t { kMine = 1, kFirst = 2, kOther = 4, kFix = 8, kValid = 16 };
-  uint32_t prev = 0;
-
-  // Tail of the last V tile of a CTA tile: both issuing warps ask for it and wait for it, also the one that does
-  // not use the tile, so that every phase of the two barriers is seen by everybody.  (The phase count lives in
-  // shared memory: this warp has 40 registers and needs it once in many tiles.)
+  // Tail of the last V tile of a CTA tile (tail_fix_loop): both issuing warps ask for it and wait for it, also the
+  // one that does not use the tile, so that every phase of the two barriers is seen by everybody.  (The phase count
+  // lives in shared memory: this warp has 40 registers and needs it once in many tiles.)
   auto tail_fix = [&](uint32_t slot) -> bool {
     const uint32_t n = bar->fix_seen[t];
     __syncwarp();
@@ -198,89 +185,91 @@ __device__ __forceinline__ void mma_loop(const Tc5Params& p, Barriers* bar, uint
     return mbar_wait(smem_addr(&bar->v_fixed), n & 1, abort_flag, 22);
   };
 
-  // O_t (+)= P_t V of the previous unit, in two halves of 64 keys so that the first starts while the softmax
-  // threads still work on the second.
-  auto issue_pv = [&]() -> bool {
-    uint32_t slot, par;
-    ring.next(slot, par);
-    if (!(prev & kMine)) return !(prev & kFix) || tail_fix(slot);
-    if (prev & kFirst) {  // the previous tile's epilogue must have read O_t
-      if (!mbar_wait(bar_ofree, (ofree_cnt & 1) ^ 1, abort_flag, 16)) return false;
-      ++ofree_cnt;
-    } else {              // the correction warps must have rescaled O_t for this block
-      if (!mbar_wait(bar_oready, oready_cnt & 1, abort_flag, 17)) return false;
-      ++oready_cnt;
-    }
-    if (!mbar_wait(bar_kvfull0 + slot * 8, par, abort_flag, 18)) return false;
-    if ((prev & kFix) && !tail_fix(slot)) return false;
-    const uint64_t v_desc = v_desc0 + slot * kSlotStep;
-    if (!mbar_wait(bar_pfull0, p_cnt & 1, abort_flag, 19)) return false;  // first 64 keys of P
-    tc_fence_after();
-    if (elect_one()) {
-      if (prev & kFirst) mma_ss_c<false>(o_tmem, p_desc, v_desc, idesc_pv);
-      else mma_ss_c<true>(o_tmem, p_desc, v_desc, idesc_pv);
-#pragma unroll
-      for (int ks = 1; ks < 4; ++ks) mma_ss_c<true>(o_tmem, p_desc + k_off(ks), v_desc + (uint64_t)(ks * (2048 >> 4)), idesc_pv);
-    }
-    if (!mbar_wait(bar_pfull1, p_cnt & 1, abort_flag, 20)) return false;  // last 64 keys
-    tc_fence_after();
-    if (elect_one()) {
-#pragma unroll
-      for (int ks = 4; ks < 8; ++ks) mma_ss_c<true>(o_tmem, p_desc + k_off(ks), v_desc + (uint64_t)(ks * (2048 >> 4)), idesc_pv);
-      mma_commit(bar_odone);
-      mma_commit(bar_kvempty0 + slot * 8);
-      if (!(prev & kOther)) mma_commit(bar_kvempty0 + slot * 8);
-    }
-    __syncwarp();
-    ++p_cnt;
-    return true;
-  };
-
   TileSched sched(p);
   for (int n = sched.first(); n < p.total_tiles; n = sched.next()) {
     TileInfo ti;
     tile_info(p, n, ti);
     if (ti.uhi <= ti.ulo) continue;
+    if (ti.has[t]) {
+      if (!mbar_wait(smem_addr(&bar->q_full[t]), q_cnt & 1, abort_flag, 13)) return;
+      ++q_cnt;
+    }
     const int jlo_t = ti.has[t] ? ti.jlo[t] : 0, jhi_t = ti.has[t] ? ti.jhi[t] : 0;
     const int jlo_o = ti.has[o] ? ti.jlo[o] : 0, jhi_o = ti.has[o] ? ti.jhi[o] : 0;
-    const int fix_j = tile_needs_tail_fix(p, ti) ? ti.uhi - 1 : -1;
-    for (int j = ti.ulo; j < ti.uhi; ++j) {
-      // ---- S_t = Q_t K_j^T.  Tiles only the other sub-tile uses need no arrival from this warp (that warp
-      //      arrives twice); tiles nobody uses cannot occur (the union of two touching intervals has no hole).
-      const bool mine = j >= jlo_t && j < jhi_t, other = j >= jlo_o && j < jhi_o;
-      {
-        uint32_t slot, par;
-        ring.next(slot, par);
-        if (mine) {
-          if (j == jlo_t) {  // first block of the tile: Q_t must have landed
-            if (!mbar_wait(smem_addr(&bar->q_full[t]), q_cnt & 1, abort_flag, 13)) return;
-            ++q_cnt;
-          }
-          const uint64_t k_desc = k_desc0 + slot * kSlotStep;
-          if (!mbar_wait(bar_kvfull0 + slot * 8, par, abort_flag, 14)) return;
-          // the softmax threads must have copied the previous S_t out of TMEM
-          if (qk_cnt > 0 && !mbar_wait(bar_sfree, (qk_cnt - 1) & 1, abort_flag, 15)) return;
-          ++qk_cnt;
-          tc_fence_after();
-          if (elect_one()) {
-            mma_ss_c<false>(s_tmem, q_desc, k_desc, idesc_qk);
+    const int fix_j = (FIX && tile_needs_tail_fix(p, ti)) ? ti.uhi - 1 : -1;  // the block whose V tile needs its tail cleared
+
+    // S_t = Q_t K_j^T.  Tiles only the other sub-tile uses need no arrival from this warp (that warp
+    // arrives twice); tiles nobody uses cannot occur (the union of two touching intervals has no hole).
+    auto issue_qk = [&](int j) -> bool {
+      uint32_t slot, par;
+      ring.next(slot, par);
+      if (j < jlo_t || j >= jhi_t) return true;
+      const uint64_t k_desc = k_desc0 + slot * kSlotStep;
+      if (!mbar_wait(bar_kvfull0 + slot * 8, par, abort_flag, 14)) return false;
+      // the softmax threads must have copied the previous S_t out of TMEM
+      if (qk_cnt > 0 && !mbar_wait(bar_sfree, (qk_cnt - 1) & 1, abort_flag, 15)) return false;
+      ++qk_cnt;
+      tc_fence_after();
+      const bool other = j >= jlo_o && j < jhi_o;
+      if (elect_one()) {
+        mma_ss_c<false>(s_tmem, q_desc, k_desc, idesc_qk);
 #pragma unroll
-            for (int ks = 1; ks < 8; ++ks) mma_ss_c<true>(s_tmem, q_desc + k_off(ks), k_desc + k_off(ks), idesc_qk);
-            mma_commit(bar_sfull);
-            if (j == jhi_t - 1) mma_commit(smem_addr(&bar->q_empty[t]));
-            mma_commit(bar_kvempty0 + slot * 8);
-            if (!other) mma_commit(bar_kvempty0 + slot * 8);
-          }
-          __syncwarp();
-        }
+        for (int ks = 1; ks < 8; ++ks) mma_ss_c<true>(s_tmem, q_desc + k_off(ks), k_desc + k_off(ks), idesc_qk);
+        mma_commit(bar_sfull);
+        if (j == jhi_t - 1) mma_commit(smem_addr(&bar->q_empty[t]));
+        mma_commit(bar_kvempty0 + slot * 8);
+        if (!other) mma_commit(bar_kvempty0 + slot * 8);
       }
-      // ---- P.V of the unit before this one
-      if ((prev & kValid) && !issue_pv()) return;
-      prev = kValid | (mine ? kMine : 0u) | ((mine && j == jlo_t) ? kFirst : 0u) | (other ? kOther : 0u) |
-             (j == fix_j ? kFix : 0u);
+      __syncwarp();
+      return true;
+    };
+
+    // O_t (+)= P_t V_j, in two halves of 64 keys so that the first starts while the softmax threads
+    // still work on the second.
+    auto issue_pv = [&](int j) -> bool {
+      uint32_t slot, par;
+      ring.next(slot, par);
+      if (j < jlo_t || j >= jhi_t) return !FIX || j != fix_j || tail_fix(slot);
+      const bool first_pv = j == jlo_t;
+      if (first_pv) {  // the previous tile's epilogue must have read O_t
+        if (!mbar_wait(bar_ofree, (ofree_cnt & 1) ^ 1, abort_flag, 16)) return false;
+        ++ofree_cnt;
+      } else {         // the correction warps must have rescaled O_t for this block
+        if (!mbar_wait(bar_oready, oready_cnt & 1, abort_flag, 17)) return false;
+        ++oready_cnt;
+      }
+      if (!mbar_wait(bar_kvfull0 + slot * 8, par, abort_flag, 18)) return false;
+      if (FIX && j == fix_j && !tail_fix(slot)) return false;
+      const uint64_t v_desc = v_desc0 + slot * kSlotStep;
+      if (!mbar_wait(bar_pfull0, p_cnt & 1, abort_flag, 19)) return false;  // first 64 keys of P
+      tc_fence_after();
+      if (elect_one()) {
+        if (first_pv) mma_ss_c<false>(o_tmem, p_desc, v_desc, idesc_pv);
+        else mma_ss_c<true>(o_tmem, p_desc, v_desc, idesc_pv);
+#pragma unroll
+        for (int ks = 1; ks < 4; ++ks) mma_ss_c<true>(o_tmem, p_desc + k_off(ks), v_desc + (uint64_t)(ks * (2048 >> 4)), idesc_pv);
+      }
+      if (!mbar_wait(bar_pfull1, p_cnt & 1, abort_flag, 20)) return false;  // last 64 keys
+      tc_fence_after();
+      const bool other = j >= jlo_o && j < jhi_o;
+      if (elect_one()) {
+#pragma unroll
+        for (int ks = 4; ks < 8; ++ks) mma_ss_c<true>(o_tmem, p_desc + k_off(ks), v_desc + (uint64_t)(ks * (2048 >> 4)), idesc_pv);
+        mma_commit(bar_odone);
+        mma_commit(bar_kvempty0 + slot * 8);
+        if (!other) mma_commit(bar_kvempty0 + slot * 8);
+      }
+      __syncwarp();
+      ++p_cnt;
+      return true;
+    };
+
+    if (!issue_qk(ti.ulo)) return;
+    for (int j = ti.ulo; j < ti.uhi; ++j) {
+      if (j + 1 < ti.uhi && !issue_qk(j + 1)) return;
+      if (!issue_pv(j)) return;
     }
   }
-  if (prev & kValid) issue_pv();
 }
 
 }  // namespace tc5

@@ -78,10 +78,6 @@ __device__ __forceinline__ void poly_exp2_x2(uint64_t x2, float& p0, float& p1) 
 #ifndef FA_TC5_RESCALE_THRESHOLD
 #define FA_TC5_RESCALE_THRESHOLD 0.f
 #endif
-#ifndef FA_TC5_EXP_TURNS
-#define FA_TC5_EXP_TURNS 0
-#endif
-constexpr int kExpTurns = FA_TC5_EXP_TURNS;  // polls a softmax warp spends waiting for its scheduler's other softmax warp to leave its exponentials (0: none)
 constexpr int kPolyPairs = FA_TC5_POLY;  // of every 4 pairs of exponentials, how many use the polynomial
 constexpr float kRescaleThreshold = FA_TC5_RESCALE_THRESHOLD;
 
@@ -207,18 +203,6 @@ __device__ __forceinline__ void softmax_loop(const Tc5Params& p, Barriers* bar, 
       const uint64_t negms2 = pack_f32x2(neg_ms, neg_ms);
 
       // ---- exponentials, P -> shared memory ----
-      // The two softmax warps of a scheduler (one per sub-tile) share its special-function unit.  When both are in
-      // their exponentials at once each runs at half speed and the unit then idles while both look for their next
-      // row maximum; taking turns keeps it busy.  The turn is only a hint (a flag and a bounded number of polls):
-      // it cannot block, whatever the other warp does.
-      if (kExpTurns > 0) {
-        if (lane == 0) {
-          volatile int* other = &bar->exp_busy[1 - t][warp_in_wg];
-          for (int w = 0; w < kExpTurns && *other; ++w) __nanosleep(40);
-          bar->exp_busy[t][warp_in_wg] = 1;
-        }
-        __syncwarp();
-      }
       uint64_t sum2[4];
 #pragma unroll
       for (int q = 0; q < 4; ++q) sum2[q] = pack_f32x2(0.f, 0.f);
@@ -235,7 +219,6 @@ __device__ __forceinline__ void softmax_loop(const Tc5Params& p, Barriers* bar, 
       chunk_exp<T, kPolyPairs>(sc[2], scale2, negms2, sum2, pk);
       store_p_chunk(p_row, p_xor, 2, pk);
       chunk_exp<T, kPolyPairs>(sc[3], scale2, negms2, sum2, pk);
-      if (kExpTurns > 0 && lane == 0) *(volatile int*)&bar->exp_busy[t][warp_in_wg] = 0;
       store_p_chunk(p_row, p_xor, 3, pk);
       fence_proxy_async();
       __syncwarp();

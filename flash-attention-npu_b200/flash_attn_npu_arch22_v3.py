@@ -7,13 +7,13 @@ native module never exported.  Backed by libfa_b200.so.
 from __future__ import annotations
 
 import ctypes as C
+import weakref
 
 import torch
 
 from flash_b200 import lib as L
 from flash_b200 import ops
 
-_PLAN_MAGIC = 0x0FA5B200
 
 
 def _reject(cond, msg):
@@ -43,17 +43,35 @@ def fwd(q, k, v, k_new_, v_new_, q_v_, out_, cu_seqlens_q_, cu_seqlens_k_, cu_se
     _reject(attention_chunk != 0, "NPU FlashAttention does not support attention_chunk")
     if softmax_scale_ is None:
         softmax_scale_ = q.shape[-1] ** (-0.5)
-    if scheduler_metadata_ is not None:
-        meta = getattr(scheduler_metadata_, "_fa_b200_plan", None)
-        if meta is not None and num_splits == 0:
-            num_splits = meta["num_splits"]
+    plan_bytes = _plan_bytes(scheduler_metadata_) if scheduler_metadata_ is not None else None
     out, lse = ops.attention_forward(
         q, k, v, out=out_, k_new=k_new_, v_new=v_new_, cu_seqlens_q=cu_seqlens_q_, cu_seqlens_k=cu_seqlens_k_,
         max_seqlen_q=max_seqlen_q_, max_seqlen_k=max_seqlen_k_, seqused_k=seqused_k_, cache_batch_idx=kv_batch_idx_,
         block_table=page_table_, rotary_cos=rotary_cos_, rotary_sin=rotary_sin_,
         rotary_interleaved=is_rotary_interleaved, softmax_scale=softmax_scale_, causal=is_causal,
-        window_left=window_size_left, window_right=window_size_right, softcap=softcap, num_splits=num_splits)
+        window_left=window_size_left, window_right=window_size_right, softcap=softcap, num_splits=num_splits,
+        plan_bytes=plan_bytes)
     return [out, lse, None, None]
+
+
+# Decoded copies of metadata tensors seen before.  Reading the bytes of a device tensor costs a device-to-host copy,
+# which a decode loop that passes the same tensor object every step should pay once.  An entry belongs to one live
+# tensor object at one version (the weak reference guards against a new tensor at a recycled address or id); a
+# clone, a moved copy or a modified tensor simply misses here and is read again.
+_decoded = {}
+
+
+def _plan_bytes(meta: torch.Tensor) -> bytes:
+    if meta.dtype != torch.uint8 or meta.dim() != 1 or meta.numel() < L.PLAN_BYTES:
+        raise RuntimeError("scheduler_metadata must be the uint8 tensor returned by get_scheduler_metadata")
+    hit = _decoded.get(id(meta))
+    if hit is not None and hit[0]() is meta and hit[1] == meta._version:
+        return hit[2]
+    raw = bytes(meta[:L.PLAN_BYTES].cpu().numpy().tobytes())
+    if len(_decoded) > 64:
+        _decoded.clear()
+    _decoded[id(meta)] = (weakref.ref(meta), meta._version, raw)
+    return raw
 
 
 def get_scheduler_metadata(batch_size, max_seqlen_q, max_seqlen_k, num_heads_q, num_heads_kv, headdim, headdim_v,
@@ -61,46 +79,63 @@ def get_scheduler_metadata(batch_size, max_seqlen_q, max_seqlen_k, num_heads_q, 
                            seqused_q=None, cache_leftpad=None, page_size=None, max_seqlen_k_new=0, causal=False,
                            window_size_left=-1, window_size_right=-1, attention_chunk=0, has_softcap=False,
                            num_splits=0, pack_gqa=None, sm_margin=0):
-    """Pre-plans a KV-cache forward (tile configuration and KV splits) without touching the
-    sequence lengths on the host.  Returns an opaque uint8 tensor on the device of cache_seqlens;
-    pass it back as ``scheduler_metadata=``.  (The reference computes its plan with an AICPU kernel
-    and a host synchronisation, flash_api.cpp:43-56; this one is pure host arithmetic.)"""
-    lib = L.load()
+    """Plans a forward ahead of the call -- kernel family, tile configuration, KV splits, grid -- from the shapes
+    alone, without touching the sequence lengths on the host.  Returns an opaque uint8 tensor on the device of
+    cache_seqlens whose bytes ARE the plan (a header naming the problem, then the plan); pass it back as
+    ``scheduler_metadata=``.  The forward checks the header against its own arguments: bytes made for other shapes,
+    dtype or mask are refused.  (The reference computes its plan with an AICPU kernel and a host synchronisation,
+    csrc/arch22/flash_attn_npu_v3/flash_api.cpp:43-56,493-558; this one is host arithmetic.)  Tensors are assumed
+    contiguous and 16-byte aligned, as the torch allocator makes them; a call whose tensors are not is planned afresh."""
+    _reject(cu_seqlens_k_new is not None or seqused_q is not None or cache_leftpad is not None,
+            "NPU FlashAttention does not support cu_seqlens_k_new / seqused_q / cache_leftpad")
+    _reject(attention_chunk != 0, "NPU FlashAttention does not support attention_chunk")
+    _reject(headdim_v is not None and headdim_v != headdim, "head dims of q / k and v must be equal")
     p = L.FwdParams()
-    dummy = 256  # plan only checks pointers for NULL-ness
-    p.q = p.k = p.v = p.o = p.lse = dummy
-    p.seqused_k = dummy
-    p.b, p.seqlen_q, p.seqlen_k = batch_size, max_seqlen_q, max_seqlen_k
-    p.h, p.h_k, p.d = num_heads_q, num_heads_kv, headdim
-    p.total_q = batch_size * max_seqlen_q
+    stand_in = 256  # only NULL-ness and alignment of the pointers matter to the planner
+    p.q = p.k = p.v = p.o = p.lse = stand_in
+    b, s_q, s_k, h, h_k, d = int(batch_size), int(max_seqlen_q), int(max_seqlen_k), int(num_heads_q), int(num_heads_kv), int(headdim)
+    p.b, p.seqlen_q, p.seqlen_k, p.h, p.h_k, p.d = b, s_q, s_k, h, h_k, d
+    p.q_head_stride = p.o_head_stride = d
+    p.q_row_stride = p.o_row_stride = h * d
     if cu_seqlens_q is not None:
-        p.cu_seqlens_q = dummy
-        p.total_q = batch_size * max_seqlen_q
+        p.cu_seqlens_q = stand_in
+        p.total_q = b * s_q  # an upper bound: the plan only depends on it through the LSE layout
         p.lse_head_stride = p.total_q
     else:
-        p.lse_batch_stride, p.lse_head_stride = num_heads_q * max_seqlen_q, max_seqlen_q
-    if page_size is not None:
-        p.block_table, p.page_size, p.kv_outer = dummy, int(page_size), 1
+        p.total_q = b * s_q
+        p.q_batch_stride = p.o_batch_stride = s_q * h * d
+        p.lse_batch_stride, p.lse_head_stride = h * s_q, s_q
+    p.k_head_stride = p.v_head_stride = d
+    p.k_row_stride = p.v_row_stride = h_k * d
+    if cu_seqlens_k is not None:
+        p.cu_seqlens_k, p.total_k = stand_in, b * s_k
+    else:
+        p.seqused_k = stand_in
+        if page_size is not None:
+            p.block_table, p.page_size = stand_in, int(page_size)
+            pages = -(-s_k // int(page_size))
+            p.seqlen_k = pages * int(page_size)
+            p.block_table_batch_stride, p.kv_outer = pages, b * pages
+            p.k_batch_stride = p.v_batch_stride = int(page_size) * h_k * d
+        else:
+            p.k_batch_stride = p.v_batch_stride = s_k * h_k * d
     if max_seqlen_k_new:
-        p.k_new = p.v_new = dummy
+        p.k_new = p.v_new = stand_in
         p.seqlen_new = int(max_seqlen_k_new)
+        p.knew_head_stride = p.vnew_head_stride = d
+        p.knew_row_stride = p.vnew_row_stride = h_k * d
+        p.knew_batch_stride = p.vnew_batch_stride = int(max_seqlen_k_new) * h_k * d
     p.dtype = L.FA_BF16 if qkv_dtype == torch.bfloat16 else L.FA_FP16
-    p.causal, p.window_left, p.window_right = int(bool(causal)), window_size_left, window_size_right
+    p.causal, p.window_left, p.window_right = int(bool(causal)), int(window_size_left), int(window_size_right)
     p.max_seqlen_k_known = -1
-    p.num_splits = num_splits
-    p.kernel = L.KERNEL_MMA
+    p.num_splits = int(num_splits)
+    p.kernel = L.KERNEL_AUTO
     dev = cache_seqlens.device
     p.num_sm = ops._num_sm(dev) if dev.type == "cuda" else 148
-    p.softmax_scale = 1.0
+    p.softmax_scale = float(d) ** -0.5
     p.softcap = 1.0 if has_softcap else 0.0
-    plan = L.FwdPlan()
-    L.check(lib.fa_b200_fwd_plan(C.byref(p), C.byref(plan)))
-    words = [_PLAN_MAGIC, plan.kernel, plan.config, plan.pack_gqa, plan.block_m, plan.block_n, plan.m_blocks,
-             plan.num_splits, plan.blocks_per_split, plan.grid]
-    meta = torch.tensor(words, dtype=torch.int32).view(torch.uint8).to(dev, non_blocking=True)
-    meta._fa_b200_plan = {"num_splits": plan.num_splits, "blocks_per_split": plan.blocks_per_split,
-                          "config": plan.config, "grid": plan.grid}
-    return meta
+    raw = ops.encode_plan(p)
+    return torch.frombuffer(bytearray(raw), dtype=torch.uint8).to(dev)
 
 
 def fwd_combine(out_partial, lse_partial, out=None, out_dtype=None):

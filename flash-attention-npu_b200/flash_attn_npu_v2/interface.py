@@ -3,7 +3,8 @@
 Same function names, argument order, defaults and return conventions as
 flash_attn_npu_v2/interface_arch22.py of the reference (:965-1573); the native calls go to
 ``flash_attn_npu_arch22_v2`` (here a ctypes-backed module over libfa_b200.so) positionally,
-exactly as the reference calls its pybind extension (:61-75, :1551-1572).
+exactly as the reference calls its pybind extension (:61-75, :1551-1572); the dense and varlen forward and
+backward go through ``torch.library`` operators of the reference's names (``custom_ops.py``).
 
 ``flash_attn_func`` and ``flash_attn_varlen_func`` (and their packed variants) are differentiable:
 autograd Functions with the structure of the reference's (:774-824, :827-900), whose backward
@@ -17,6 +18,8 @@ import torch
 import torch.nn.functional as F
 
 import flash_attn_npu_arch22_v2 as _ext
+
+from . import custom_ops as _ops  # registers the torch.library operators the calls below go through
 
 
 def maybe_contiguous(x):
@@ -43,8 +46,9 @@ class FlashAttnFunc(torch.autograd.Function):
                 return_softmax):
         d = q.size(3)
         qp, kp, vp = _pad_head([maybe_contiguous(x) for x in (q, k, v)], d)
-        out_padded, lse, s_dmask, _ = _ext.fwd(qp, kp, vp, None, alibi_slopes, dropout_p, softmax_scale, causal,
-                                               window_size[0], window_size[1], softcap, False, None)
+        out_padded, lse, s_dmask, _ = _ops._flash_attn_forward(qp, kp, vp, dropout_p, softmax_scale, causal,
+                                                               window_size[0], window_size[1], softcap, alibi_slopes,
+                                                               False)
         if any(t.requires_grad for t in (q, k, v)):
             ctx.save_for_backward(qp, kp, vp, out_padded, lse)
             ctx.args = (dropout_p, softmax_scale, causal, window_size, softcap, alibi_slopes, deterministic, d)
@@ -57,8 +61,9 @@ class FlashAttnFunc(torch.autograd.Function):
         q, k, v, out, lse = ctx.saved_tensors
         dropout_p, softmax_scale, causal, window_size, softcap, alibi_slopes, deterministic, d = ctx.args
         dout_padded = _pad_head([maybe_contiguous(dout)], d)[0]
-        dq, dk, dv, _ = _ext.bwd(dout_padded, q, k, v, out, lse, None, None, None, alibi_slopes, dropout_p,
-                                 softmax_scale, causal, window_size[0], window_size[1], softcap, deterministic, None, None)
+        dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
+        _ops._flash_attn_backward(dout_padded, q, k, v, out, lse, dq, dk, dv, dropout_p, softmax_scale, causal,
+                                  window_size[0], window_size[1], softcap, alibi_slopes, deterministic, None)
         return dq[..., :d], dk[..., :d], dv[..., :d], None, None, None, None, None, None, None, None
 
 
@@ -70,10 +75,9 @@ class FlashAttnVarlenFunc(torch.autograd.Function):
                 window_size, softcap, alibi_slopes, deterministic, block_table):
         d = q.size(2)
         qp, kp, vp = _pad_head([maybe_contiguous(x) for x in (q, k, v)], d)
-        out_padded, lse, s_dmask, _ = _ext.varlen_fwd(qp, kp, vp, None, cu_seqlens_q, cu_seqlens_k, None, None,
-                                                      block_table, alibi_slopes, max_seqlen_q, max_seqlen_k, dropout_p,
-                                                      softmax_scale, False, causal, window_size[0], window_size[1],
-                                                      softcap, False, None)
+        out_padded, lse, s_dmask, _ = _ops._flash_attn_varlen_forward(
+            qp, kp, vp, cu_seqlens_q, cu_seqlens_k, max_seqlen_q, max_seqlen_k, dropout_p, softmax_scale, causal,
+            window_size[0], window_size[1], softcap, alibi_slopes, False, block_table, None, None, False)
         if any(t.requires_grad for t in (q, k, v)):
             ctx.save_for_backward(qp, kp, vp, out_padded, lse, cu_seqlens_q, cu_seqlens_k)
             ctx.args = (max_seqlen_q, max_seqlen_k, dropout_p, softmax_scale, causal, window_size, softcap,
@@ -88,9 +92,10 @@ class FlashAttnVarlenFunc(torch.autograd.Function):
         (max_seqlen_q, max_seqlen_k, dropout_p, softmax_scale, causal, window_size, softcap, alibi_slopes, deterministic,
          d) = ctx.args
         dout_padded = _pad_head([maybe_contiguous(dout)], d)[0]
-        dq, dk, dv, _ = _ext.varlen_bwd(dout_padded, q, k, v, out, lse, None, None, None, cu_seqlens_q, cu_seqlens_k,
-                                        alibi_slopes, max_seqlen_q, max_seqlen_k, dropout_p, softmax_scale, False, causal,
-                                        window_size[0], window_size[1], softcap, deterministic, None, None)
+        dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
+        _ops._flash_attn_varlen_backward(dout_padded, q, k, v, out, lse, dq, dk, dv, cu_seqlens_q, cu_seqlens_k,
+                                         max_seqlen_q, max_seqlen_k, dropout_p, softmax_scale, causal, window_size[0],
+                                         window_size[1], softcap, alibi_slopes, deterministic, None, False)
         return (dq[..., :d], dk[..., :d], dv[..., :d]) + (None,) * 12
 
 

@@ -16,6 +16,8 @@ import torch
 
 import flash_attn_npu_arch22_v3 as _ext
 
+from . import custom_ops as _ops  # registers the torch.library operators the calls below go through
+
 
 def maybe_contiguous(x):
     return x.contiguous() if x is not None and x.stride(-1) != 1 else x
@@ -34,15 +36,22 @@ def _forward(q, k, v, k_new=None, v_new=None, qv=None, out_=None, cu_seqlens_q=N
     if d % 8 != 0:  # pad the head dim like the v2 front end does; sliced back below
         pad = 8 - d % 8
         q, k, v = [torch.nn.functional.pad(t, [0, pad]) for t in (q, k, v)]
-    out, lse, out_accum, lse_accum = _ext.fwd(
-        q, k, v, k_new, v_new, qv, out_, cu_seqlens_q, cu_seqlens_k, cu_seqlens_k_new, seqused_q, seqused_k,
-        max_seqlen_q, max_seqlen_k, page_table, kv_batch_idx, leftpad_k, rotary_cos, rotary_sin, seqlens_rotary,
-        q_descale, k_descale, v_descale, softmax_scale, causal, window_size_left, window_size_right,
-        attention_chunk, softcap, rotary_interleaved, scheduler_metadata, num_splits, pack_gqa, sm_margin)
-    if out_accum is None:
-        out_accum = torch.tensor([], device=out.device)
-    if lse_accum is None:
-        lse_accum = torch.tensor([], device=out.device)
+    args = (q, k, v, k_new, v_new, qv, out_, cu_seqlens_q, cu_seqlens_k, cu_seqlens_k_new, seqused_q, seqused_k,
+            max_seqlen_q, max_seqlen_k, page_table, kv_batch_idx, leftpad_k, rotary_cos, rotary_sin, seqlens_rotary,
+            q_descale, k_descale, v_descale, softmax_scale, causal, window_size_left, window_size_right,
+            attention_chunk, softcap, rotary_interleaved, scheduler_metadata, num_splits, pack_gqa, sm_margin)
+    unsupported = (qv, cu_seqlens_k_new, seqused_q, leftpad_k, seqlens_rotary, q_descale, k_descale, v_descale)
+    if out_ is not None or any(x is not None for x in unsupported) or attention_chunk != 0:
+        # a caller-provided output cannot be an operator result (it would alias an input), and the arguments this
+        # backend rejects are rejected by the extension with the reference's messages
+        out, lse, out_accum, lse_accum = _ops._call(*args)
+    elif k_new is not None:  # new tokens are written into the cache: the operator that says so
+        out, lse, out_accum, lse_accum = _ops._flash_attn_forward_inplace(
+            q, k, v, k_new, v_new, cu_seqlens_q, seqused_k, max_seqlen_q, page_table, kv_batch_idx, rotary_cos,
+            rotary_sin, softmax_scale, causal, window_size_left, window_size_right, softcap, rotary_interleaved,
+            scheduler_metadata, num_splits, pack_gqa, sm_margin)
+    else:
+        out, lse, out_accum, lse_accum = _ops._flash_attn_forward(*args)
     return out[..., :d], lse, out_accum, lse_accum
 
 
@@ -70,10 +79,11 @@ class _AttnFunc(torch.autograd.Function):
         dout = maybe_contiguous(dout)
         if q.shape[-1] != d:
             dout = torch.nn.functional.pad(dout, [0, q.shape[-1] - d])
-        dq, dk, dv, _ = _ext.bwd(dout, q, k, v, out.contiguous(), lse, None, None, None, cu_q, cu_k, kw.get("seqused_q"),
-                                 kw.get("seqused_k"), kw.get("max_seqlen_q"), kw.get("max_seqlen_k"),
-                                 kw.get("softmax_scale"), kw.get("causal", False), kw.get("window_size_left", -1),
-                                 kw.get("window_size_right", -1), kw.get("softcap", 0.0), False, kw.get("sm_margin", 0))
+        dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
+        _ops._flash_attn_backward(dout, q, k, v, out.contiguous(), lse, cu_q, cu_k, kw.get("seqused_q"),
+                                  kw.get("seqused_k"), kw.get("max_seqlen_q"), kw.get("max_seqlen_k"), dq, dk, dv,
+                                  kw.get("softmax_scale"), kw.get("causal", False), kw.get("window_size_left", -1),
+                                  kw.get("window_size_right", -1), kw.get("softcap", 0.0), False, kw.get("sm_margin", 0))
         return dq[..., :d], dk[..., :d], dv[..., :d], None
 
 

@@ -84,7 +84,9 @@ EXPORTS = (
     "fa_b200_fwd", "fa_b200_fwd_noalloc", "fa_b200_fwd_plan", "fa_b200_combine", "fa_b200_normalize_window",
     "fa_b200_check_status", "fa_b200_last_error", "fa_b200_status_string", "fa_b200_abi_version",
     "fa_b200_launch_count", "fa_b200_bwd", "fa_b200_bwd_workspace_bytes",
+    "fa_b200_plan_encode", "fa_b200_plan_decode", "fa_b200_fwd_planned",
 )
+PLAN_BYTES = 192  # FA_B200_PLAN_BYTES
 
 _lib = None
 
@@ -104,6 +106,12 @@ def load() -> C.CDLL:
     lib.fa_b200_fwd_noalloc.restype = C.c_int
     lib.fa_b200_fwd_plan.argtypes = [C.POINTER(FwdParams), C.POINTER(FwdPlan)]
     lib.fa_b200_fwd_plan.restype = C.c_int
+    lib.fa_b200_plan_encode.argtypes = [C.POINTER(FwdParams), _p, C.c_size_t]
+    lib.fa_b200_plan_encode.restype = C.c_int
+    lib.fa_b200_plan_decode.argtypes = [_p, C.c_size_t, C.POINTER(FwdPlan)]
+    lib.fa_b200_plan_decode.restype = C.c_int
+    lib.fa_b200_fwd_planned.argtypes = [C.POINTER(FwdParams), _p, C.c_size_t, _p, C.c_size_t, _p]
+    lib.fa_b200_fwd_planned.restype = C.c_int
     lib.fa_b200_bwd.argtypes = [C.POINTER(BwdParams), _p, C.c_size_t, _p]
     lib.fa_b200_bwd.restype = C.c_int
     lib.fa_b200_bwd_workspace_bytes.argtypes = [C.POINTER(BwdParams)]

@@ -173,12 +173,15 @@ def validate_forward(q, k, v, out, lse, kw) -> None:
             raise RuntimeError("lse must be a contiguous fp32 tensor of shape (b, h, s_q) / (h, total_q) on q's device")
 
 
-def attention_forward(q, k, v, *, out=None, lse=None, return_plan=False, **kw) -> Tuple[torch.Tensor, torch.Tensor]:
+def attention_forward(q, k, v, *, out=None, lse=None, return_plan=False, plan_bytes: Optional[bytes] = None,
+                      **kw) -> Tuple[torch.Tensor, torch.Tensor]:
     """Runs the forward on the current CUDA stream.  Returns (out, lse[, plan]).
 
     out has q's shape (dtype of q, fp32 when partial_out); lse is fp32 (b, h, s_q), or
     (h, total_q) for varlen q.  k / v caches are mutated in place when k_new, v_new are given.
     ``out`` / ``lse`` may be given (e.g. views of one message buffer); they are allocated otherwise.
+    ``plan_bytes``: a plan made ahead of the call (``encode_plan`` / get_scheduler_metadata); it is checked against
+    this call's shapes and taken over where it applies (fa_b200_fwd_planned).
     """
     lib = L.load()
     validate_forward(q, k, v, out, lse, kw)
@@ -191,14 +194,30 @@ def attention_forward(q, k, v, *, out=None, lse=None, return_plan=False, **kw) -
         p = build_params(q, k, v, out, lse, num_sm=_num_sm(q.device), **kw)
         plan = L.FwdPlan()
         L.check(lib.fa_b200_fwd_plan(C.byref(p), C.byref(plan)))
-        ws = None
-        if plan.workspace_bytes:
-            ws = torch.empty(plan.workspace_bytes, dtype=torch.uint8, device=q.device)
+        ws_bytes = plan.workspace_bytes
+        if plan_bytes is not None:
+            blob = C.create_string_buffer(bytes(plan_bytes), len(plan_bytes))
+            forced = L.FwdPlan()
+            L.check(lib.fa_b200_plan_decode(blob, len(plan_bytes), C.byref(forced)))
+            ws_bytes = max(ws_bytes, forced.workspace_bytes)  # whichever of the two plans ends up being used
+        ws = torch.empty(ws_bytes, dtype=torch.uint8, device=q.device) if ws_bytes else None
         stream = torch.cuda.current_stream(q.device).cuda_stream
-        L.check(lib.fa_b200_fwd(C.byref(p), _ptr(ws), plan.workspace_bytes, stream))
+        if plan_bytes is not None:
+            L.check(lib.fa_b200_fwd_planned(C.byref(p), blob, len(plan_bytes), _ptr(ws), ws_bytes, stream))
+        else:
+            L.check(lib.fa_b200_fwd(C.byref(p), _ptr(ws), ws_bytes, stream))
     if return_plan:
         return out, lse, plan
     return out, lse
+
+
+def encode_plan(p: "L.FwdParams") -> bytes:
+    """Plans the problem described by ``p`` (sizes, flags and NULL-ness of the pointers; nothing is dereferenced)
+    and returns the plan as FA_B200_PLAN_BYTES opaque bytes for ``attention_forward(plan_bytes=...)``."""
+    lib = L.load()
+    buf = C.create_string_buffer(L.PLAN_BYTES)
+    L.check(lib.fa_b200_plan_encode(C.byref(p), buf, L.PLAN_BYTES))
+    return buf.raw
 
 
 def attention_forward_noalloc(q, k, v, out, lse, **kw) -> None:

@@ -20,6 +20,9 @@
  *   fa_b200_fwd_plan            the host tiling / flash-decode decision of the same functions
  *                               (flash_api.cpp:514-556) and the split planner
  *                               csrc/arch22/flash_attn_npu_v3/fa_split.h:483-510
+ *   fa_b200_plan_encode /       get_scheduler_metadata, csrc/arch22/flash_attn_npu_v3/flash_api.cpp:493-558 (plan
+ *   fa_b200_plan_decode /       computed ahead of the call, returned as opaque bytes) and the scheduler_metadata_
+ *   fa_b200_fwd_planned         argument of mha_fwd, csrc/arch22/flash_attn_npu_v3/flash_api.cpp:92,322-380
  *   fa_b200_combine             CombineScale, csrc/arch22/flash_attn_npu_v2/CombineScale.hpp:76-357
  *                               (and the Python-level flash_attn_combine,
  *                                flash_attn_npu_v3/interface_arch22.py:930-931)
@@ -168,6 +171,22 @@ int fa_b200_fwd_noalloc(const fa_fwd_params* p, void* stream);
 /* Host-only: validates `p` and reports what fa_b200_fwd would launch.  Needs no GPU when
  * p->num_sm > 0. */
 int fa_b200_fwd_plan(const fa_fwd_params* p, fa_fwd_plan* plan);
+
+/* Plans as opaque bytes (the scheduler metadata of the reference's FA3-style API).
+ * fa_b200_plan_encode (host-only) plans `p` like fa_b200_fwd_plan -- only sizes, flags and NULL-ness of the
+ * pointers matter, the pointers are never dereferenced -- and writes FA_B200_PLAN_BYTES bytes: a header naming the
+ * problem (batch, max_seqlen_q, max_seqlen_k, heads, head dim, dtype, mask) and the plan.
+ * fa_b200_fwd_planned is fa_b200_fwd with such bytes: it refuses them (FA_ERR_INVALID) when they were made by
+ * another library version or for other shapes, dtype or mask; takes over kernel family, tile configuration and KV
+ * splits when the call has the same optional parts (cache lengths, pages, new tokens, ...) as the planned one; and
+ * plans afresh otherwise.  With a KV cache, max_seqlen_k of the plan bounds the keys of every sequence: a longer
+ * cache_seqlens entry is clamped and reported by fa_b200_check_status.  The workspace must hold the larger of
+ * fa_b200_plan_decode's and fa_b200_fwd_plan's workspace_bytes. */
+#define FA_B200_PLAN_BYTES 192
+int fa_b200_plan_encode(const fa_fwd_params* p, void* buf, size_t buf_bytes);
+int fa_b200_plan_decode(const void* buf, size_t buf_bytes, fa_fwd_plan* plan);
+int fa_b200_fwd_planned(const fa_fwd_params* p, const void* plan, size_t plan_bytes, void* workspace, size_t workspace_bytes,
+                        void* stream);
 
 /* ------------------------------------------------------------------------------------------------
  * Backward (dQ, dK, dV) of the dense / packed-varlen forward.  Replaces the reference's mha_bwd /
