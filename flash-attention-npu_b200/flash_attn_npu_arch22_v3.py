@@ -44,6 +44,14 @@ def fwd(q, k, v, k_new_, v_new_, q_v_, out_, cu_seqlens_q_, cu_seqlens_k_, cu_se
     if softmax_scale_ is None:
         softmax_scale_ = q.shape[-1] ** (-0.5)
     plan_bytes = _plan_bytes(scheduler_metadata_) if scheduler_metadata_ is not None else None
+    if k.dim() == 3 and cu_seqlens_k_ is None and seqused_k_ is not None and page_table_ is None:
+        # Packed (total_k, h_k, d) keys described by their per-sequence lengths alone: the reference's kernel takes
+        # the prefix sums of seqused_k as the sequence starts (its tests feed flash_attn_with_kvcache this way,
+        # tests/test_flash_attn_npu_v3.py:326-331,336-340).  The longest sequence is not known on the host, so the
+        # total serves as its bound.
+        _reject(k_new_ is not None, "appending new tokens needs a KV cache with one row per sequence")
+        cu_seqlens_k_ = torch.nn.functional.pad(torch.cumsum(seqused_k_, 0, dtype=torch.int32), (1, 0))
+        seqused_k_, max_seqlen_k_ = None, int(k.shape[0])
     out, lse = ops.attention_forward(
         q, k, v, out=out_, k_new=k_new_, v_new=v_new_, cu_seqlens_q=cu_seqlens_q_, cu_seqlens_k=cu_seqlens_k_,
         max_seqlen_q=max_seqlen_q_, max_seqlen_k=max_seqlen_k_, seqused_k=seqused_k_, cache_batch_idx=kv_batch_idx_,

@@ -1,7 +1,8 @@
 """GPU parity tests: the CUDA path, called through the drop-in Python modules (and so through the
 C ABI of libfa_b200.so), against (a) the committed reference-golden fixtures and (b) the CPU
-oracle on seeded inputs shaped like the reference's own test tables
-(tests/test_flash_attn_npu_v2.py:145-255, :410-431, :494-521 of the reference).
+oracle on seeded inputs of shapes the reference's own test tables do not have (ragged packed
+sequences, the host-buffer pipeline, tile-order chunks; the tables themselves are in
+test_reference_tables_gpu.py).
 
 Tolerance: the reference's rule rtol = atol = 1e-2 on O and LSE everywhere; its data_compare
 helper and the 2x-error rule additionally on N(0,1) inputs (on U(-5,5) bf16 inputs data_compare
@@ -51,139 +52,8 @@ def test_fixture(name):
 
 
 # ----------------------------------------------------------------------------------------------
-# (b) reference-style case tables, seeded, against the oracle
+# (b) the reference's case tables live in test_reference_tables_gpu.py (all rows); below: shapes they do not have
 # ----------------------------------------------------------------------------------------------
-KVCACHE_CASES = [
-    # dtype, batch, heads, kv_heads, s_q, s_kv, d, paged, causal, wl, wr, softcap
-    (BF, 1, 1, 1, 1024, 1024, 128, 1, False, -1, -1, 0.0),
-    (BF, 3, 4, 4, 1024, 1024, 128, 0, True, -1, -1, 0.0),
-    (FP, 3, 1, 1, 512, 512, 128, 1, False, -1, -1, 0.0),
-    (BF, 1, 1, 1, 1, 1024, 128, 1, True, -1, -1, 0.0),
-    (BF, 2, 16, 4, 256, 2048, 128, 0, True, -1, -1, 50.0),
-    (BF, 1, 32, 4, 65, 2048, 256, 0, False, -1, -1, 50.0),
-    (BF, 2, 24, 2, 6, 2048, 128, 0, False, -1, -1, 30.0),
-    (BF, 8, 64, 8, 1, 4096, 128, 0, False, -1, -1, 0.0),
-    (BF, 2, 128, 8, 1, 4096, 128, 0, False, -1, -1, 0.0),
-    (BF, 2, 128, 32, 64, 2048, 128, 0, True, -1, -1, 0.0),
-    (BF, 2, 64, 4, 10, 4096, 128, 0, False, -1, -1, 0.0),
-    (BF, 2, 64, 8, 1, 4096, 256, 0, False, -1, -1, 0.0),
-    (BF, 2, 32, 4, 16, 1024, 256, 0, False, -1, -1, 0.0),
-    (BF, 2, 16, 2, 5, 4096, 128, 1, True, -1, -1, 0.0),
-    (BF, 2, 16, 2, 15, 2048, 128, 1, True, -1, -1, 0.0),
-    (BF, 1, 64, 4, 7, 2048, 128, 1, False, -1, -1, 0.0),
-    (BF, 1, 32, 8, 13, 2048, 256, 1, False, -1, -1, 0.0),
-    (BF, 1, 128, 4, 1, 2048, 128, 1, True, -1, -1, 0.0),
-    (BF, 1, 10, 2, 10, 4096, 256, 1, True, -1, -1, 0.0),
-    (BF, 1, 1, 1, 1024, 1024, 128, 1, True, 512, 256, 0.0),
-    (BF, 1, 1, 1, 1024, 1024, 128, 1, True, 512, 0, 0.0),
-    (BF, 1, 1, 1, 1024, 1024, 128, 1, False, 0, 256, 0.0),
-    (FP, 2, 2, 2, 512, 512, 128, 0, False, 64, 128, 0.0),
-    (BF, 3, 4, 4, 1024, 1024, 128, 0, True, -128, 864, 0.0),
-    (FP, 2, 2, 1, 128, 128, 128, 1, True, -1, -1, 0.0),
-    (BF, 1, 8, 2, 1, 512, 128, 0, True, -1, -1, 0.0),
-]
-
-
-@pytest.mark.parametrize("case", KVCACHE_CASES, ids=lambda c: "-".join(str(x).replace("torch.", "") for x in c))
-def test_kvcache_table(case):
-    import flash_attn_npu_v2 as fa2
-    dtype, b, h, hk, sq, skv, d, paged, causal, wl, wr, softcap = case
-    g = torch.Generator().manual_seed(hash(case[1:]) % (2 ** 31))
-    q = U.uniform((b, sq, h, d), dtype, g)
-    page = 128
-    if paged:
-        per = (skv + page - 1) // page
-        nblk = max(64, per * b)
-        kc = U.uniform((nblk, page, hk, d), dtype, g)
-        vc = U.uniform((nblk, page, hk, d), dtype, g)
-        bt = torch.arange(per * b, dtype=torch.int32).view(b, per)  # identity table like the reference (:272-279)
-    else:
-        kc = U.uniform((b, skv, hk, d), dtype, g)
-        vc = U.uniform((b, skv, hk, d), dtype, g)
-        bt = None
-    lens = torch.full((b,), skv, dtype=torch.int32)
-    gold_out, gold_lse = OA.flash_attn_with_kvcache(q, kc, vc, cache_seqlens=lens, block_table=bt, causal=causal,
-                                                    window_size=(wl, wr), softcap=softcap)
-    out, lse = fa2.flash_attn_with_kvcache(q.cuda(), kc.cuda(), vc.cuda(), None, None, cache_seqlens=lens.cuda(),
-                                           block_table=_cuda(bt), causal=causal, window_size=[wl, wr],
-                                           softcap=softcap, rotary_interleaved=False, return_softmax_lse=True)
-    U.check_rules(out, lse, gold_out, gold_lse, strict_data_compare=False, tag=str(case))
-
-
-FWD_CASES = [
-    # dtype, batch, heads, kv_heads, s_q, s_kv, d, causal, softcap
-    (FP, 1, 1, 1, 1024, 1024, 128, False, 0.0),
-    (FP, 3, 4, 4, 1024, 1024, 128, True, 0.0),
-    (FP, 4, 2, 1, 513, 513, 128, False, 0.0),
-    (BF, 3, 4, 4, 1024, 1024, 128, True, 0.0),
-    (BF, 3, 1, 1, 512, 512, 128, False, 0.0),
-    (FP, 3, 1, 1, 512, 512, 128, False, 30.0),
-    (BF, 2, 4, 4, 1024, 1024, 128, True, 50.0),
-    (BF, 2, 4, 2, 300, 300, 64, True, 0.0),
-]
-
-
-@pytest.mark.parametrize("case", FWD_CASES, ids=lambda c: "-".join(str(x).replace("torch.", "") for x in c))
-def test_fwd_table(case):
-    import flash_attn_npu_v2 as fa2
-    dtype, b, h, hk, sq, skv, d, causal, softcap = case
-    g = torch.Generator().manual_seed(hash(case[1:]) % (2 ** 31))
-    q = U.uniform((b, sq, h, d), dtype, g)
-    k = U.uniform((b, skv, hk, d), dtype, g)
-    v = U.uniform((b, skv, hk, d), dtype, g)
-    gold_out, gold_lse = OA.flash_attn_func(q, k, v, causal=causal, softcap=softcap)
-    out, lse, _ = fa2.flash_attn_func(q.cuda(), k.cuda(), v.cuda(), 0.0, causal=causal, window_size=[-1, -1],
-                                      softcap=softcap, return_attn_probs=True)
-    U.check_rules(out, lse, gold_out, gold_lse, strict_data_compare=False, tag=str(case))
-    out_only = fa2.flash_attn_func(q.cuda(), k.cuda(), v.cuda(), causal=causal, softcap=softcap)
-    assert torch.equal(out_only, out)
-
-
-VARLEN_CASES = [
-    # dtype, batch, heads, kv_heads, s_q, s_kv, d, causal, wl, wr, softcap
-    (BF, 1, 1, 1, 512, 1024, 128, True, -1, -1, 0.0),
-    (BF, 2, 4, 4, 1024, 1024, 128, False, -1, -1, 0.0),
-    (FP, 3, 5, 1, 512, 512, 128, True, -1, -1, 0.0),
-    (FP, 3, 5, 1, 777, 888, 192, False, -1, -1, 0.0),
-    (FP, 2, 5, 1, 777, 888, 256, True, -1, -1, 0.0),
-    (BF, 1, 1, 1, 1777, 2048, 64, True, -1, -1, 0.0),
-    (BF, 2, 5, 1, 311, 2048, 111, True, -1, -1, 0.0),
-    (BF, 1, 1, 1, 512, 512, 128, True, 512, 0, 0.0),
-    (BF, 1, 1, 1, 512, 512, 128, True, 256, 128, 0.0),
-    (FP, 2, 4, 4, 256, 256, 128, False, 64, 128, 0.0),
-    (BF, 1, 1, 1, 512, 512, 128, False, 0, 256, 0.0),
-    (BF, 2, 6, 2, 128, 256, 128, True, 127, 0, 0.0),
-    (BF, 2, 4, 4, 128, 512, 128, True, 511, 0, 0.0),
-    (FP, 1, 2, 2, 64, 192, 128, False, 32, 64, 0.0),
-    (BF, 1, 1, 1, 1, 1024, 128, True, 512, 0, 0.0),
-    (FP, 2, 1, 1, 512, 512, 128, False, 508, -256, 0.0),
-    (BF, 1, 1, 1, 1024, 1024, 128, True, -128, 864, 0.0),
-    (BF, 2, 6, 2, 2, 1024, 128, True, 256, 0, 0.0),
-    (FP, 3, 5, 1, 777, 888, 192, False, -1, -1, 30.0),
-    (BF, 2, 5, 1, 311, 2048, 111, True, -1, -1, 50.0),
-]
-
-
-@pytest.mark.parametrize("case", VARLEN_CASES, ids=lambda c: "-".join(str(x).replace("torch.", "") for x in c))
-def test_varlen_table(case):
-    import flash_attn_npu_v2 as fa2
-    dtype, b, h, hk, sq, skv, d, causal, wl, wr, softcap = case
-    g = torch.Generator().manual_seed(hash(case[1:]) % (2 ** 31))
-    q = U.uniform((b * sq, h, d), dtype, g)
-    k = U.uniform((b * skv, hk, d), dtype, g)
-    v = U.uniform((b * skv, hk, d), dtype, g)
-    cq = torch.arange(0, (b + 1) * sq, sq, dtype=torch.int32)
-    ck = torch.arange(0, (b + 1) * skv, skv, dtype=torch.int32)
-    scale = 1.0 / d ** 0.5
-    gold_out, gold_lse = OA.flash_attn_varlen_func(q, k, v, cq, ck, sq, skv, softmax_scale=scale, causal=causal,
-                                                   window_size=(wl, wr), softcap=softcap)
-    out, lse, _ = fa2.flash_attn_varlen_func(q.cuda(), k.cuda(), v.cuda(), cq.cuda(), ck.cuda(), sq, skv,
-                                             dropout_p=0.0, softmax_scale=scale, causal=causal,
-                                             window_size=(wl, wr), softcap=softcap, return_attn_probs=True)
-    assert out.shape == q.shape and lse.shape == (h, b * sq)
-    U.check_rules(out, lse, gold_out, gold_lse, strict_data_compare=False, tag=str(case))
-
-
 def test_varlen_ragged_lengths():
     """Ragged, including an empty sequence (the reference tables only use equal lengths)."""
     import flash_attn_npu_v2 as fa2
