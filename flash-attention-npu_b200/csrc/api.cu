@@ -328,15 +328,35 @@ static int make_plan(const fa_fwd_params& a_in, Planned* out, const fa_fwd_plan*
   return FA_OK;
 }
 
+// The merge kernel is launched with programmatic stream serialisation: the launch itself and the start of its CTAs
+// overlap the tail of the kernel in front of it on the stream (the split-KV attention kernel, which signals
+// griddepcontrol.launch_dependents when it starts); the kernel waits for that kernel's completion before it reads
+// (combine.cuh).  This hides most of what a second launch costs behind a kernel of a few hundred microseconds.
+template <typename OutT>
+static cudaError_t launch_combine_t(const fa_combine_params& c, int grid, cudaStream_t st) {
+  cudaLaunchConfig_t cfg;
+  std::memset(&cfg, 0, sizeof(cfg));
+  cfg.gridDim = dim3(grid);
+  cfg.blockDim = dim3(kCombineWarps * 32);
+  cfg.dynamicSmemBytes = 0;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, combine_kernel<OutT>, c);
+}
+
 static int launch_combine(const fa_combine_params& c, cudaStream_t st) {
   const int64_t rows = (int64_t)c.b * c.s * c.h;
   if (rows == 0) return FA_OK;
   const int grid = (int)((rows + kCombineWarps - 1) / kCombineWarps);
-  if (c.out_dtype == FA_BF16) combine_kernel<__nv_bfloat16><<<grid, kCombineWarps * 32, 0, st>>>(c);
-  else if (c.out_dtype == FA_FP16) combine_kernel<__half><<<grid, kCombineWarps * 32, 0, st>>>(c);
-  else if (c.out_dtype == 2) combine_kernel<float><<<grid, kCombineWarps * 32, 0, st>>>(c);
+  cudaError_t e;
+  if (c.out_dtype == FA_BF16) e = launch_combine_t<__nv_bfloat16>(c, grid, st);
+  else if (c.out_dtype == FA_FP16) e = launch_combine_t<__half>(c, grid, st);
+  else if (c.out_dtype == 2) e = launch_combine_t<float>(c, grid, st);
   else return fail(FA_ERR_INVALID, "bad out_dtype");
-  cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return fail(FA_ERR_CUDA, std::string("combine launch: ") + cudaGetErrorString(e));
   ++g_launches;
   return FA_OK;

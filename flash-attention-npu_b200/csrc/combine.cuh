@@ -33,6 +33,10 @@ __device__ __forceinline__ void store4<__half>(__half* dst, float4 v) {
 
 template <typename OutT>
 __global__ void __launch_bounds__(kCombineWarps * 32) combine_kernel(const __grid_constant__ fa_combine_params p) {
+  // The merge is launched as a programmatic dependent of the kernel in front of it (launch_combine): its CTAs may
+  // become resident while that kernel still runs and wait here until it has completed and its writes are visible.
+  // Without such a kernel in front this returns at once.
+  asm volatile("griddepcontrol.wait;\n" ::: "memory");
   const int lane = threadIdx.x & 31;
   const int64_t row = (int64_t)blockIdx.x * kCombineWarps + (threadIdx.x >> 5);
   const int64_t n_rows = (int64_t)p.b * p.s * p.h;

@@ -28,6 +28,8 @@ fwd_decode_kernel(const __grid_constant__ KParams p, const __grid_constant__ CUt
   __shared__ DecSeg s_seg;
   __shared__ DecWalk s_walk;
 
+  // A merge kernel queued behind this one may start launching its CTAs now (they wait for this grid to complete).
+  asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int g8 = lane >> 2, t4 = lane & 3;
   const int wm = (warp < Tr::NCW) ? warp / Tr::WN : 0;  // row group of a consumer warp

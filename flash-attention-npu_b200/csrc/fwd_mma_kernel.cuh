@@ -13,6 +13,8 @@ __global__ void __launch_bounds__(Tr::NTHREADS) fwd_mma_kernel(const __grid_cons
   __shared__ int s_red[32];
   __shared__ float s_lse[Tr::BM];
 
+  // A merge kernel queued behind this one may start launching its CTAs now (they wait for this grid to complete).
+  asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int wm = warp / Tr::WN, wn = warp % Tr::WN;
   const int g8 = lane >> 2, t4 = lane & 3;
