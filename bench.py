@@ -387,9 +387,18 @@ class DecodeLongSharded(DecodeBase):
     strong = True
     use_graph = True
 
+    exchange = "peer"  # "peer": partials over peer memory (flash_b200.dist.PeerExchange); "nccl": all-gather + merge
+    px = None
+
     def setup(self, dev, rank, world):
         from flash_b200 import dist as D
         self.world = world
+        if world > 1 and self.exchange == "peer":
+            try:
+                self.px = D.PeerExchange(self.b * self.h, self.d, dev)
+            except Exception as e:  # every rank fails alike (the handles travel through a collective)
+                print(f"[bench] peer exchange unavailable ({e}); using the NCCL all-gather", file=sys.stderr)
+                self.px = None
         self.lo, self.hi = D.kv_shard_range(self.L, world, rank)
         g = torch.Generator(device=dev).manual_seed(5)
         self.q = torch.randn((self.b, 1, self.h, self.d), generator=g, device=dev).to(BF)
@@ -401,7 +410,16 @@ class DecodeLongSharded(DecodeBase):
 
     def run(self, q):
         from flash_b200 import dist as D
-        return D.sharded_decode(q, self.kc, self.vc, kv_pos_offset=self.lo, kv_total=self.L, causal=True)
+        return D.sharded_decode(q, self.kc, self.vc, kv_pos_offset=self.lo, kv_total=self.L, causal=True, exchange=self.px)
+
+    def release(self):
+        super().release()
+        if self.px is not None:
+            import torch.distributed as dist
+            torch.cuda.synchronize()
+            dist.barrier()  # every rank has finished its last merge before anybody unmaps
+            self.px.close()
+            self.px = None
 
     def cpu_sample(self, budget_s):
         """Oracle on the first 16384 keys of one sequence of this configuration, generated on the host."""
@@ -482,6 +500,8 @@ def measure(key, args, steps, warmup, dev, rank, world, local_rank, peaks, barri
     import torch.distributed as dist
     from flash_b200 import lib as _L
     wl = WORKLOADS[key]()
+    if key == "c5":
+        wl.exchange = args.c5_exchange
     if args.shrink > 1:
         if key == "c5":
             wl.L //= args.shrink
@@ -580,6 +600,9 @@ def measure(key, args, steps, warmup, dev, rank, world, local_rank, peaks, barri
             "gpu_launches": gpu_launches,
             "clocks": clocks,
         }
+        if key == "c5":
+            entry["config"]["exchange"] = ("peer memory (NVLink stores + flags)" if getattr(wl, "px", None) is not None
+                                           else ("NCCL all-gather" if world > 1 else "none (one rank)"))
         if wl.bound == "hbm":  # the north star quotes the decode target against the nominal 8 TB/s too
             entry["roofline"]["frac_of_nominal_8tbs"] = achieved / 8000.0
         if not args.no_cpu_baseline and world == 1:
@@ -604,6 +627,8 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--cpu-budget", type=float, default=12.0)
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (profiling runs)")
+    ap.add_argument("--c5-exchange", default="peer", choices=["peer", "nccl"],
+                    help="how the sequence shards of c5 are merged across GPUs")
     ap.add_argument("--shrink", type=int, default=1,
                     help="divide the batch (c2-c4) or the key length (c5) by this factor: small cases for ncu captures")
     args = ap.parse_args()

@@ -14,6 +14,7 @@
 #include <string>
 
 #include "combine.cuh"
+#include "exchange.cuh"
 #include "decode_configs.cuh"
 #include "mma_configs.cuh"
 #include "tc5_api.cuh"
@@ -362,8 +363,9 @@ static int launch_combine(const fa_combine_params& c, cudaStream_t st) {
   return FA_OK;
 }
 
+// skip_merge: leave the split partials in the workspace (the caller merges them itself); *splits_out = their number.
 static int run_fwd(const fa_fwd_params& a, void* workspace, size_t workspace_bytes, cudaStream_t st,
-                   const fa_fwd_plan* forced = nullptr) {
+                   const fa_fwd_plan* forced = nullptr, bool skip_merge = false, int* splits_out = nullptr) {
   if (!a.q || !a.k || !a.v || !a.o || !a.lse) return fail(FA_ERR_INVALID, "q, k, v, o and lse must be non-null");
   Planned P;
   int rc = make_plan(a, &P, forced);
@@ -427,8 +429,9 @@ static int run_fwd(const fa_fwd_params& a, void* workspace, size_t workspace_byt
   }
   if (e != cudaSuccess) return fail(FA_ERR_CUDA, std::string("attention kernel launch: ") + cudaGetErrorString(e));
   ++g_launches;
+  if (splits_out) *splits_out = P.pl.num_splits;
 
-  if (P.pl.num_splits > 1) {
+  if (P.pl.num_splits > 1 && !skip_merge) {
     fa_combine_params c;
     std::memset(&c, 0, sizeof(c));
     const bool varlen_q = a.cu_seqlens_q != nullptr;
@@ -508,6 +511,108 @@ static int run_fwd_noalloc(const fa_fwd_params& a_in, cudaStream_t st) {
   rc = noalloc_scratch_ptr(&scratch);
   if (rc != FA_OK) return rc;
   return run_fwd(a, scratch, kNoAllocScratchBytes, st);
+}
+
+// ------------------------------------------------------------------------------------------------
+// Sequence-sharded decode across GPUs over peer memory (exchange.cuh).
+// ------------------------------------------------------------------------------------------------
+static size_t exchange_bytes(int world, int64_t rows, int d) {
+  return (size_t)kXchgHeaderBytes + (size_t)2 * world * rows * (d + 4) * sizeof(float);
+}
+
+static size_t exchange_workspace(const fa_fwd_params& a, int ns) {
+  const size_t lse_elems = (size_t)a.b * a.h * a.seqlen_q;
+  return (((size_t)ns * lse_elems * sizeof(float) + 15) & ~(size_t)15) + (size_t)ns * lse_elems * a.d * sizeof(float);
+}
+
+template <typename Kern>
+static cudaError_t launch_dependent(Kern kern, const XchgParams& xp, int grid, cudaStream_t st) {
+  cudaLaunchConfig_t cfg;
+  std::memset(&cfg, 0, sizeof(cfg));
+  cfg.gridDim = dim3(grid);
+  cfg.blockDim = dim3(kCombineWarps * 32);
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kern, xp);
+}
+
+static int run_fwd_exchange(const fa_fwd_params& a_in, void* workspace, size_t workspace_bytes, const fa_exchange& x,
+                            cudaStream_t st) {
+  if (!a_in.q || !a_in.k || !a_in.v || !a_in.o || !a_in.lse) return fail(FA_ERR_INVALID, "q, k, v, o and lse must be non-null");
+  if (x.world < 1 || x.world > FA_B200_MAX_RANKS || x.rank < 0 || x.rank >= x.world)
+    return fail(FA_ERR_INVALID, "bad rank / world size of the exchange");
+  for (int r = 0; r < x.world; ++r)
+    if (!x.bufs[r]) return fail(FA_ERR_INVALID, "an exchange buffer is not mapped");
+  if (a_in.cu_seqlens_q) return fail(FA_ERR_UNSUPPORTED, "the cross-GPU exchange takes dense (b, s_q, h, d) queries");
+  if (a_in.d % 4 != 0) return fail(FA_ERR_INVALID, "head dimension must be a multiple of 4");
+  const int64_t rows = (int64_t)a_in.b * a_in.seqlen_q * a_in.h;
+  if (x.buf_bytes < exchange_bytes(x.world, rows, a_in.d))
+    return fail(FA_ERR_WORKSPACE, "the exchange buffers are too small for this problem (fa_b200_exchange_bytes)");
+  if (rows == 0) return FA_OK;
+
+  // the attention over this rank's keys leaves fp32 partials [split][b, h, s_q] / [split][b, h, s_q][d] in the workspace
+  fa_fwd_params a = a_in;
+  a.partial_out = 1;
+  a.lse_batch_stride = (int64_t)a.h * a.seqlen_q;
+  a.lse_head_stride = a.seqlen_q;
+  Planned P;
+  int rc = make_plan(a, &P);
+  if (rc != FA_OK) return rc;
+  const int ns_plan = P.pl.kernel == FA_KERNEL_TCGEN05 ? 1 : P.pl.num_splits;
+  const size_t need = exchange_workspace(a, ns_plan);
+  if (!workspace || workspace_bytes < need) return fail(FA_ERR_WORKSPACE, "workspace missing or too small (fa_b200_fwd_exchange_workspace)");
+  if ((reinterpret_cast<uintptr_t>(workspace) & 15) != 0) return fail(FA_ERR_WORKSPACE, "workspace must be 16-byte aligned");
+  const size_t lse_elems = (size_t)a.b * a.h * a.seqlen_q;
+  float* lse_part = reinterpret_cast<float*>(workspace);
+  float* o_part = reinterpret_cast<float*>(reinterpret_cast<char*>(workspace) + (((size_t)ns_plan * lse_elems * sizeof(float) + 15) & ~(size_t)15));
+  a.lse = lse_part;  // a single split writes its partial through o / lse, laid out like slot 0 of the split layout
+  a.o = o_part;
+  a.o_batch_stride = (int64_t)a.h * a.seqlen_q * a.d;
+  a.o_head_stride = (int64_t)a.seqlen_q * a.d;
+  a.o_row_stride = a.d;
+  int ns = 1;
+  rc = run_fwd(a, workspace, workspace_bytes, st, nullptr, true, &ns);
+  if (rc != FA_OK) return rc;
+  if (ns != ns_plan) return fail(FA_ERR_CUDA, "split plan changed between planning and launch");
+
+  XchgParams xp;
+  std::memset(&xp, 0, sizeof(xp));
+  fa_combine_params& c = xp.c;
+  c.o_partial = o_part;
+  c.lse_partial = lse_part;
+  c.o = a_in.o;
+  c.lse = a_in.lse;
+  c.num_splits = ns;
+  c.b = a.b; c.s = a.seqlen_q; c.h = a.h; c.d = a.d;
+  c.lp_split_stride = (int64_t)lse_elems;
+  c.lp_batch_stride = a.lse_batch_stride;
+  c.lp_row_stride = 1;
+  c.lp_head_stride = a.lse_head_stride;
+  c.op_split_stride = (int64_t)lse_elems * a.d;
+  c.op_batch_stride = a.lse_batch_stride * a.d;
+  c.op_row_stride = a.d;
+  c.op_head_stride = a.lse_head_stride * a.d;
+  c.o_batch_stride = a_in.o_batch_stride; c.o_row_stride = a_in.o_row_stride; c.o_head_stride = a_in.o_head_stride;
+  c.lse_batch_stride = a_in.lse_batch_stride; c.lse_row_stride = 1; c.lse_head_stride = a_in.lse_head_stride;
+  c.out_dtype = a_in.dtype;
+  for (int r = 0; r < x.world; ++r) xp.bufs[r] = reinterpret_cast<char*>(x.bufs[r]);
+  xp.world = x.world;
+  xp.rank = x.rank;
+  xp.timeout_cycles = x.timeout_cycles > 0 ? x.timeout_cycles : 4000000000LL;  // about two seconds of SM clock
+  xp.status = device_status_word();
+  const int grid = (int)((rows + kCombineWarps - 1) / kCombineWarps);
+  cudaError_t e = launch_dependent(xchg_push_kernel, xp, grid, st);
+  if (e != cudaSuccess) return fail(FA_ERR_CUDA, std::string("exchange push launch: ") + cudaGetErrorString(e));
+  ++g_launches;
+  e = a_in.dtype == FA_BF16 ? launch_dependent(xchg_merge_kernel<__nv_bfloat16>, xp, grid, st)
+                            : launch_dependent(xchg_merge_kernel<__half>, xp, grid, st);
+  if (e != cudaSuccess) return fail(FA_ERR_CUDA, std::string("exchange merge launch: ") + cudaGetErrorString(e));
+  ++g_launches;
+  return FA_OK;
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -637,6 +742,68 @@ int fa_b200_plan_decode(const void* buf, size_t buf_bytes, fa_fwd_plan* plan) {
   return rc;
 }
 
+size_t fa_b200_exchange_bytes(int32_t world, int64_t rows, int32_t d) { return fa::exchange_bytes(world, rows, d); }
+
+int fa_b200_exchange_alloc(size_t bytes, void** ptr, void* handle64) {
+  fa::g_err.clear();
+  if (!ptr || !handle64 || bytes < (size_t)fa::kXchgHeaderBytes) return fa::fail(FA_ERR_INVALID, "bad argument");
+  static_assert(sizeof(cudaIpcMemHandle_t) == 64, "IPC handles are 64 bytes");
+  void* q = nullptr;
+  cudaError_t e = cudaMalloc(&q, bytes);
+  if (e == cudaSuccess) e = cudaMemset(q, 0, bytes);
+  cudaIpcMemHandle_t h;
+  if (e == cudaSuccess) e = cudaIpcGetMemHandle(&h, q);
+  if (e != cudaSuccess) {
+    if (q) cudaFree(q);
+    return fa::fail(FA_ERR_CUDA, std::string("exchange buffer: ") + cudaGetErrorString(e));
+  }
+  std::memcpy(handle64, &h, sizeof(h));
+  *ptr = q;
+  return FA_OK;
+}
+
+int fa_b200_exchange_open(const void* handle64, void** ptr) {
+  fa::g_err.clear();
+  if (!ptr || !handle64) return fa::fail(FA_ERR_INVALID, "bad argument");
+  cudaIpcMemHandle_t h;
+  std::memcpy(&h, handle64, sizeof(h));
+  void* q = nullptr;
+  const cudaError_t e = cudaIpcOpenMemHandle(&q, h, cudaIpcMemLazyEnablePeerAccess);
+  if (e != cudaSuccess) return fa::fail(FA_ERR_CUDA, std::string("mapping a peer's exchange buffer: ") + cudaGetErrorString(e));
+  *ptr = q;
+  return FA_OK;
+}
+
+int fa_b200_exchange_close(void* ptr) {
+  fa::g_err.clear();
+  const cudaError_t e = cudaIpcCloseMemHandle(ptr);
+  return e == cudaSuccess ? FA_OK : fa::fail(FA_ERR_CUDA, std::string("unmapping a peer's exchange buffer: ") + cudaGetErrorString(e));
+}
+
+int fa_b200_exchange_free(void* ptr) {
+  fa::g_err.clear();
+  const cudaError_t e = cudaFree(ptr);
+  return e == cudaSuccess ? FA_OK : fa::fail(FA_ERR_CUDA, std::string("freeing the exchange buffer: ") + cudaGetErrorString(e));
+}
+
+size_t fa_b200_fwd_exchange_workspace(const fa_fwd_params* p) {
+  if (!p) return 0;
+  fa::g_err.clear();
+  fa_fwd_params a = *p;
+  a.partial_out = 1;
+  a.lse_batch_stride = (int64_t)a.h * a.seqlen_q;
+  a.lse_head_stride = a.seqlen_q;
+  fa::Planned P;
+  if (fa::make_plan(a, &P) != FA_OK) return 0;
+  return fa::exchange_workspace(a, P.pl.kernel == FA_KERNEL_TCGEN05 ? 1 : P.pl.num_splits);
+}
+
+int fa_b200_fwd_exchange(const fa_fwd_params* p, void* workspace, size_t workspace_bytes, const fa_exchange* x, void* stream) {
+  if (!p || !x) return fa::fail(FA_ERR_INVALID, "null argument");
+  fa::g_err.clear();
+  return fa::run_fwd_exchange(*p, workspace, workspace_bytes, *x, reinterpret_cast<cudaStream_t>(stream));
+}
+
 int fa_b200_fwd_plan(const fa_fwd_params* p, fa_fwd_plan* plan) {
   if (!p || !plan) return fa::fail(FA_ERR_INVALID, "null argument");
   fa::g_err.clear();
@@ -671,6 +838,9 @@ int fa_b200_check_status(void* stream) {
   const int v = fa::tc5_read_status(reinterpret_cast<cudaStream_t>(stream));
   if (v == 0) return FA_OK;
   if (v < 0) return fa::fail(FA_ERR_CUDA, "cannot read the device status word");
+  if (v & fa::kStatusExchangeTimeout)
+    return fa::fail(FA_ERR_CUDA, "a rank did not deliver its partial to the cross-GPU merge within the time limit "
+                                 "(results of that call are invalid)");
   if (v & fa::kStatusBadIndex)
     return fa::fail(FA_ERR_INVALID, "a block_table / cache_batch_idx entry or a cache length was out of range "
                                     "(the kernels read zeros instead; results of that launch are invalid)");

@@ -1,0 +1,170 @@
+// Cross-GPU merge of sequence-sharded decode partials over peer memory (NVLink), one process per GPU.
+//
+// Every rank holds one exchange buffer that all ranks have mapped (CUDA IPC):
+//   header | data[2 parities][world][rows][d + 4] fp32   (a row is O[d], LSE, 3 floats of padding: 16-byte aligned)
+// Step e (a device-side epoch, so that a captured graph can be replayed):
+//   push kernel    merges this rank's split partials row by row (the arithmetic of combine.cuh) and writes the
+//                  row (O, LSE) into slot [e & 1][rank] of EVERY rank's buffer with plain stores; the CTA that
+//                  finishes last publishes the epoch into flags[rank] of every rank (release, system scope);
+//   merge kernel   waits until flags[r] >= e for every r (acquire, system scope, bounded by a cycle budget: on
+//                  expiry it raises kStatusExchangeTimeout and goes on, the results of that call are invalid),
+//                  then merges the world partials of slot [e & 1] into the output.
+// A rank can be at most one step ahead of another (its merge of step e waits for the others' push of step e, which
+// follows their merge of step e - 1 on their streams), so two parities are enough.  No multicast, no collective
+// library: plain peer stores and loads.  The merged result equals what an all-gather followed by the merge kernel
+// gives (same arithmetic, same order), which is how flash_b200.dist checks it.
+#pragma once
+
+#include "combine.cuh"
+
+namespace fa {
+
+constexpr int kStatusExchangeTimeout = 0x08000000;
+constexpr int kXchgHeaderBytes = 256;
+
+struct XchgHeader {
+  unsigned int epoch;        // steps this rank has pushed
+  unsigned int done_ctas;    // push kernel: CTAs finished in the current step
+  unsigned int flags[FA_B200_MAX_RANKS];  // flags[r]: steps rank r has delivered into this buffer
+};
+static_assert(sizeof(XchgHeader) <= kXchgHeaderBytes, "exchange header too large");
+
+struct XchgParams {
+  fa_combine_params c;      // local partials (o_partial / lse_partial, strides, sizes); o / lse = final output
+  char* bufs[FA_B200_MAX_RANKS];
+  int32_t world, rank;
+  long long timeout_cycles;
+  int32_t* status;
+};
+
+__device__ __forceinline__ float* xchg_row(char* buf, int parity, int world, int src_rank, int64_t n_rows, int d, int64_t row) {
+  const int64_t slot = ((int64_t)parity * world + src_rank) * n_rows + row;
+  return reinterpret_cast<float*>(buf + kXchgHeaderBytes) + slot * (d + 4);
+}
+
+__global__ void __launch_bounds__(kCombineWarps * 32) xchg_push_kernel(const __grid_constant__ XchgParams p) {
+  asm volatile("griddepcontrol.wait;\n" ::: "memory");  // the attention kernel in front has completed
+  const fa_combine_params& c = p.c;
+  XchgHeader* hdr = reinterpret_cast<XchgHeader*>(p.bufs[p.rank]);
+  const unsigned int epoch = *reinterpret_cast<volatile unsigned int*>(&hdr->epoch) + 1u;  // this step
+  const int parity = (int)(epoch & 1u);
+  const int lane = threadIdx.x & 31;
+  const int64_t row = (int64_t)blockIdx.x * kCombineWarps + (threadIdx.x >> 5);
+  const int64_t n_rows = (int64_t)c.b * c.s * c.h;
+  if (row < n_rows) {
+    const int hh = (int)(row % c.h);
+    const int ss = (int)((row / c.h) % c.s);
+    const int bb = (int)(row / ((int64_t)c.h * c.s));
+    const float* lp = c.lse_partial + bb * c.lp_batch_stride + ss * c.lp_row_stride + hh * c.lp_head_stride;
+    const float* op = c.o_partial + bb * c.op_batch_stride + ss * c.op_row_stride + hh * c.op_head_stride;
+    float m = -INFINITY;
+    for (int i = lane; i < c.num_splits; i += 32) m = fmaxf(m, lp[(int64_t)i * c.lp_split_stride]);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+    const bool dead = (m == -INFINITY);
+    float tot = 0.f;
+    if (!dead)
+      for (int i = lane; i < c.num_splits; i += 32) tot += __expf(lp[(int64_t)i * c.lp_split_stride] - m);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) tot += __shfl_xor_sync(0xffffffffu, tot, o);
+    const float inv = dead ? 0.f : 1.f / tot;
+    const float lse_row = dead ? -INFINITY : m + logf(tot);
+    for (int col = lane * 4; col < c.d; col += 128) {
+      float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (!dead) {
+        for (int i = 0; i < c.num_splits; ++i) {
+          const float l = lp[(int64_t)i * c.lp_split_stride];
+          if (l == -INFINITY) continue;
+          const float w = __expf(l - m) * inv;
+          const float4 x = *reinterpret_cast<const float4*>(op + (int64_t)i * c.op_split_stride + col);
+          acc.x += w * x.x; acc.y += w * x.y; acc.z += w * x.z; acc.w += w * x.w;
+        }
+      }
+      for (int r = 0; r < p.world; ++r) {  // the same row into every rank's buffer (peer stores over NVLink)
+        *reinterpret_cast<float4*>(xchg_row(p.bufs[r], parity, p.world, p.rank, n_rows, c.d, row) + col) = acc;
+      }
+    }
+    if (lane == 0)
+      for (int r = 0; r < p.world; ++r) xchg_row(p.bufs[r], parity, p.world, p.rank, n_rows, c.d, row)[c.d] = lse_row;
+  }
+  // The CTA that finishes last publishes the step to every rank.
+  __threadfence_system();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const unsigned int before = atomicAdd(&hdr->done_ctas, 1u);
+    if (before + 1u == gridDim.x) {
+      hdr->done_ctas = 0u;
+      *reinterpret_cast<volatile unsigned int*>(&hdr->epoch) = epoch;
+      __threadfence_system();
+      for (int r = 0; r < p.world; ++r) {
+        unsigned int* flag = &reinterpret_cast<XchgHeader*>(p.bufs[r])->flags[p.rank];
+        asm volatile("st.release.sys.global.u32 [%0], %1;\n" ::"l"(flag), "r"(epoch) : "memory");
+      }
+    }
+  }
+}
+
+template <typename OutT>
+__global__ void __launch_bounds__(kCombineWarps * 32) xchg_merge_kernel(const __grid_constant__ XchgParams p) {
+  asm volatile("griddepcontrol.wait;\n" ::: "memory");  // this rank's push kernel has completed (and set the epoch)
+  const fa_combine_params& c = p.c;
+  char* buf = p.bufs[p.rank];
+  XchgHeader* hdr = reinterpret_cast<XchgHeader*>(buf);
+  const unsigned int epoch = *reinterpret_cast<volatile unsigned int*>(&hdr->epoch);
+  const int parity = (int)(epoch & 1u);
+  __shared__ int s_ok;
+  if (threadIdx.x == 0) {
+    int ok = 1;
+    const long long t0 = clock64();
+    for (int r = 0; r < p.world && ok; ++r) {
+      const unsigned int* flag = &hdr->flags[r];
+      for (;;) {
+        unsigned int v;
+        asm volatile("ld.acquire.sys.global.u32 %0, [%1];\n" : "=r"(v) : "l"(flag) : "memory");
+        if ((int)(v - epoch) >= 0) break;
+        if (clock64() - t0 > p.timeout_cycles) {  // a rank did not deliver: give up, say so, keep the context usable
+          ok = 0;
+          if (p.status) atomicOr(p.status, kStatusExchangeTimeout);
+          break;
+        }
+        __nanosleep(200);
+      }
+    }
+    s_ok = ok;
+  }
+  __syncthreads();
+  if (!s_ok) return;
+  const int lane = threadIdx.x & 31;
+  const int64_t row = (int64_t)blockIdx.x * kCombineWarps + (threadIdx.x >> 5);
+  const int64_t n_rows = (int64_t)c.b * c.s * c.h;
+  if (row >= n_rows) return;
+  const int hh = (int)(row % c.h);
+  const int ss = (int)((row / c.h) % c.s);
+  const int bb = (int)(row / ((int64_t)c.h * c.s));
+  float m = -INFINITY;
+  for (int r = 0; r < p.world; ++r) m = fmaxf(m, __ldcg(xchg_row(buf, parity, p.world, r, n_rows, c.d, row) + c.d));
+  const bool dead = (m == -INFINITY);
+  float tot = 0.f;
+  if (!dead)
+    for (int r = 0; r < p.world; ++r) tot += __expf(__ldcg(xchg_row(buf, parity, p.world, r, n_rows, c.d, row) + c.d) - m);
+  const float inv = dead ? 0.f : 1.f / tot;
+  OutT* out = reinterpret_cast<OutT*>(c.o) + bb * c.o_batch_stride + ss * c.o_row_stride + hh * c.o_head_stride;
+  for (int col = lane * 4; col < c.d; col += 128) {
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (!dead) {
+      for (int r = 0; r < p.world; ++r) {
+        const float* src = xchg_row(buf, parity, p.world, r, n_rows, c.d, row);
+        const float l = __ldcg(src + c.d);
+        if (l == -INFINITY) continue;
+        const float w = __expf(l - m) * inv;
+        const float4 x = __ldcg(reinterpret_cast<const float4*>(src + col));
+        acc.x += w * x.x; acc.y += w * x.y; acc.z += w * x.z; acc.w += w * x.w;
+      }
+    }
+    store4<OutT>(out + col, acc);
+  }
+  if (c.lse && lane == 0)
+    c.lse[bb * c.lse_batch_stride + ss * c.lse_row_stride + hh * c.lse_head_stride] = dead ? INFINITY : m + logf(tot);
+}
+
+}  // namespace fa

@@ -79,12 +79,23 @@ class BwdParams(C.Structure):
     )
 
 
+MAX_RANKS = 16  # FA_B200_MAX_RANKS
+
+
+class Exchange(C.Structure):
+    """Mirror of ``fa_exchange``."""
+    _fields_ = [("bufs", _p * MAX_RANKS), ("buf_bytes", C.c_size_t), ("world", _i32), ("rank", _i32),
+                ("timeout_cycles", _i64)]
+
+
 # every symbol include/fa_b200.h declares
 EXPORTS = (
     "fa_b200_fwd", "fa_b200_fwd_noalloc", "fa_b200_fwd_plan", "fa_b200_combine", "fa_b200_normalize_window",
     "fa_b200_check_status", "fa_b200_last_error", "fa_b200_status_string", "fa_b200_abi_version",
     "fa_b200_launch_count", "fa_b200_bwd", "fa_b200_bwd_workspace_bytes",
     "fa_b200_plan_encode", "fa_b200_plan_decode", "fa_b200_fwd_planned",
+    "fa_b200_exchange_bytes", "fa_b200_exchange_alloc", "fa_b200_exchange_open", "fa_b200_exchange_close",
+    "fa_b200_exchange_free", "fa_b200_fwd_exchange_workspace", "fa_b200_fwd_exchange",
 )
 PLAN_BYTES = 192  # FA_B200_PLAN_BYTES
 
@@ -112,6 +123,20 @@ def load() -> C.CDLL:
     lib.fa_b200_plan_decode.restype = C.c_int
     lib.fa_b200_fwd_planned.argtypes = [C.POINTER(FwdParams), _p, C.c_size_t, _p, C.c_size_t, _p]
     lib.fa_b200_fwd_planned.restype = C.c_int
+    lib.fa_b200_exchange_bytes.argtypes = [_i32, _i64, _i32]
+    lib.fa_b200_exchange_bytes.restype = C.c_size_t
+    lib.fa_b200_exchange_alloc.argtypes = [C.c_size_t, C.POINTER(_p), _p]
+    lib.fa_b200_exchange_alloc.restype = C.c_int
+    lib.fa_b200_exchange_open.argtypes = [_p, C.POINTER(_p)]
+    lib.fa_b200_exchange_open.restype = C.c_int
+    lib.fa_b200_exchange_close.argtypes = [_p]
+    lib.fa_b200_exchange_close.restype = C.c_int
+    lib.fa_b200_exchange_free.argtypes = [_p]
+    lib.fa_b200_exchange_free.restype = C.c_int
+    lib.fa_b200_fwd_exchange_workspace.argtypes = [C.POINTER(FwdParams)]
+    lib.fa_b200_fwd_exchange_workspace.restype = C.c_size_t
+    lib.fa_b200_fwd_exchange.argtypes = [C.POINTER(FwdParams), _p, C.c_size_t, C.POINTER(Exchange), _p]
+    lib.fa_b200_fwd_exchange.restype = C.c_int
     lib.fa_b200_bwd.argtypes = [C.POINTER(BwdParams), _p, C.c_size_t, _p]
     lib.fa_b200_bwd.restype = C.c_int
     lib.fa_b200_bwd_workspace_bytes.argtypes = [C.POINTER(BwdParams)]

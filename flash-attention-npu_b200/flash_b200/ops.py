@@ -211,6 +211,29 @@ def attention_forward(q, k, v, *, out=None, lse=None, return_plan=False, plan_by
     return out, lse
 
 
+def attention_forward_exchange(q, k, v, exchange: "L.Exchange", *, out=None, lse=None, **kw):
+    """Attention of q over this rank's shard of the keys, merged with the other ranks' shards over peer memory
+    (fa_b200_fwd_exchange).  ``kw`` as for ``attention_forward`` (kv_pos_offset / kv_total place the shard in the
+    sequence); returns the final (out, lse), identical on every rank."""
+    lib = L.load()
+    validate_forward(q, k, v, out, lse, kw)
+    if kw.get("cu_seqlens_q") is not None:
+        raise RuntimeError("the cross-GPU exchange takes dense (b, s_q, h, d) queries")
+    if out is None:
+        out = torch.empty_like(q)
+    if lse is None:
+        lse = torch.empty(_lse_shape(q, False), dtype=torch.float32, device=q.device)
+    with torch.cuda.device(q.device):
+        p = build_params(q, k, v, out, lse, num_sm=_num_sm(q.device), **kw)
+        nbytes = lib.fa_b200_fwd_exchange_workspace(C.byref(p))
+        if nbytes == 0:  # the plan was refused: the library holds the reason
+            L.check(L.load().fa_b200_fwd_plan(C.byref(p), C.byref(L.FwdPlan())) or -1)
+        ws = torch.empty(nbytes, dtype=torch.uint8, device=q.device)
+        L.check(lib.fa_b200_fwd_exchange(C.byref(p), _ptr(ws), nbytes, C.byref(exchange),
+                                         torch.cuda.current_stream(q.device).cuda_stream))
+    return out, lse
+
+
 def encode_plan(p: "L.FwdParams") -> bytes:
     """Plans the problem described by ``p`` (sizes, flags and NULL-ness of the pointers; nothing is dereferenced)
     and returns the plan as FA_B200_PLAN_BYTES opaque bytes for ``attention_forward(plan_bytes=...)``."""

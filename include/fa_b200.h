@@ -23,6 +23,8 @@
  *   fa_b200_plan_encode /       get_scheduler_metadata, csrc/arch22/flash_attn_npu_v3/flash_api.cpp:493-558 (plan
  *   fa_b200_plan_decode /       computed ahead of the call, returned as opaque bytes) and the scheduler_metadata_
  *   fa_b200_fwd_planned         argument of mha_fwd, csrc/arch22/flash_attn_npu_v3/flash_api.cpp:92,322-380
+ *   fa_b200_exchange_* /        (none: sequence-sharded decode across GPUs over peer memory)
+ *   fa_b200_fwd_exchange
  *   fa_b200_combine             CombineScale, csrc/arch22/flash_attn_npu_v2/CombineScale.hpp:76-357
  *                               (and the Python-level flash_attn_combine,
  *                                flash_attn_npu_v3/interface_arch22.py:930-931)
@@ -228,6 +230,35 @@ typedef struct fa_bwd_params {
 size_t fa_b200_bwd_workspace_bytes(const fa_bwd_params* p);
 /* Three launches on `stream` (plus a memset of the accumulator): rowsum, main kernel, dQ conversion. */
 int fa_b200_bwd(const fa_bwd_params* p, void* workspace, size_t workspace_bytes, void* stream);
+
+/* ------------------------------------------------------------------------------------------------
+ * Sequence-sharded decode across GPUs over peer memory (one process per GPU, NVLink / NVSwitch).  No counterpart in
+ * the reference (it has no distributed code); the merge arithmetic is CombineScale's
+ * (csrc/arch22/flash_attn_npu_v2/CombineScale.hpp:165-309).
+ * Every rank owns one exchange buffer that all ranks map (CUDA IPC): fa_b200_exchange_alloc returns the buffer and a
+ * 64-byte handle to hand to the other ranks (any host channel), fa_b200_exchange_open maps a peer's buffer.
+ * fa_b200_fwd_exchange runs the attention over this rank's shard of the keys (p->kv_pos_offset / p->kv_total give its
+ * place in the sequence), then one kernel that merges this rank's split partials and stores the result into every
+ * rank's buffer with plain peer stores followed by a release flag, then one kernel that waits for every rank's flag
+ * and merges the shards into p->o / p->lse.  The wait is bounded (timeout_cycles, default about two seconds): when
+ * a rank does not deliver, the kernel gives up, fa_b200_check_status reports it, the call's results are invalid and
+ * the context stays usable.  All ranks must make the same sequence of calls on one buffer set; a buffer is sized for
+ * at most the rows x head dim it was allocated for.  q must be dense (b, s_q, h, d).
+ * ------------------------------------------------------------------------------------------------ */
+#define FA_B200_MAX_RANKS 16
+typedef struct fa_exchange {
+  void* bufs[FA_B200_MAX_RANKS]; /* exchange buffer of every rank as mapped into this process; [rank] is this rank's own */
+  size_t buf_bytes;              /* size each of them was allocated with */
+  int32_t world, rank;
+  int64_t timeout_cycles;        /* SM clock cycles the merge waits for the slowest rank; 0 = default */
+} fa_exchange;
+size_t fa_b200_exchange_bytes(int32_t world, int64_t rows, int32_t d); /* rows = b * s_q * h */
+int fa_b200_exchange_alloc(size_t bytes, void** ptr, void* handle64);  /* cudaMalloc + zero + IPC handle */
+int fa_b200_exchange_open(const void* handle64, void** ptr);
+int fa_b200_exchange_close(void* ptr);
+int fa_b200_exchange_free(void* ptr);
+size_t fa_b200_fwd_exchange_workspace(const fa_fwd_params* p);
+int fa_b200_fwd_exchange(const fa_fwd_params* p, void* workspace, size_t workspace_bytes, const fa_exchange* x, void* stream);
 
 /* Merge of split partials (also used across GPUs). */
 int fa_b200_combine(const fa_combine_params* p, void* stream);
