@@ -412,6 +412,22 @@ class DecodeLongSharded(DecodeBase):
         from flash_b200 import dist as D
         return D.sharded_decode(q, self.kc, self.vc, kv_pos_offset=self.lo, kv_total=self.L, causal=True, exchange=self.px)
 
+    def local_only_ms(self, steps=50):
+        """This rank's share of a step without the exchange (attention over its shard + merge of its own splits):
+        what the cross-GPU step time is made of besides waiting for the slowest rank."""
+        from flash_b200 import ops
+        run = lambda: ops.attention_forward(self.q, self.kc, self.vc, softmax_scale=self.d ** -0.5, causal=True,
+                                            kv_pos_offset=self.lo, kv_total=self.L, partial_out=True)
+        for _ in range(10):
+            run()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps):
+            run()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / steps
+
     def release(self):
         super().release()
         if self.px is not None:
@@ -570,6 +586,12 @@ def measure(key, args, steps, warmup, dev, rank, world, local_rank, peaks, barri
     else:
         units_all = wl.units
     used_graph = getattr(wl, "graph", None) is not None
+    local_ms = None
+    if key == "c5" and world > 1:  # every rank's own work per step, gathered: the slowest one paces the lock-step
+        mine = torch.tensor([wl.local_only_ms()], dtype=torch.float64, device=dev)
+        every = [torch.zeros_like(mine) for _ in range(world)]
+        dist.all_gather(every, mine)
+        local_ms = sorted(float(x[0]) for x in every)
     entry = None
     if rank == 0:
         value = units_all * steps / (total_ms * 1e-3) * wl.scale
@@ -600,6 +622,8 @@ def measure(key, args, steps, warmup, dev, rank, world, local_rank, peaks, barri
             "gpu_launches": gpu_launches,
             "clocks": clocks,
         }
+        if local_ms is not None:
+            entry["config"]["local_ms_per_step_min_median_max"] = [local_ms[0], local_ms[len(local_ms) // 2], local_ms[-1]]
         if key == "c5":
             entry["config"]["exchange"] = ("peer memory (NVLink stores + flags)" if getattr(wl, "px", None) is not None
                                            else ("NCCL all-gather" if world > 1 else "none (one rank)"))
