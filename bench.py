@@ -618,7 +618,9 @@ def measure(key, args, steps, warmup, dev, rank, world, local_rank, peaks, barri
                          "frac": achieved / peak, "traffic": traffic, "traffic_unit": "bytes per launch",
                          "traffic_source": traffic_src, "peak_source": peaks["_source"],
                          "per_launch": "one attention launch per step" + (" (+ merge)" if gpu_launches > steps else "")},
-            "e2e": {"value": e2e, "unit": wl.unit, "h2d_bytes_per_step": wl.h2d, "d2h_bytes_per_step": wl.d2h},
+            "e2e": {"value": e2e, "unit": wl.unit, "h2d_bytes_per_step": wl.h2d, "d2h_bytes_per_step": wl.d2h,
+                    # what the slowest rank's host link delivered: at N > 1 all ranks pull from one host's pinned memory
+                    "h2d_gb_per_s_per_gpu": wl.h2d * steps / (e2e_ms * 1e-3) / 1e9, "ms_per_step": e2e_ms / steps},
             "gpu_launches": gpu_launches,
             "clocks": clocks,
         }
