@@ -11,6 +11,8 @@
 namespace fa {
 
 int fail_bwd(int code, const std::string& msg);  // api.cu: records the thread's last error
+bool bwd_tc5_eligible(const fa_bwd_params& a);   // bwd_tc5.cu
+int bwd_tc5_launch(const BwdParams& p, const fa_bwd_params& a, cudaStream_t st, std::string* err);
 void count_launches(int n);                      // api.cu: fa_b200_launch_count
 
 static size_t align16(size_t x) { return (x + 15) & ~(size_t)15; }
@@ -101,7 +103,12 @@ int fa_b200_bwd(const fa_bwd_params* a, void* workspace, size_t workspace_bytes,
   p.dq_accum = reinterpret_cast<float*>(workspace);
   p.delta = reinterpret_cast<float*>(reinterpret_cast<char*>(workspace) + acc_bytes);
 
-  cudaError_t e = cudaMemsetAsync(p.dq_accum, 0, acc_bytes, cs);
+  if (a->kernel < 0 || a->kernel > 2) return fail_bwd(FA_ERR_INVALID, "kernel must be 0 (automatic), 1 (mma.sync) or 2 (tcgen05)");
+  const bool tc5 = a->kernel != 1 && bwd_tc5_eligible(*a);
+  if (a->kernel == 2 && !tc5)
+    return fail_bwd(FA_ERR_UNSUPPORTED, "the tcgen05 backward covers head dim 128 without softcap (packed input: total_k given)");
+  cudaError_t e = cudaSuccess;
+  if (!tc5) e = cudaMemsetAsync(p.dq_accum, 0, acc_bytes, cs);
   if (e != cudaSuccess) return fail_bwd(FA_ERR_CUDA, std::string("cudaMemsetAsync: ") + cudaGetErrorString(e));
   const bool bf = a->dtype == FA_BF16;
   const int delta_grid = (int)((rows * a->h + 3) / 4);
@@ -109,6 +116,13 @@ int fa_b200_bwd(const fa_bwd_params* a, void* workspace, size_t workspace_bytes,
   else bwd_delta_kernel<__half><<<delta_grid, 128, 0, cs>>>(p);
   e = cudaGetLastError();
   if (e != cudaSuccess) return fail_bwd(FA_ERR_CUDA, std::string("backward (delta) launch: ") + cudaGetErrorString(e));
+  if (tc5) {
+    std::string err;
+    const int rc = bwd_tc5_launch(p, *a, cs, &err);
+    if (rc != FA_OK) return fail_bwd(rc, err);
+    count_launches(3);
+    return FA_OK;
+  }
   const int n_kblocks = (a->seqlen_k + kBwdBN - 1) / kBwdBN;
   if (p.d_pad == 64) e = bf ? launch_bwd<64, __nv_bfloat16>(p, n_kblocks, cs) : launch_bwd<64, __half>(p, n_kblocks, cs);
   else if (p.d_pad == 128) e = bf ? launch_bwd<128, __nv_bfloat16>(p, n_kblocks, cs) : launch_bwd<128, __half>(p, n_kblocks, cs);

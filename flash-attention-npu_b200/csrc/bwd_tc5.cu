@@ -1,0 +1,57 @@
+// tcgen05 backward kernels: TMA descriptors and launch (kernels in bwd_tc5_kernel.cuh).
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+#include <string>
+
+#include "bwd_tc5_kernel.cuh"
+#include "tc5_api.cuh"
+
+namespace fa {
+
+// Head dim 128 without softcap; packed input needs the number of k / v rows for the TMA bounds.  Alignment and
+// stride rules are those fa_b200_bwd has already checked (16-byte rows).
+bool bwd_tc5_eligible(const fa_bwd_params& a) {
+  if (a.d != 128 || a.softcap > 0.f) return false;
+  if (a.cu_seqlens_q && a.total_k <= 0) return false;
+  return true;
+}
+
+int bwd_tc5_launch(const BwdParams& p, const fa_bwd_params& a, cudaStream_t st, std::string* err) {
+  using namespace btc5;
+  int32_t* status = device_status_word();
+  if (!status) { *err = "cannot look up the device status word"; return FA_ERR_CUDA; }
+  const bool varlen = a.cu_seqlens_q != nullptr;
+  const int64_t q_rows = varlen ? a.total_q : a.seqlen_q, k_rows = varlen ? a.total_k : a.seqlen_k;
+  const int64_t outer = varlen ? 1 : a.b;
+  CUtensorMap tq, tdo, tk, tv;
+  // Packed sequences: one row axis for the whole tensor.  A tile that runs past the end of its sequence reads rows of
+  // the next one (their P is 0 by the mask or by LSE = +inf), past the end of the tensor it reads zeros.
+  const bool ok =
+      tma_encode_rows(&tq, a.q, a.dtype, a.d, a.h, q_rows, outer, a.q_head_stride, a.q_row_stride, a.q_batch_stride, kBlk) &&
+      tma_encode_rows(&tdo, a.dout, a.dtype, a.d, a.h, q_rows, outer, a.do_head_stride, a.do_row_stride, a.do_batch_stride, kBlk) &&
+      tma_encode_rows(&tk, a.k, a.dtype, a.d, a.h_k, k_rows, outer, a.k_head_stride, a.k_row_stride, a.k_batch_stride, kBlk) &&
+      tma_encode_rows(&tv, a.v, a.dtype, a.d, a.h_k, k_rows, outer, a.v_head_stride, a.v_row_stride, a.v_batch_stride, kBlk);
+  if (!ok) { *err = "cuTensorMapEncodeTiled failed"; return FA_ERR_CUDA; }
+  const dim3 grid_kv((a.seqlen_k + kBlk - 1) / kBlk, a.h_k, a.b), grid_q((a.seqlen_q + kBlk - 1) / kBlk, a.h, a.b);
+  cudaError_t e = cudaSuccess;
+  auto launch = [&](auto kern, dim3 grid) {
+    if (e != cudaSuccess) return;
+    e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+    if (e == cudaSuccess) {
+      kern<<<grid, kThreads, kSmemBytes, st>>>(p, tq, tdo, tk, tv, status);
+      e = cudaGetLastError();
+    }
+  };
+  if (a.dtype == FA_BF16) {
+    launch(bwd_dkv_kernel<__nv_bfloat16, 1>, grid_kv);
+    launch(bwd_dq_kernel<__nv_bfloat16, 1>, grid_q);
+  } else {
+    launch(bwd_dkv_kernel<__half, 0>, grid_kv);
+    launch(bwd_dq_kernel<__half, 0>, grid_q);
+  }
+  if (e != cudaSuccess) { *err = std::string("tcgen05 backward launch: ") + cudaGetErrorString(e); return FA_ERR_CUDA; }
+  return FA_OK;
+}
+
+}  // namespace fa

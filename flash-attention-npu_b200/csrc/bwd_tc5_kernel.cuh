@@ -1,0 +1,560 @@
+// Attention backward on the Blackwell tensor cores (tcgen05.mma, accumulators and the P / dS operands in TMEM,
+// Q / K / V / dO tiles by TMA), head dim 128, dense and packed-varlen input.
+//
+// Same arithmetic as bwd_kernel.cuh, which follows the reference's golden (tests/fa_small_op_golden.py:160-353) and
+// replaces its FAG kernels (csrc/arch22/flash_attn_npu_v3/fag_kernel.cpp):
+//   P = exp(S scale - LSE)   dP = dO V^T   dS = P o (dP - D) scale   dV = P^T dO   dK = dS^T Q   dQ = dS K
+// with P and dS rounded to the input dtype before the second matrix products and fp32 accumulation.
+//
+// Two kernels, no atomics (the results do not depend on any order of arrival):
+//   bwd_dkv_kernel  one CTA per 128 keys of a (batch entry, kv head).  K and V stay in shared memory, the query
+//                   blocks that see the keys (of every query head of the group) stream through a two-stage ring.
+//                   It computes the TRANSPOSED products S^T = K Q^T and dP^T = V dO^T, so that a TMEM lane is a key:
+//                   P^T and dS^T, written back into the TMEM columns their fp32 sources came from, are the A
+//                   operands of dV += P^T dO and dK += dS^T Q (dO and Q as N-contiguous B operands from the same
+//                   tiles).  TMEM: S^T | dP^T | dV | dK.
+//   bwd_dq_kernel   one CTA per 128 query rows of a (batch entry, head).  Q and dO stay in shared memory, K and V
+//                   stream through a ring; S = Q K^T, dP = dO V^T, dS (16-bit) goes to TMEM columns of its own and
+//                   is the A operand of dQ += dS K (K as an N-contiguous B operand from the tile S was computed
+//                   from).  S and dP are free as soon as they are in registers, so the products of the next block
+//                   run under this block's exponentials.  TMEM: S | dP | dQ | dS.
+// The elementwise work has no row reduction (LSE and D are inputs), so it is split by columns over 16 warps: a
+// thread owns one TMEM lane and 32 of the 128 columns.
+// Warps 0-15 elementwise + epilogue, warp 16 issues the MMAs (one elected lane), warp 17 is the TMA producer.
+// Every wait is bounded; a wait that gives up raises the CTA's abort flag and ends in the device status word.
+#pragma once
+
+#include "bwd_kernel.cuh"
+#include "tc5_ptx.cuh"
+
+namespace fa {
+namespace btc5 {
+
+using namespace tc5;
+
+constexpr int kBlk = 128;                 // rows of a query block = keys of a key block
+constexpr int kHalfBytes = kBlk * 128;    // one 64-column half of a [128 x 128] 16-bit tile (128-byte rows)
+constexpr int kTileBytes = 2 * kHalfBytes;
+constexpr int kEwWarps = 16, kMmaWarp = 16, kTmaWarp = 17;
+constexpr int kThreads = 18 * 32;
+constexpr int kBarBytes = 3072;
+constexpr int kDqSlots = 5;               // K / V ring of bwd_dq_kernel
+constexpr int kSmemBytes = 7 * kTileBytes + kBarBytes;   // both kernels: 2 resident tiles + 5 ring tiles (dQ), 2 + 2 x 2 (dK / dV)
+static_assert(kSmemBytes <= 232448, "more than the 227 KiB a CTA can have");
+
+// 16 columns / 8 columns of one TMEM lane per thread
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];\n"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_st8(uint32_t taddr, const uint32_t (&r)[8]) {
+  asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};\n" ::"r"(taddr), "r"(r[0]), "r"(r[1]),
+               "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7])
+               : "memory");
+}
+
+// Bit e set: element (first + e) lies in [lo, hi].
+__device__ __forceinline__ uint32_t range_bits(int first, int lo, int hi) {
+  const int n_lo = min(max(lo - first, 0), 32);
+  const int n_hi = min(max(hi - first + 1, 0), 32);
+  const uint32_t below_hi = n_hi >= 32 ? 0xffffffffu : ((1u << n_hi) - 1u);
+  const uint32_t below_lo = n_lo >= 32 ? 0xffffffffu : ((1u << n_lo) - 1u);
+  return below_hi & ~below_lo;
+}
+
+// K-major operand tile (two 64-column halves, 128-byte swizzle): byte offset of k-step ks (16 columns), >> 4
+__device__ __forceinline__ uint64_t kmaj_off(int ks) { return (uint64_t)(((ks >> 2) * kHalfBytes + (ks & 3) * 32) >> 4); }
+// the same tile read as an N-contiguous B operand: k-step ks = 16 rows of 128 bytes
+__device__ __forceinline__ uint64_t nmaj_off(int ks) { return (uint64_t)((ks * 2048) >> 4); }
+
+struct SeqInfo {
+  int q_row0, q_len, k_row0, k_len, koff, bq;
+  int wl, wr;  // window sides in force; negative = unbounded
+};
+__device__ __forceinline__ SeqInfo seq_info(const BwdParams& p, int bi) {
+  SeqInfo s;
+  s.q_row0 = 0; s.q_len = p.seqlen_q; s.k_row0 = 0; s.k_len = p.seqlen_k;
+  if (p.cu_seqlens_q) {
+    s.q_row0 = p.cu_seqlens_q[bi];
+    s.q_len = p.cu_seqlens_q[bi + 1] - s.q_row0;
+    s.k_row0 = p.cu_seqlens_k[bi];
+    s.k_len = p.cu_seqlens_k[bi + 1] - s.k_row0;
+  }
+  s.bq = p.cu_seqlens_q ? 0 : bi;
+  s.koff = s.k_len - s.q_len;
+  // a negative side is unbounded (make_window_atten_mask, tests/fa_small_op_golden.py:36-58)
+  s.wr = p.is_causal ? 0 : ((p.is_local && p.wr >= 0) ? p.wr : -1);
+  s.wl = (p.is_local && p.wl >= 0) ? p.wl : -1;
+  return s;
+}
+
+template <typename T>
+__device__ __forceinline__ void store_slice(T* dst, const uint32_t (&a)[32]) {
+#pragma unroll
+  for (int e = 0; e < 32; e += 8) {
+    uint4 w;
+    w.x = pack2<T>(__uint_as_float(a[e]), __uint_as_float(a[e + 1]));
+    w.y = pack2<T>(__uint_as_float(a[e + 2]), __uint_as_float(a[e + 3]));
+    w.z = pack2<T>(__uint_as_float(a[e + 4]), __uint_as_float(a[e + 5]));
+    w.w = pack2<T>(__uint_as_float(a[e + 6]), __uint_as_float(a[e + 7]));
+    *reinterpret_cast<uint4*>(dst + e) = w;
+  }
+}
+
+__device__ __forceinline__ void finish(int32_t* status, int aborted, int tid) {
+  if (aborted) {
+    for (int i = 0; i < 64; ++i) __nanosleep(2000);  // copies in flight may still land in this CTA's shared memory
+    if (tid == 0) atomicExch(status, (aborted << 16) | (1 + (blockIdx.x & 0xffff)));
+    __syncthreads();
+  }
+}
+
+// =================================================================================================
+// dK, dV
+// =================================================================================================
+struct BarA {
+  uint64_t kv_full, qdo_full[2], qdo_empty[2];
+  uint64_t st_full;   // MMA -> elementwise: S^T and dP^T are in TMEM
+  uint64_t pds_full;  // elementwise -> MMA: P^T and dS^T are in TMEM
+  uint64_t acc_done;  // MMA -> epilogue
+  uint32_t tmem_base;
+  int abort_flag;
+  alignas(16) float lse2[2][kBlk];  // per ring stage: LSE * log2(e) and D of the stage's query rows (read 4 at a time)
+  alignas(16) float dlt[2][kBlk];
+};
+static_assert(sizeof(BarA) <= kBarBytes, "barrier block does not fit");
+
+template <typename T, uint32_t AB_FMT>
+__global__ void __launch_bounds__(kThreads, 1)
+bwd_dkv_kernel(const __grid_constant__ BwdParams p, const __grid_constant__ CUtensorMap tm_q,
+               const __grid_constant__ CUtensorMap tm_do, const __grid_constant__ CUtensorMap tm_k,
+               const __grid_constant__ CUtensorMap tm_v, int32_t* status) {
+  extern __shared__ __align__(1024) uint8_t smem[];
+  const uint32_t base = smem_addr(smem);
+  const int tid = threadIdx.x, lane = tid & 31;
+  const int warp = __shfl_sync(0xffffffffu, tid >> 5, 0);
+  const int nb = blockIdx.x, hk = blockIdx.y, bi = blockIdx.z;
+  const SeqInfo sq = seq_info(p, bi);
+  const int key0 = nb * kBlk;
+  if (key0 >= sq.k_len) return;
+  if ((base & 1023u) != 0) {
+    if (tid == 0) atomicExch(status, 0x20000000);
+    return;
+  }
+  const int group = p.h / p.h_k;
+  // query rows that see at least one key of the block
+  const int k1 = min(sq.k_len, key0 + kBlk) - 1;
+  const int i_lo = sq.wr >= 0 ? max(0, key0 - sq.koff - sq.wr) : 0;
+  const int i_hi = sq.wl >= 0 ? min(sq.q_len - 1, k1 - sq.koff + sq.wl) : sq.q_len - 1;  // inclusive
+  const int m_lo = i_lo / kBlk;
+  const int nm = i_hi >= i_lo ? i_hi / kBlk + 1 - m_lo : 0;
+  const int iters = nm * group;
+
+  T* dk_base = reinterpret_cast<T*>(p.dk) + (int64_t)sq.bq * p.dk_batch_stride + (int64_t)(sq.k_row0 + key0) * p.dk_row_stride +
+               (int64_t)hk * p.dk_head_stride;
+  T* dv_base = reinterpret_cast<T*>(p.dv) + (int64_t)sq.bq * p.dv_batch_stride + (int64_t)(sq.k_row0 + key0) * p.dv_row_stride +
+               (int64_t)hk * p.dv_head_stride;
+  if (iters == 0) {  // nobody sees these keys
+    for (int c = tid; c < kBlk * 16; c += kThreads) {
+      const int r = c >> 4, ch = c & 15;
+      if (key0 + r < sq.k_len) {
+        *reinterpret_cast<uint4*>(dk_base + (int64_t)r * p.dk_row_stride + ch * 8) = make_uint4(0, 0, 0, 0);
+        *reinterpret_cast<uint4*>(dv_base + (int64_t)r * p.dv_row_stride + ch * 8) = make_uint4(0, 0, 0, 0);
+      }
+    }
+    return;
+  }
+
+  const uint32_t k_smem = base, v_smem = base + kTileBytes, ring = base + 2 * kTileBytes;  // stage s: Q at ring + s * 64 KiB, dO behind it
+  BarA* bar = reinterpret_cast<BarA*>(smem + 7 * kTileBytes);
+  if (tid == 0) {
+    mbar_init(smem_addr(&bar->kv_full), 1);
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(smem_addr(&bar->qdo_full[s]), 1);
+      mbar_init(smem_addr(&bar->qdo_empty[s]), 1);
+    }
+    mbar_init(smem_addr(&bar->st_full), 1);
+    mbar_init(smem_addr(&bar->pds_full), kEwWarps);
+    mbar_init(smem_addr(&bar->acc_done), 1);
+    bar->abort_flag = 0;
+    fence_barrier_init();
+  }
+  if (warp == kMmaWarp) {
+    tmem_alloc(smem_addr(&bar->tmem_base), 512);
+    tmem_relinquish();
+  }
+  if (warp == kTmaWarp && lane == 0) {
+    tma_prefetch_desc(&tm_q);
+    tma_prefetch_desc(&tm_do);
+    tma_prefetch_desc(&tm_k);
+    tma_prefetch_desc(&tm_v);
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = __shfl_sync(0xffffffffu, bar->tmem_base, 0);
+  volatile int* abort_flag = &bar->abort_flag;
+
+  if (warp == kTmaWarp) {
+    // ------------------------------------------------------------------ producer
+    if (elect_one()) {
+      const uint32_t full = smem_addr(&bar->kv_full);
+      mbar_arrive_expect_tx(full, 2 * kTileBytes);
+      tma_load_4d(k_smem, &tm_k, full, 0, hk, sq.k_row0 + key0, sq.bq);
+      tma_load_4d(k_smem + kHalfBytes, &tm_k, full, 64, hk, sq.k_row0 + key0, sq.bq);
+      tma_load_4d(v_smem, &tm_v, full, 0, hk, sq.k_row0 + key0, sq.bq);
+      tma_load_4d(v_smem + kHalfBytes, &tm_v, full, 64, hk, sq.k_row0 + key0, sq.bq);
+    }
+    __syncwarp();
+    for (int it = 0; it < iters; ++it) {
+      const int s = it & 1, head = hk * group + it / nm, row0 = (m_lo + it % nm) * kBlk;
+      if (!mbar_wait(smem_addr(&bar->qdo_empty[s]), ((it >> 1) & 1) ^ 1, abort_flag, 61)) break;
+      for (int r = lane; r < kBlk; r += 32) {
+        const int i = row0 + r;
+        const int64_t li = (int64_t)sq.bq * p.lse_batch_stride + (int64_t)head * p.lse_head_stride + sq.q_row0 + i;
+        bar->lse2[s][r] = i < sq.q_len ? p.lse[li] * kLog2e : INFINITY;  // rows beyond the sequence: P = 0
+        bar->dlt[s][r] = i < sq.q_len ? p.delta[li] : 0.f;
+      }
+      __syncwarp();
+      if (elect_one()) {
+        const uint32_t full = smem_addr(&bar->qdo_full[s]);
+        const uint32_t q_dst = ring + s * 2 * kTileBytes, do_dst = q_dst + kTileBytes;
+        mbar_arrive_expect_tx(full, 2 * kTileBytes);
+        tma_load_4d(q_dst, &tm_q, full, 0, head, sq.q_row0 + row0, sq.bq);
+        tma_load_4d(q_dst + kHalfBytes, &tm_q, full, 64, head, sq.q_row0 + row0, sq.bq);
+        tma_load_4d(do_dst, &tm_do, full, 0, head, sq.q_row0 + row0, sq.bq);
+        tma_load_4d(do_dst + kHalfBytes, &tm_do, full, 64, head, sq.q_row0 + row0, sq.bq);
+      }
+      __syncwarp();
+    }
+  } else if (warp == kMmaWarp) {
+    // ------------------------------------------------------------------ MMA issuer
+    constexpr uint32_t idesc_kk = make_idesc(AB_FMT, kBlk, kBlk, 0);  // both operands K-major
+    constexpr uint32_t idesc_nn = make_idesc(AB_FMT, kBlk, kBlk, 1);  // B N-contiguous
+    const uint64_t k_desc = make_smem_desc(k_smem, 16, 1024), v_desc = make_smem_desc(v_smem, 16, 1024);
+    bool ok = mbar_wait(smem_addr(&bar->kv_full), 0, abort_flag, 62);
+    for (int it = 0; ok && it < iters; ++it) {
+      const int s = it & 1;
+      const uint32_t q_src = ring + s * 2 * kTileBytes, do_src = q_src + kTileBytes;
+      if (!mbar_wait(smem_addr(&bar->qdo_full[s]), (it >> 1) & 1, abort_flag, 63)) break;
+      tc_fence_after();
+      if (elect_one()) {
+        const uint64_t q_desc = make_smem_desc(q_src, 16, 1024), do_desc = make_smem_desc(do_src, 16, 1024);
+#pragma unroll
+        for (int ks = 0; ks < 8; ++ks) mma_ss(tmem, k_desc + kmaj_off(ks), q_desc + kmaj_off(ks), idesc_kk, ks > 0);          // S^T = K Q^T
+#pragma unroll
+        for (int ks = 0; ks < 8; ++ks) mma_ss(tmem + 128, v_desc + kmaj_off(ks), do_desc + kmaj_off(ks), idesc_kk, ks > 0);   // dP^T = V dO^T
+        mma_commit(smem_addr(&bar->st_full));
+      }
+      __syncwarp();
+      if (!mbar_wait(smem_addr(&bar->pds_full), it & 1, abort_flag, 64)) break;
+      tc_fence_after();
+      if (elect_one()) {
+        const uint64_t q_nd = make_smem_desc(q_src, kHalfBytes, 1024), do_nd = make_smem_desc(do_src, kHalfBytes, 1024);
+        // k-step ks = query rows 16 ks .. 16 ks + 15: the 8 packed columns the owning thread wrote inside its own 32
+#pragma unroll
+        for (int ks = 0; ks < 8; ++ks)
+          mma_ts(tmem + 256, tmem + 32 * (ks >> 1) + 8 * (ks & 1), do_nd + nmaj_off(ks), idesc_nn, (it > 0 || ks > 0));       // dV += P^T dO
+#pragma unroll
+        for (int ks = 0; ks < 8; ++ks)
+          mma_ts(tmem + 384, tmem + 128 + 32 * (ks >> 1) + 8 * (ks & 1), q_nd + nmaj_off(ks), idesc_nn, (it > 0 || ks > 0));  // dK += dS^T Q
+        mma_commit(smem_addr(&bar->qdo_empty[s]));
+        if (it == iters - 1) mma_commit(smem_addr(&bar->acc_done));
+      }
+      __syncwarp();
+    }
+  } else {
+    // ------------------------------------------------------------------ elementwise: lane = key, 32 query rows per thread
+    const int kr = (warp & 3) * 32 + lane, jk = key0 + kr, q4 = warp >> 2;
+    const uint32_t lane_addr = (uint32_t)((warp & 3) * 32) << 16;
+    const uint32_t st_tmem = tmem + lane_addr + 32 * q4, dp_tmem = tmem + lane_addr + 128 + 32 * q4;
+    // query rows that see this key
+    const int vis_lo = sq.wr >= 0 ? jk - sq.koff - sq.wr : -0x40000000;
+    const int vis_hi = jk < sq.k_len ? (sq.wl >= 0 ? jk - sq.koff + sq.wl : 0x40000000) : -0x40000001;
+    const float scale_log2 = p.scale_log2, scale = p.softmax_scale;
+    bool ok = true;
+    for (int it = 0; ok && it < iters; ++it) {
+      const int s = it & 1, i0 = (m_lo + it % nm) * kBlk + 32 * q4;
+      if (!mbar_wait(smem_addr(&bar->qdo_full[s]), (it >> 1) & 1, abort_flag, 65)) { ok = false; break; }  // LSE / D of the stage
+      if (!mbar_wait(smem_addr(&bar->st_full), it & 1, abort_flag, 66)) { ok = false; break; }
+      tc_fence_after();
+      const uint32_t bits = range_bits(i0, vis_lo, vis_hi);
+#pragma unroll
+      for (int hf = 0; hf < 2; ++hf) {
+        uint32_t sv[16], dv[16];
+        tmem_ld16(st_tmem + 16 * hf, sv);
+        tmem_ld16(dp_tmem + 16 * hf, dv);
+        tmem_wait_ld();
+        uint32_t pk_p[8], pk_ds[8];
+#pragma unroll
+        for (int e4 = 0; e4 < 16; e4 += 4) {
+          const float4 l4 = *reinterpret_cast<const float4*>(&bar->lse2[s][32 * q4 + 16 * hf + e4]);
+          const float4 d4 = *reinterpret_cast<const float4*>(&bar->dlt[s][32 * q4 + 16 * hf + e4]);
+          const float lv[4] = {l4.x, l4.y, l4.z, l4.w}, dd[4] = {d4.x, d4.y, d4.z, d4.w};
+          float pv[4], ds[4];
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const bool valid = (bits >> (16 * hf + e4 + e)) & 1u;
+            pv[e] = valid ? fast_exp2(__uint_as_float(sv[e4 + e]) * scale_log2 - lv[e]) : 0.f;
+            ds[e] = pv[e] * (__uint_as_float(dv[e4 + e]) - dd[e]) * scale;
+          }
+          pk_p[e4 >> 1] = pack2<T>(pv[0], pv[1]);
+          pk_p[(e4 >> 1) + 1] = pack2<T>(pv[2], pv[3]);
+          pk_ds[e4 >> 1] = pack2<T>(ds[0], ds[1]);
+          pk_ds[(e4 >> 1) + 1] = pack2<T>(ds[2], ds[3]);
+        }
+        // into the columns this thread has just read (the first 16 of its 32): nobody else's data
+        tmem_st8(st_tmem + 8 * hf, pk_p);
+        tmem_st8(dp_tmem + 8 * hf, pk_ds);
+      }
+      tmem_wait_st();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_addr(&bar->pds_full));
+    }
+    // ---- epilogue: dV, dK of this key, 32 columns of the head dim
+    if (ok && mbar_wait(smem_addr(&bar->acc_done), 0, abort_flag, 67)) {
+      tc_fence_after();
+      uint32_t a[32];
+      tmem_ld32(tmem + lane_addr + 256 + 32 * q4, a);
+      tmem_wait_ld();
+      if (jk < sq.k_len) store_slice<T>(dv_base + (int64_t)kr * p.dv_row_stride + 32 * q4, a);
+      tmem_ld32(tmem + lane_addr + 384 + 32 * q4, a);
+      tmem_wait_ld();
+      if (jk < sq.k_len) store_slice<T>(dk_base + (int64_t)kr * p.dk_row_stride + 32 * q4, a);
+      tc_fence_before();
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  finish(status, bar->abort_flag, tid);
+  if (warp == kMmaWarp) {
+    tc_fence_after();
+    tmem_dealloc(tmem, 512);
+  }
+}
+
+// =================================================================================================
+// dQ
+// =================================================================================================
+struct BarB {
+  uint64_t qdo_full, kv_full[kDqSlots], kv_empty[kDqSlots];
+  uint64_t s_full;    // MMA -> elementwise: S and dP are in TMEM
+  uint64_t s_free;    // elementwise -> MMA: S and dP are in registers
+  uint64_t ds_full;   // elementwise -> MMA: dS is in TMEM
+  uint64_t ds_free;   // MMA -> elementwise: dQ += dS K has read dS
+  uint64_t acc_done;
+  uint32_t tmem_base;
+  int abort_flag;
+  float lse2[kBlk], dlt[kBlk];
+};
+static_assert(sizeof(BarB) <= kBarBytes, "barrier block does not fit");
+
+template <typename T, uint32_t AB_FMT>
+__global__ void __launch_bounds__(kThreads, 1)
+bwd_dq_kernel(const __grid_constant__ BwdParams p, const __grid_constant__ CUtensorMap tm_q,
+              const __grid_constant__ CUtensorMap tm_do, const __grid_constant__ CUtensorMap tm_k,
+              const __grid_constant__ CUtensorMap tm_v, int32_t* status) {
+  extern __shared__ __align__(1024) uint8_t smem[];
+  const uint32_t base = smem_addr(smem);
+  const int tid = threadIdx.x, lane = tid & 31;
+  const int warp = __shfl_sync(0xffffffffu, tid >> 5, 0);
+  const int mb = (int)gridDim.x - 1 - (int)blockIdx.x;  // late (heavy, causal) query blocks first
+  const int head = blockIdx.y, bi = blockIdx.z;
+  const SeqInfo sq = seq_info(p, bi);
+  const int row0 = mb * kBlk;
+  if (row0 >= sq.q_len) return;
+  if ((base & 1023u) != 0) {
+    if (tid == 0) atomicExch(status, 0x20000000);
+    return;
+  }
+  const int hk = head / (p.h / p.h_k);
+  // keys that at least one row of the block sees
+  const int r1 = min(sq.q_len, row0 + kBlk) - 1;
+  const int k_hi = sq.wr >= 0 ? min(sq.k_len - 1, r1 + sq.koff + sq.wr) : sq.k_len - 1;  // inclusive
+  const int k_lo = sq.wl >= 0 ? max(0, row0 + sq.koff - sq.wl) : 0;
+  const int j_lo = k_lo / kBlk;
+  const int iters = k_hi >= k_lo ? k_hi / kBlk + 1 - j_lo : 0;
+
+  T* dq_base = reinterpret_cast<T*>(p.dq) + (int64_t)sq.bq * p.dq_batch_stride + (int64_t)(sq.q_row0 + row0) * p.dq_row_stride +
+               (int64_t)head * p.dq_head_stride;
+  if (iters == 0) {  // these rows see no key
+    for (int c = tid; c < kBlk * 16; c += kThreads) {
+      const int r = c >> 4, ch = c & 15;
+      if (row0 + r < sq.q_len) *reinterpret_cast<uint4*>(dq_base + (int64_t)r * p.dq_row_stride + ch * 8) = make_uint4(0, 0, 0, 0);
+    }
+    return;
+  }
+
+  const uint32_t q_smem = base, do_smem = base + kTileBytes, ring = base + 2 * kTileBytes;
+  BarB* bar = reinterpret_cast<BarB*>(smem + 7 * kTileBytes);
+  if (tid == 0) {
+    mbar_init(smem_addr(&bar->qdo_full), 1);
+    for (int s = 0; s < kDqSlots; ++s) {
+      mbar_init(smem_addr(&bar->kv_full[s]), 1);
+      mbar_init(smem_addr(&bar->kv_empty[s]), 1);
+    }
+    mbar_init(smem_addr(&bar->s_full), 1);
+    mbar_init(smem_addr(&bar->s_free), kEwWarps);
+    mbar_init(smem_addr(&bar->ds_full), kEwWarps);
+    mbar_init(smem_addr(&bar->ds_free), 1);
+    mbar_init(smem_addr(&bar->acc_done), 1);
+    bar->abort_flag = 0;
+    fence_barrier_init();
+  }
+  if (warp == kMmaWarp) {
+    tmem_alloc(smem_addr(&bar->tmem_base), 512);
+    tmem_relinquish();
+  }
+  if (warp == kTmaWarp && lane == 0) {
+    tma_prefetch_desc(&tm_q);
+    tma_prefetch_desc(&tm_do);
+    tma_prefetch_desc(&tm_k);
+    tma_prefetch_desc(&tm_v);
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = __shfl_sync(0xffffffffu, bar->tmem_base, 0);
+  volatile int* abort_flag = &bar->abort_flag;
+
+  if (warp == kTmaWarp) {
+    // ------------------------------------------------------------------ producer
+    for (int r = lane; r < kBlk; r += 32) {
+      const int i = row0 + r;
+      const int64_t li = (int64_t)sq.bq * p.lse_batch_stride + (int64_t)head * p.lse_head_stride + sq.q_row0 + i;
+      bar->lse2[r] = i < sq.q_len ? p.lse[li] * kLog2e : INFINITY;
+      bar->dlt[r] = i < sq.q_len ? p.delta[li] : 0.f;
+    }
+    __syncwarp();
+    if (elect_one()) {
+      const uint32_t full = smem_addr(&bar->qdo_full);
+      mbar_arrive_expect_tx(full, 2 * kTileBytes);
+      tma_load_4d(q_smem, &tm_q, full, 0, head, sq.q_row0 + row0, sq.bq);
+      tma_load_4d(q_smem + kHalfBytes, &tm_q, full, 64, head, sq.q_row0 + row0, sq.bq);
+      tma_load_4d(do_smem, &tm_do, full, 0, head, sq.q_row0 + row0, sq.bq);
+      tma_load_4d(do_smem + kHalfBytes, &tm_do, full, 64, head, sq.q_row0 + row0, sq.bq);
+    }
+    __syncwarp();
+    uint32_t cnt = 0;
+    for (int it = 0; it < 2 * iters; ++it, ++cnt) {  // K(j), V(j), K(j + 1), ...
+      const uint32_t slot = cnt % kDqSlots, par = (cnt / kDqSlots) & 1;
+      const int krow = sq.k_row0 + (j_lo + (it >> 1)) * kBlk;
+      const CUtensorMap* tm = (it & 1) ? &tm_v : &tm_k;
+      if (!mbar_wait(smem_addr(&bar->kv_empty[slot]), par ^ 1, abort_flag, 71)) break;
+      if (elect_one()) {
+        const uint32_t full = smem_addr(&bar->kv_full[slot]);
+        mbar_arrive_expect_tx(full, kTileBytes);
+        tma_load_4d(ring + slot * kTileBytes, tm, full, 0, hk, krow, sq.bq);
+        tma_load_4d(ring + slot * kTileBytes + kHalfBytes, tm, full, 64, hk, krow, sq.bq);
+      }
+      __syncwarp();
+    }
+  } else if (warp == kMmaWarp) {
+    // ------------------------------------------------------------------ MMA issuer
+    constexpr uint32_t idesc_kk = make_idesc(AB_FMT, kBlk, kBlk, 0);
+    constexpr uint32_t idesc_nn = make_idesc(AB_FMT, kBlk, kBlk, 1);
+    const uint64_t q_desc = make_smem_desc(q_smem, 16, 1024), do_desc = make_smem_desc(do_smem, 16, 1024);
+    // dQ (+)= dS K of block i, whose K tile sits in ring slot kslot
+    auto issue_dq = [&](int i, uint32_t kslot) -> bool {
+      if (!mbar_wait(smem_addr(&bar->ds_full), i & 1, abort_flag, 72)) return false;
+      tc_fence_after();
+      if (elect_one()) {
+        const uint64_t k_nd = make_smem_desc(ring + kslot * kTileBytes, kHalfBytes, 1024);
+#pragma unroll
+        for (int ks = 0; ks < 8; ++ks) mma_ts(tmem + 256, tmem + 384 + 8 * ks, k_nd + nmaj_off(ks), idesc_nn, (i > 0 || ks > 0));
+        mma_commit(smem_addr(&bar->ds_free));
+        mma_commit(smem_addr(&bar->kv_empty[kslot]));
+        if (i == iters - 1) mma_commit(smem_addr(&bar->acc_done));
+      }
+      __syncwarp();
+      return true;
+    };
+    bool ok = mbar_wait(smem_addr(&bar->qdo_full), 0, abort_flag, 73);
+    uint32_t cnt = 0, prev_kslot = 0;
+    for (int it = 0; ok && it < iters; ++it) {
+      const uint32_t kslot = cnt % kDqSlots, kpar = (cnt / kDqSlots) & 1;
+      ++cnt;
+      const uint32_t vslot = cnt % kDqSlots, vpar = (cnt / kDqSlots) & 1;
+      ++cnt;
+      if (!mbar_wait(smem_addr(&bar->kv_full[kslot]), kpar, abort_flag, 74)) { ok = false; break; }
+      if (!mbar_wait(smem_addr(&bar->kv_full[vslot]), vpar, abort_flag, 75)) { ok = false; break; }
+      if (it > 0 && !mbar_wait(smem_addr(&bar->s_free), (it - 1) & 1, abort_flag, 76)) { ok = false; break; }
+      tc_fence_after();
+      if (elect_one()) {
+        const uint64_t k_desc = make_smem_desc(ring + kslot * kTileBytes, 16, 1024);
+        const uint64_t v_desc = make_smem_desc(ring + vslot * kTileBytes, 16, 1024);
+#pragma unroll
+        for (int ks = 0; ks < 8; ++ks) mma_ss(tmem, q_desc + kmaj_off(ks), k_desc + kmaj_off(ks), idesc_kk, ks > 0);           // S = Q K^T
+#pragma unroll
+        for (int ks = 0; ks < 8; ++ks) mma_ss(tmem + 128, do_desc + kmaj_off(ks), v_desc + kmaj_off(ks), idesc_kk, ks > 0);    // dP = dO V^T
+        mma_commit(smem_addr(&bar->s_full));
+        mma_commit(smem_addr(&bar->kv_empty[vslot]));
+      }
+      __syncwarp();
+      if (it > 0 && !issue_dq(it - 1, prev_kslot)) { ok = false; break; }
+      prev_kslot = kslot;
+    }
+    if (ok) issue_dq(iters - 1, prev_kslot);
+  } else {
+    // ------------------------------------------------------------------ elementwise: lane = query row, 32 keys per thread
+    const int r = (warp & 3) * 32 + lane, i = row0 + r, q4 = warp >> 2;
+    const uint32_t lane_addr = (uint32_t)((warp & 3) * 32) << 16;
+    const float scale_log2 = p.scale_log2, scale = p.softmax_scale;
+    int hi = sq.k_len - 1, lo = 0;
+    if (sq.wr >= 0) hi = min(hi, i + sq.koff + sq.wr);
+    if (sq.wl >= 0) lo = max(0, i + sq.koff - sq.wl);
+    bool ok = mbar_wait(smem_addr(&bar->qdo_full), 0, abort_flag, 77);
+    const float lse2 = ok ? bar->lse2[r] : 0.f, dl = ok ? bar->dlt[r] : 0.f;
+    for (int it = 0; ok && it < iters; ++it) {
+      if (!mbar_wait(smem_addr(&bar->s_full), it & 1, abort_flag, 78)) { ok = false; break; }
+      tc_fence_after();
+      uint32_t sv[32], dv[32];
+      tmem_ld32(tmem + lane_addr + 32 * q4, sv);
+      tmem_ld32(tmem + lane_addr + 128 + 32 * q4, dv);
+      tmem_wait_ld();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_addr(&bar->s_free));  // the products of the next block may overwrite S and dP
+      const uint32_t bits = range_bits((j_lo + it) * kBlk + 32 * q4, lo, hi);
+      uint32_t pk[16];
+#pragma unroll
+      for (int e = 0; e < 32; e += 2) {
+        const float p0 = ((bits >> e) & 1u) ? fast_exp2(__uint_as_float(sv[e]) * scale_log2 - lse2) : 0.f;
+        const float p1 = ((bits >> (e + 1)) & 1u) ? fast_exp2(__uint_as_float(sv[e + 1]) * scale_log2 - lse2) : 0.f;
+        pk[e >> 1] = pack2<T>(p0 * (__uint_as_float(dv[e]) - dl) * scale, p1 * (__uint_as_float(dv[e + 1]) - dl) * scale);
+      }
+      if (it > 0 && !mbar_wait(smem_addr(&bar->ds_free), (it - 1) & 1, abort_flag, 79)) { ok = false; break; }
+      tc_fence_after();
+      tmem_st16(tmem + lane_addr + 384 + 16 * q4, pk);
+      tmem_wait_st();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_addr(&bar->ds_full));
+    }
+    if (ok && mbar_wait(smem_addr(&bar->acc_done), 0, abort_flag, 80)) {
+      tc_fence_after();
+      uint32_t a[32];
+      tmem_ld32(tmem + lane_addr + 256 + 32 * q4, a);
+      tmem_wait_ld();
+      if (i < sq.q_len) store_slice<T>(dq_base + (int64_t)r * p.dq_row_stride + 32 * q4, a);
+      tc_fence_before();
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  finish(status, bar->abort_flag, tid);
+  if (warp == kMmaWarp) {
+    tc_fence_after();
+    tmem_dealloc(tmem, 512);
+  }
+}
+
+}  // namespace btc5
+}  // namespace fa

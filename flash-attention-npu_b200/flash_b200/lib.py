@@ -42,7 +42,7 @@ class FwdParams(C.Structure):
             "causal", "window_left", "window_right", "max_seqlen_k_known",
             "kv_pos_offset", "kv_total", "partial_out",
             "num_splits", "kernel", "num_sm", "total_k", "kv_outer")]
-        + [("softmax_scale", C.c_float), ("softcap", C.c_float)]
+        + [("softmax_scale", C.c_float), ("softcap", C.c_float), ("total_k", _i32), ("kernel", _i32)]
     )
 
 
@@ -75,7 +75,7 @@ class BwdParams(C.Structure):
         + [("lse_batch_stride", _i64), ("lse_head_stride", _i64)]
         + [(n, _i32) for n in ("b", "seqlen_q", "seqlen_k", "h", "h_k", "d", "total_q", "dtype", "causal",
                                "window_left", "window_right")]
-        + [("softmax_scale", C.c_float), ("softcap", C.c_float)]
+        + [("softmax_scale", C.c_float), ("softcap", C.c_float), ("total_k", _i32), ("kernel", _i32)]
     )
 
 

@@ -302,9 +302,10 @@ def combine(o_partial: torch.Tensor, lse_partial: torch.Tensor, out: Optional[to
 
 def attention_backward(dout, q, k, v, out, lse, *, dq=None, dk=None, dv=None, softmax_scale=None, causal=False,
                        window_left=-1, window_right=-1, softcap=0.0, cu_seqlens_q=None, cu_seqlens_k=None,
-                       max_seqlen_q=None, max_seqlen_k=None):
+                       max_seqlen_q=None, max_seqlen_k=None, kernel=0):
     """dQ, dK, dV of ``attention_forward`` (dense (b, s, h, d) or packed varlen (total, h, d) tensors) from
-    the forward's ``out`` and ``lse``.  Head dim a multiple of 8, at most 256; no dropout / alibi."""
+    the forward's ``out`` and ``lse``.  Head dim a multiple of 8, at most 256; no dropout / alibi.
+    ``kernel``: 0 automatic (tcgen05 kernels for head dim 128 without softcap), 1 the mma.sync kernel, 2 tcgen05."""
     lib = L.load()
     ts = (dout, q, k, v, out)
     if not all(t.is_cuda for t in ts) or not lse.is_cuda:
@@ -341,6 +342,7 @@ def attention_backward(dout, q, k, v, out, lse, *, dq=None, dk=None, dv=None, so
         total_q, h, d = q.shape
         h_k = k.shape[1]
         p.b, p.seqlen_q, p.seqlen_k, p.total_q = cu_seqlens_q.numel() - 1, int(max_seqlen_q), int(max_seqlen_k), total_q
+        p.total_k = k.shape[0]
         p.lse_batch_stride, p.lse_head_stride = 0, lse.stride(0)
         if tuple(lse.shape) != (h, total_q):
             raise RuntimeError("softmax_lse must be (nheads, total_q)")
@@ -356,6 +358,7 @@ def attention_backward(dout, q, k, v, out, lse, *, dq=None, dk=None, dv=None, so
     p.window_left, p.window_right = int(window_left), int(window_right)
     p.softmax_scale = float(softmax_scale if softmax_scale is not None else d ** -0.5)
     p.softcap = float(softcap)
+    p.kernel = int(kernel)
     with torch.cuda.device(q.device):
         nbytes = lib.fa_b200_bwd_workspace_bytes(C.byref(p))
         ws = torch.empty(max(nbytes, 16), dtype=torch.uint8, device=q.device)

@@ -224,11 +224,15 @@ typedef struct fa_bwd_params {
   int32_t dtype, causal, window_left, window_right;
   float softmax_scale;
   float softcap; /* 0 = off */
+  int32_t total_k; /* rows of k / v for packed input (the tcgen05 kernels' TMA bounds); 0 = not given */
+  int32_t kernel;  /* 0 automatic; 1 force the mma.sync kernel; 2 force the tcgen05 kernels (FA_ERR_UNSUPPORTED if they do not cover the problem) */
 } fa_bwd_params;
 
 /* Bytes of device scratch fa_b200_bwd needs (fp32 dQ accumulator + rowsum(dO o O)). */
 size_t fa_b200_bwd_workspace_bytes(const fa_bwd_params* p);
-/* Three launches on `stream` (plus a memset of the accumulator): rowsum, main kernel, dQ conversion. */
+/* Three launches on `stream`.  Head dim 128 without softcap: rowsum, then two tcgen05 kernels (dK / dV per key block,
+ * dQ per query block; no atomics, so the results are bit-reproducible).  Otherwise: a memset of the fp32 dQ accumulator,
+ * rowsum, the mma.sync kernel (dQ through atomic adds), dQ conversion. */
 int fa_b200_bwd(const fa_bwd_params* p, void* workspace, size_t workspace_bytes, void* stream);
 
 /* ------------------------------------------------------------------------------------------------
