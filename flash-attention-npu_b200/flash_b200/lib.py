@@ -42,7 +42,7 @@ class FwdParams(C.Structure):
             "causal", "window_left", "window_right", "max_seqlen_k_known",
             "kv_pos_offset", "kv_total", "partial_out",
             "num_splits", "kernel", "num_sm", "total_k", "kv_outer")]
-        + [("softmax_scale", C.c_float), ("softcap", C.c_float), ("total_k", _i32), ("kernel", _i32)]
+        + [("softmax_scale", C.c_float), ("softcap", C.c_float)]
     )
 
 

@@ -29,6 +29,8 @@ def test_struct_layout_matches_header():
     assert C.sizeof(L.FwdParams) == 408
     assert C.sizeof(L.FwdPlan) == 72
     assert C.sizeof(L.CombineParams) == 176
+    assert C.sizeof(L.BwdParams) == 360
+    assert C.sizeof(L.Exchange) == 152
 
 
 @pytest.mark.parametrize("sq,mk,causal,wl,wr", [
