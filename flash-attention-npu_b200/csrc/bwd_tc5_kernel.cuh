@@ -20,9 +20,15 @@
 //                   run under this block's exponentials.  TMEM: S | dP | dQ | dS.
 // The elementwise work has no row reduction (LSE and D are inputs), so it is split by columns over 16 warps: a
 // thread owns one TMEM lane and 32 of the 128 columns.
-// Warps 0-15 elementwise + epilogue, warp 16 issues the MMAs (one elected lane), warp 17 is the TMA producer.
+// Warps 0-15 elementwise + epilogue; warps 16-18 issue the MMAs (one elected lane each), each its own share: one
+// issuing thread next to busy warps gets a tcgen05.mma out only every ~130 cycles, half the rate the tensor pipe
+// takes them at, so the products of a block are spread over two (dK / dV: the S^T / dV chain and the dP^T / dK chain,
+// each chain's TMEM hazards stay inside one in-order issuer) or three (dQ: S, dP, dQ) warps on different
+// schedulers; warp 19 is the TMA producer.
 // Every wait is bounded; a wait that gives up raises the CTA's abort flag and ends in the device status word.
 #pragma once
+
+#include <type_traits>
 
 #include "bwd_kernel.cuh"
 #include "tc5_ptx.cuh"
@@ -35,10 +41,10 @@ using namespace tc5;
 constexpr int kBlk = 128;                 // rows of a query block = keys of a key block
 constexpr int kHalfBytes = kBlk * 128;    // one 64-column half of a [128 x 128] 16-bit tile (128-byte rows)
 constexpr int kTileBytes = 2 * kHalfBytes;
-constexpr int kEwWarps = 16, kMmaWarp = 16, kTmaWarp = 17;
-constexpr int kThreads = 18 * 32;
+constexpr int kEwWarps = 16, kMmaWarp = 16 /* .. 18 */, kTmaWarp = 19;
+constexpr int kThreads = 20 * 32;
 constexpr int kBarBytes = 3072;
-constexpr int kDqSlots = 5;               // K / V ring of bwd_dq_kernel
+constexpr int kDqSlots = 5, kDqKSlots = 3;  // rings of bwd_dq_kernel: three K tiles (slots 0-2), two V tiles (slots 3-4)
 constexpr int kSmemBytes = 7 * kTileBytes + kBarBytes;   // both kernels: 2 resident tiles + 5 ring tiles (dQ), 2 + 2 x 2 (dK / dV)
 static_assert(kSmemBytes <= 232448, "more than the 227 KiB a CTA can have");
 
@@ -64,6 +70,42 @@ __device__ __forceinline__ uint32_t range_bits(int first, int lo, int hi) {
   const uint32_t below_hi = n_hi >= 32 ? 0xffffffffu : ((1u << n_hi) - 1u);
   const uint32_t below_lo = n_lo >= 32 ? 0xffffffffu : ((1u << n_lo) - 1u);
   return below_hi & ~below_lo;
+}
+
+// Build-time constant: of every 4 pairs of exponentials, how many are evaluated by polynomial on the FMA pipe instead
+// of the special-function unit (whose 16 results per clock per SM are what bounds the elementwise phase otherwise).
+#ifndef FA_BWD_POLY
+#define FA_BWD_POLY 0
+#endif
+constexpr int kPolyPairs = FA_BWD_POLY;
+
+// Two elements:  P = exp2(s * scale_log2 - lse2)  (0 where masked),  dS = P * (dP - D) * scale, both as packed 16-bit
+// pairs.  nlse2 = -lse2 and ndls2 = -D * scale per element, so the arithmetic is two packed fused multiply-adds, two
+// exponentials and one packed multiply.
+// (poly is a constant after unrolling: pair number & 3 < kPolyPairs)
+template <typename T, bool MASK>
+__device__ __forceinline__ void ew_pair(const bool poly, uint32_t s0, uint32_t s1, uint32_t d0, uint32_t d1, uint64_t scale_log2_2,
+                                        uint64_t nlse2, uint64_t scale2, uint64_t ndls2, uint32_t bits, int e,
+                                        uint32_t& pk_p, uint32_t& pk_ds) {
+  const uint64_t x2 = fma_f32x2(pack_f32x2(__uint_as_float(s0), __uint_as_float(s1)), scale_log2_2, nlse2);
+  float p0, p1;
+  if (poly) {
+    poly_exp2_x2(x2, p0, p1);
+  } else {
+    float x0, x1;
+    unpack_f32x2(x2, x0, x1);
+    p0 = fast_exp2(x0);
+    p1 = fast_exp2(x1);
+  }
+  if (MASK) {
+    p0 = ((bits >> e) & 1u) ? p0 : 0.f;
+    p1 = ((bits >> (e + 1)) & 1u) ? p1 : 0.f;
+  }
+  const uint64_t t2 = fma_f32x2(pack_f32x2(__uint_as_float(d0), __uint_as_float(d1)), scale2, ndls2);
+  float ds0, ds1;
+  unpack_f32x2(mul_f32x2(pack_f32x2(p0, p1), t2), ds0, ds1);
+  pk_p = pack2<T>(p0, p1);
+  pk_ds = pack2<T>(ds0, ds1);
 }
 
 // K-major operand tile (two 64-column halves, 128-byte swizzle): byte offset of k-step ks (16 columns), >> 4
@@ -123,8 +165,8 @@ struct BarA {
   uint64_t acc_done;  // MMA -> epilogue
   uint32_t tmem_base;
   int abort_flag;
-  alignas(16) float lse2[2][kBlk];  // per ring stage: LSE * log2(e) and D of the stage's query rows (read 4 at a time)
-  alignas(16) float dlt[2][kBlk];
+  alignas(16) float nlse2[2][kBlk];  // per ring stage: -LSE * log2(e) and -D * scale of the stage's query rows (read 4 at a time)
+  alignas(16) float ndls[2][kBlk];
 };
 static_assert(sizeof(BarA) <= kBarBytes, "barrier block does not fit");
 
@@ -175,11 +217,11 @@ bwd_dkv_kernel(const __grid_constant__ BwdParams p, const __grid_constant__ CUte
     mbar_init(smem_addr(&bar->kv_full), 1);
     for (int s = 0; s < 2; ++s) {
       mbar_init(smem_addr(&bar->qdo_full[s]), 1);
-      mbar_init(smem_addr(&bar->qdo_empty[s]), 1);
+      mbar_init(smem_addr(&bar->qdo_empty[s]), 2);  // one commit per issuing warp
     }
-    mbar_init(smem_addr(&bar->st_full), 1);
+    mbar_init(smem_addr(&bar->st_full), 2);
     mbar_init(smem_addr(&bar->pds_full), kEwWarps);
-    mbar_init(smem_addr(&bar->acc_done), 1);
+    mbar_init(smem_addr(&bar->acc_done), 2);
     bar->abort_flag = 0;
     fence_barrier_init();
   }
@@ -216,8 +258,8 @@ bwd_dkv_kernel(const __grid_constant__ BwdParams p, const __grid_constant__ CUte
       for (int r = lane; r < kBlk; r += 32) {
         const int i = row0 + r;
         const int64_t li = (int64_t)sq.bq * p.lse_batch_stride + (int64_t)head * p.lse_head_stride + sq.q_row0 + i;
-        bar->lse2[s][r] = i < sq.q_len ? p.lse[li] * kLog2e : INFINITY;  // rows beyond the sequence: P = 0
-        bar->dlt[s][r] = i < sq.q_len ? p.delta[li] : 0.f;
+        bar->nlse2[s][r] = i < sq.q_len ? -p.lse[li] * kLog2e : -INFINITY;  // rows beyond the sequence: P = 0
+        bar->ndls[s][r] = i < sq.q_len ? -p.delta[li] * p.softmax_scale : 0.f;
       }
       __syncwarp();
       if (elect_one()) {
@@ -231,42 +273,49 @@ bwd_dkv_kernel(const __grid_constant__ BwdParams p, const __grid_constant__ CUte
       }
       __syncwarp();
     }
-  } else if (warp == kMmaWarp) {
-    // ------------------------------------------------------------------ MMA issuer
+  } else if (warp == kMmaWarp || warp == kMmaWarp + 1) {
+    // ------------------------------------------------------------------ MMA issuers: chain 0 = S^T, dV; chain 1 = dP^T, dK
+    const int r = warp - kMmaWarp;
     constexpr uint32_t idesc_kk = make_idesc(AB_FMT, kBlk, kBlk, 0);  // both operands K-major
     constexpr uint32_t idesc_nn = make_idesc(AB_FMT, kBlk, kBlk, 1);  // B N-contiguous
-    const uint64_t k_desc = make_smem_desc(k_smem, 16, 1024), v_desc = make_smem_desc(v_smem, 16, 1024);
+    // descriptors are built once, a stage is one constant added, the accumulate flags are compile-time
+    const uint64_t a_desc = make_smem_desc(r ? v_smem : k_smem, 16, 1024);                    // K (S^T = K Q^T) or V (dP^T = V dO^T)
+    const uint64_t b_desc0 = make_smem_desc(ring + (r ? kTileBytes : 0), 16, 1024);           // Q or dO, K-major
+    const uint64_t b_nd0 = make_smem_desc(ring + (r ? 0 : kTileBytes), kHalfBytes, 1024);     // dO (dV += P^T dO) or Q (dK += dS^T Q), N-contiguous
+    constexpr uint64_t kStageStep = (2 * kTileBytes) >> 4;
+    const uint32_t src_tmem = tmem + 128 * r, acc_tmem = tmem + 256 + 128 * r;
+    const uint32_t bar_stfull = smem_addr(&bar->st_full), bar_pds = smem_addr(&bar->pds_full);
+    const uint32_t bar_full0 = smem_addr(&bar->qdo_full[0]), bar_empty0 = smem_addr(&bar->qdo_empty[0]);
     bool ok = mbar_wait(smem_addr(&bar->kv_full), 0, abort_flag, 62);
     for (int it = 0; ok && it < iters; ++it) {
       const int s = it & 1;
-      const uint32_t q_src = ring + s * 2 * kTileBytes, do_src = q_src + kTileBytes;
-      if (!mbar_wait(smem_addr(&bar->qdo_full[s]), (it >> 1) & 1, abort_flag, 63)) break;
+      const uint64_t st = (uint64_t)s * kStageStep;
+      if (!mbar_wait(bar_full0 + 8 * s, (it >> 1) & 1, abort_flag, 63)) break;
       tc_fence_after();
       if (elect_one()) {
-        const uint64_t q_desc = make_smem_desc(q_src, 16, 1024), do_desc = make_smem_desc(do_src, 16, 1024);
+        const uint64_t b_desc = b_desc0 + st;
+        mma_ss_c<false>(src_tmem, a_desc, b_desc, idesc_kk);
 #pragma unroll
-        for (int ks = 0; ks < 8; ++ks) mma_ss(tmem, k_desc + kmaj_off(ks), q_desc + kmaj_off(ks), idesc_kk, ks > 0);          // S^T = K Q^T
-#pragma unroll
-        for (int ks = 0; ks < 8; ++ks) mma_ss(tmem + 128, v_desc + kmaj_off(ks), do_desc + kmaj_off(ks), idesc_kk, ks > 0);   // dP^T = V dO^T
-        mma_commit(smem_addr(&bar->st_full));
+        for (int ks = 1; ks < 8; ++ks) mma_ss_c<true>(src_tmem, a_desc + kmaj_off(ks), b_desc + kmaj_off(ks), idesc_kk);
+        mma_commit(bar_stfull);
       }
       __syncwarp();
-      if (!mbar_wait(smem_addr(&bar->pds_full), it & 1, abort_flag, 64)) break;
+      if (!mbar_wait(bar_pds, it & 1, abort_flag, 64)) break;
       tc_fence_after();
       if (elect_one()) {
-        const uint64_t q_nd = make_smem_desc(q_src, kHalfBytes, 1024), do_nd = make_smem_desc(do_src, kHalfBytes, 1024);
+        const uint64_t b_nd = b_nd0 + st;
         // k-step ks = query rows 16 ks .. 16 ks + 15: the 8 packed columns the owning thread wrote inside its own 32
+        if (it == 0) mma_ts_c<false>(acc_tmem, src_tmem, b_nd, idesc_nn);
+        else mma_ts_c<true>(acc_tmem, src_tmem, b_nd, idesc_nn);
 #pragma unroll
-        for (int ks = 0; ks < 8; ++ks)
-          mma_ts(tmem + 256, tmem + 32 * (ks >> 1) + 8 * (ks & 1), do_nd + nmaj_off(ks), idesc_nn, (it > 0 || ks > 0));       // dV += P^T dO
-#pragma unroll
-        for (int ks = 0; ks < 8; ++ks)
-          mma_ts(tmem + 384, tmem + 128 + 32 * (ks >> 1) + 8 * (ks & 1), q_nd + nmaj_off(ks), idesc_nn, (it > 0 || ks > 0));  // dK += dS^T Q
-        mma_commit(smem_addr(&bar->qdo_empty[s]));
+        for (int ks = 1; ks < 8; ++ks) mma_ts_c<true>(acc_tmem, src_tmem + 32 * (ks >> 1) + 8 * (ks & 1), b_nd + nmaj_off(ks), idesc_nn);
+        mma_commit(bar_empty0 + 8 * s);
         if (it == iters - 1) mma_commit(smem_addr(&bar->acc_done));
       }
       __syncwarp();
     }
+  } else if (warp > kMmaWarp + 1) {
+    // spare issuing warp of the dQ kernel's layout: nothing to do here
   } else {
     // ------------------------------------------------------------------ elementwise: lane = key, 32 query rows per thread
     const int kr = (warp & 3) * 32 + lane, jk = key0 + kr, q4 = warp >> 2;
@@ -275,14 +324,10 @@ bwd_dkv_kernel(const __grid_constant__ BwdParams p, const __grid_constant__ CUte
     // query rows that see this key
     const int vis_lo = sq.wr >= 0 ? jk - sq.koff - sq.wr : -0x40000000;
     const int vis_hi = jk < sq.k_len ? (sq.wl >= 0 ? jk - sq.koff + sq.wl : 0x40000000) : -0x40000001;
-    const float scale_log2 = p.scale_log2, scale = p.softmax_scale;
-    bool ok = true;
-    for (int it = 0; ok && it < iters; ++it) {
-      const int s = it & 1, i0 = (m_lo + it % nm) * kBlk + 32 * q4;
-      if (!mbar_wait(smem_addr(&bar->qdo_full[s]), (it >> 1) & 1, abort_flag, 65)) { ok = false; break; }  // LSE / D of the stage
-      if (!mbar_wait(smem_addr(&bar->st_full), it & 1, abort_flag, 66)) { ok = false; break; }
-      tc_fence_after();
-      const uint32_t bits = range_bits(i0, vis_lo, vis_hi);
+    const uint64_t sl2 = pack_f32x2(p.scale_log2, p.scale_log2), sc2 = pack_f32x2(p.softmax_scale, p.softmax_scale);
+    // one block of the loop body: 2 x 16 query rows of this key
+    auto block = [&](auto mask_tag, int s, uint32_t bits) {
+      constexpr bool MASK = decltype(mask_tag)::value;
 #pragma unroll
       for (int hf = 0; hf < 2; ++hf) {
         uint32_t sv[16], dv[16];
@@ -292,25 +337,32 @@ bwd_dkv_kernel(const __grid_constant__ BwdParams p, const __grid_constant__ CUte
         uint32_t pk_p[8], pk_ds[8];
 #pragma unroll
         for (int e4 = 0; e4 < 16; e4 += 4) {
-          const float4 l4 = *reinterpret_cast<const float4*>(&bar->lse2[s][32 * q4 + 16 * hf + e4]);
-          const float4 d4 = *reinterpret_cast<const float4*>(&bar->dlt[s][32 * q4 + 16 * hf + e4]);
-          const float lv[4] = {l4.x, l4.y, l4.z, l4.w}, dd[4] = {d4.x, d4.y, d4.z, d4.w};
-          float pv[4], ds[4];
-#pragma unroll
-          for (int e = 0; e < 4; ++e) {
-            const bool valid = (bits >> (16 * hf + e4 + e)) & 1u;
-            pv[e] = valid ? fast_exp2(__uint_as_float(sv[e4 + e]) * scale_log2 - lv[e]) : 0.f;
-            ds[e] = pv[e] * (__uint_as_float(dv[e4 + e]) - dd[e]) * scale;
-          }
-          pk_p[e4 >> 1] = pack2<T>(pv[0], pv[1]);
-          pk_p[(e4 >> 1) + 1] = pack2<T>(pv[2], pv[3]);
-          pk_ds[e4 >> 1] = pack2<T>(ds[0], ds[1]);
-          pk_ds[(e4 >> 1) + 1] = pack2<T>(ds[2], ds[3]);
+          const float4 l4 = *reinterpret_cast<const float4*>(&bar->nlse2[s][32 * q4 + 16 * hf + e4]);
+          const float4 d4 = *reinterpret_cast<const float4*>(&bar->ndls[s][32 * q4 + 16 * hf + e4]);
+          ew_pair<T, MASK>(((e4 >> 1) & 3) < kPolyPairs, sv[e4], sv[e4 + 1], dv[e4], dv[e4 + 1], sl2, pack_f32x2(l4.x, l4.y), sc2,
+                                                          pack_f32x2(d4.x, d4.y), bits, 16 * hf + e4, pk_p[e4 >> 1], pk_ds[e4 >> 1]);
+          ew_pair<T, MASK>((((e4 >> 1) + 1) & 3) < kPolyPairs, sv[e4 + 2], sv[e4 + 3], dv[e4 + 2], dv[e4 + 3], sl2,
+                                                                pack_f32x2(l4.z, l4.w), sc2, pack_f32x2(d4.z, d4.w), bits,
+                                                                16 * hf + e4 + 2, pk_p[(e4 >> 1) + 1], pk_ds[(e4 >> 1) + 1]);
         }
         // into the columns this thread has just read (the first 16 of its 32): nobody else's data
         tmem_st8(st_tmem + 8 * hf, pk_p);
         tmem_st8(dp_tmem + 8 * hf, pk_ds);
       }
+    };
+    bool ok = true;
+    for (int it = 0; ok && it < iters; ++it) {
+      const int s = it & 1, r0 = (m_lo + it % nm) * kBlk, i0 = r0 + 32 * q4;
+      if (!mbar_wait(smem_addr(&bar->qdo_full[s]), (it >> 1) & 1, abort_flag, 65)) { ok = false; break; }  // LSE / D of the stage
+      if (!mbar_wait(smem_addr(&bar->st_full), it & 1, abort_flag, 66)) { ok = false; break; }
+      tc_fence_after();
+      // does any (key of the block, query row of the block) pair fall outside the mask?  (the same answer in every thread;
+      // rows beyond the sequence need no mask: their -LSE is -inf)
+      bool need_mask = key0 + kBlk > sq.k_len;
+      if (sq.wr >= 0) need_mask = need_mask || (key0 + kBlk - 1 > r0 + sq.koff + sq.wr);
+      if (sq.wl >= 0) need_mask = need_mask || (key0 < min(sq.q_len, r0 + kBlk) - 1 + sq.koff - sq.wl);
+      if (need_mask) block(std::true_type{}, s, range_bits(i0, vis_lo, vis_hi));
+      else block(std::false_type{}, s, 0xffffffffu);
       tmem_wait_st();
       tc_fence_before();
       __syncwarp();
@@ -351,7 +403,7 @@ struct BarB {
   uint64_t acc_done;
   uint32_t tmem_base;
   int abort_flag;
-  float lse2[kBlk], dlt[kBlk];
+  float nlse2[kBlk], ndls[kBlk];  // -LSE * log2(e) and -D * scale of the block's query rows
 };
 static_assert(sizeof(BarB) <= kBarBytes, "barrier block does not fit");
 
@@ -397,9 +449,9 @@ bwd_dq_kernel(const __grid_constant__ BwdParams p, const __grid_constant__ CUten
     mbar_init(smem_addr(&bar->qdo_full), 1);
     for (int s = 0; s < kDqSlots; ++s) {
       mbar_init(smem_addr(&bar->kv_full[s]), 1);
-      mbar_init(smem_addr(&bar->kv_empty[s]), 1);
+      mbar_init(smem_addr(&bar->kv_empty[s]), 2);  // K: the S and the dQ issuer; V: the dP issuer, twice
     }
-    mbar_init(smem_addr(&bar->s_full), 1);
+    mbar_init(smem_addr(&bar->s_full), 2);           // S and dP
     mbar_init(smem_addr(&bar->s_free), kEwWarps);
     mbar_init(smem_addr(&bar->ds_full), kEwWarps);
     mbar_init(smem_addr(&bar->ds_free), 1);
@@ -428,8 +480,8 @@ bwd_dq_kernel(const __grid_constant__ BwdParams p, const __grid_constant__ CUten
     for (int r = lane; r < kBlk; r += 32) {
       const int i = row0 + r;
       const int64_t li = (int64_t)sq.bq * p.lse_batch_stride + (int64_t)head * p.lse_head_stride + sq.q_row0 + i;
-      bar->lse2[r] = i < sq.q_len ? p.lse[li] * kLog2e : INFINITY;
-      bar->dlt[r] = i < sq.q_len ? p.delta[li] : 0.f;
+      bar->nlse2[r] = i < sq.q_len ? -p.lse[li] * kLog2e : -INFINITY;
+      bar->ndls[r] = i < sq.q_len ? -p.delta[li] * p.softmax_scale : 0.f;
     }
     __syncwarp();
     if (elect_one()) {
@@ -441,11 +493,13 @@ bwd_dq_kernel(const __grid_constant__ BwdParams p, const __grid_constant__ CUten
       tma_load_4d(do_smem + kHalfBytes, &tm_do, full, 64, head, sq.q_row0 + row0, sq.bq);
     }
     __syncwarp();
-    uint32_t cnt = 0;
-    for (int it = 0; it < 2 * iters; ++it, ++cnt) {  // K(j), V(j), K(j + 1), ...
-      const uint32_t slot = cnt % kDqSlots, par = (cnt / kDqSlots) & 1;
-      const int krow = sq.k_row0 + (j_lo + (it >> 1)) * kBlk;
-      const CUtensorMap* tm = (it & 1) ? &tm_v : &tm_k;
+    // K(j) lives in slot j % 3 and is held until dQ += dS K of its block has run; V(j) in slot 3 + j % 2 until dP has
+    for (int it = 0; it < 2 * iters; ++it) {  // K(j), V(j), K(j + 1), ...
+      const int jj = it >> 1, is_v = it & 1;
+      const uint32_t slot = is_v ? kDqKSlots + (jj & 1) : jj % kDqKSlots;
+      const uint32_t par = is_v ? (jj >> 1) & 1 : (jj / kDqKSlots) & 1;
+      const int krow = sq.k_row0 + (j_lo + jj) * kBlk;
+      const CUtensorMap* tm = is_v ? &tm_v : &tm_k;
       if (!mbar_wait(smem_addr(&bar->kv_empty[slot]), par ^ 1, abort_flag, 71)) break;
       if (elect_one()) {
         const uint32_t full = smem_addr(&bar->kv_full[slot]);
@@ -455,62 +509,71 @@ bwd_dq_kernel(const __grid_constant__ BwdParams p, const __grid_constant__ CUten
       }
       __syncwarp();
     }
-  } else if (warp == kMmaWarp) {
-    // ------------------------------------------------------------------ MMA issuer
+  } else if (warp == kMmaWarp || warp == kMmaWarp + 1) {
+    // ------------------------------------------------------------------ MMA issuers 0 / 1: S = Q K^T / dP = dO V^T
+    const int r = warp - kMmaWarp;
     constexpr uint32_t idesc_kk = make_idesc(AB_FMT, kBlk, kBlk, 0);
-    constexpr uint32_t idesc_nn = make_idesc(AB_FMT, kBlk, kBlk, 1);
-    const uint64_t q_desc = make_smem_desc(q_smem, 16, 1024), do_desc = make_smem_desc(do_smem, 16, 1024);
-    // dQ (+)= dS K of block i, whose K tile sits in ring slot kslot
-    auto issue_dq = [&](int i, uint32_t kslot) -> bool {
-      if (!mbar_wait(smem_addr(&bar->ds_full), i & 1, abort_flag, 72)) return false;
-      tc_fence_after();
-      if (elect_one()) {
-        const uint64_t k_nd = make_smem_desc(ring + kslot * kTileBytes, kHalfBytes, 1024);
-#pragma unroll
-        for (int ks = 0; ks < 8; ++ks) mma_ts(tmem + 256, tmem + 384 + 8 * ks, k_nd + nmaj_off(ks), idesc_nn, (i > 0 || ks > 0));
-        mma_commit(smem_addr(&bar->ds_free));
-        mma_commit(smem_addr(&bar->kv_empty[kslot]));
-        if (i == iters - 1) mma_commit(smem_addr(&bar->acc_done));
-      }
-      __syncwarp();
-      return true;
-    };
+    const uint64_t a_desc = make_smem_desc(r ? do_smem : q_smem, 16, 1024);
+    const uint64_t ring_kd = make_smem_desc(ring, 16, 1024);
+    constexpr uint64_t kSlotStep = kTileBytes >> 4;
+    const uint32_t bar_full0 = smem_addr(&bar->kv_full[0]), bar_empty0 = smem_addr(&bar->kv_empty[0]);
+    const uint32_t bar_sfull = smem_addr(&bar->s_full), bar_sfree = smem_addr(&bar->s_free);
+    const uint32_t d_tmem = tmem + 128 * r;
     bool ok = mbar_wait(smem_addr(&bar->qdo_full), 0, abort_flag, 73);
-    uint32_t cnt = 0, prev_kslot = 0;
+    uint32_t slot = r ? kDqKSlots : 0, par = 0;  // slot of K(it) (issuer 0: 0, 1, 2, 0 ..) or V(it) (issuer 1: 3, 4, 3 ..)
     for (int it = 0; ok && it < iters; ++it) {
-      const uint32_t kslot = cnt % kDqSlots, kpar = (cnt / kDqSlots) & 1;
-      ++cnt;
-      const uint32_t vslot = cnt % kDqSlots, vpar = (cnt / kDqSlots) & 1;
-      ++cnt;
-      if (!mbar_wait(smem_addr(&bar->kv_full[kslot]), kpar, abort_flag, 74)) { ok = false; break; }
-      if (!mbar_wait(smem_addr(&bar->kv_full[vslot]), vpar, abort_flag, 75)) { ok = false; break; }
-      if (it > 0 && !mbar_wait(smem_addr(&bar->s_free), (it - 1) & 1, abort_flag, 76)) { ok = false; break; }
+      if (!mbar_wait(bar_full0 + 8 * slot, par, abort_flag, 74)) break;
+      if (it > 0 && !mbar_wait(bar_sfree, (it - 1) & 1, abort_flag, 76)) break;
       tc_fence_after();
       if (elect_one()) {
-        const uint64_t k_desc = make_smem_desc(ring + kslot * kTileBytes, 16, 1024);
-        const uint64_t v_desc = make_smem_desc(ring + vslot * kTileBytes, 16, 1024);
+        const uint64_t b_desc = ring_kd + slot * kSlotStep;
+        mma_ss_c<false>(d_tmem, a_desc, b_desc, idesc_kk);
 #pragma unroll
-        for (int ks = 0; ks < 8; ++ks) mma_ss(tmem, q_desc + kmaj_off(ks), k_desc + kmaj_off(ks), idesc_kk, ks > 0);           // S = Q K^T
-#pragma unroll
-        for (int ks = 0; ks < 8; ++ks) mma_ss(tmem + 128, do_desc + kmaj_off(ks), v_desc + kmaj_off(ks), idesc_kk, ks > 0);    // dP = dO V^T
-        mma_commit(smem_addr(&bar->s_full));
-        mma_commit(smem_addr(&bar->kv_empty[vslot]));
+        for (int ks = 1; ks < 8; ++ks) mma_ss_c<true>(d_tmem, a_desc + kmaj_off(ks), b_desc + kmaj_off(ks), idesc_kk);
+        mma_commit(bar_sfull);
+        mma_commit(bar_empty0 + 8 * slot);
+        if (r) mma_commit(bar_empty0 + 8 * slot);  // nobody else reads the V tile
       }
       __syncwarp();
-      if (it > 0 && !issue_dq(it - 1, prev_kslot)) { ok = false; break; }
-      prev_kslot = kslot;
+      if (++slot == (r ? kDqSlots : kDqKSlots)) { slot = r ? kDqKSlots : 0; par ^= 1; }
     }
-    if (ok) issue_dq(iters - 1, prev_kslot);
+  } else if (warp == kMmaWarp + 2) {
+    // ------------------------------------------------------------------ MMA issuer 2: dQ += dS K
+    constexpr uint32_t idesc_nn = make_idesc(AB_FMT, kBlk, kBlk, 1);
+    const uint64_t ring_nd = make_smem_desc(ring, kHalfBytes, 1024);
+    constexpr uint64_t kSlotStep = kTileBytes >> 4;
+    const uint32_t bar_full0 = smem_addr(&bar->kv_full[0]), bar_empty0 = smem_addr(&bar->kv_empty[0]);
+    const uint32_t bar_dsfull = smem_addr(&bar->ds_full), bar_dsfree = smem_addr(&bar->ds_free);
+    uint32_t slot = 0, par = 0;  // ring position of K(it)
+    for (int it = 0; it < iters; ++it) {
+      if (!mbar_wait(bar_full0 + 8 * slot, par, abort_flag, 75)) break;  // long complete: S of this block has used the tile
+      if (!mbar_wait(bar_dsfull, it & 1, abort_flag, 72)) break;
+      tc_fence_after();
+      if (elect_one()) {
+        const uint64_t k_nd = ring_nd + slot * kSlotStep;
+        if (it == 0) mma_ts_c<false>(tmem + 256, tmem + 384, k_nd, idesc_nn);
+        else mma_ts_c<true>(tmem + 256, tmem + 384, k_nd, idesc_nn);
+#pragma unroll
+        for (int ks = 1; ks < 8; ++ks) mma_ts_c<true>(tmem + 256, tmem + 384 + 8 * ks, k_nd + nmaj_off(ks), idesc_nn);
+        mma_commit(bar_dsfree);
+        mma_commit(bar_empty0 + 8 * slot);
+        if (it == iters - 1) mma_commit(smem_addr(&bar->acc_done));
+      }
+      __syncwarp();
+      if (++slot == kDqKSlots) { slot = 0; par ^= 1; }
+    }
   } else {
     // ------------------------------------------------------------------ elementwise: lane = query row, 32 keys per thread
     const int r = (warp & 3) * 32 + lane, i = row0 + r, q4 = warp >> 2;
     const uint32_t lane_addr = (uint32_t)((warp & 3) * 32) << 16;
-    const float scale_log2 = p.scale_log2, scale = p.softmax_scale;
     int hi = sq.k_len - 1, lo = 0;
     if (sq.wr >= 0) hi = min(hi, i + sq.koff + sq.wr);
     if (sq.wl >= 0) lo = max(0, i + sq.koff - sq.wl);
     bool ok = mbar_wait(smem_addr(&bar->qdo_full), 0, abort_flag, 77);
-    const float lse2 = ok ? bar->lse2[r] : 0.f, dl = ok ? bar->dlt[r] : 0.f;
+    const float nl = ok ? bar->nlse2[r] : 0.f, nd = ok ? bar->ndls[r] : 0.f;
+    const uint64_t sl2 = pack_f32x2(p.scale_log2, p.scale_log2), sc2 = pack_f32x2(p.softmax_scale, p.softmax_scale);
+    const uint64_t nlse2 = pack_f32x2(nl, nl), ndls2 = pack_f32x2(nd, nd);
+    const int i_max = min(sq.q_len, row0 + kBlk) - 1;
     for (int it = 0; ok && it < iters; ++it) {
       if (!mbar_wait(smem_addr(&bar->s_full), it & 1, abort_flag, 78)) { ok = false; break; }
       tc_fence_after();
@@ -521,13 +584,21 @@ bwd_dq_kernel(const __grid_constant__ BwdParams p, const __grid_constant__ CUten
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(smem_addr(&bar->s_free));  // the products of the next block may overwrite S and dP
-      const uint32_t bits = range_bits((j_lo + it) * kBlk + 32 * q4, lo, hi);
-      uint32_t pk[16];
+      const int c0 = (j_lo + it) * kBlk;
+      // does any (row of the block, key of the block) pair fall outside the mask?  (the same answer in every thread)
+      bool need_mask = c0 + kBlk > sq.k_len;
+      if (sq.wr >= 0) need_mask = need_mask || (c0 + kBlk - 1 > row0 + sq.koff + sq.wr);
+      if (sq.wl >= 0) need_mask = need_mask || (c0 < i_max + sq.koff - sq.wl);
+      uint32_t pk[16], unused;
+      if (need_mask) {
+        const uint32_t bits = range_bits(c0 + 32 * q4, lo, hi);
 #pragma unroll
-      for (int e = 0; e < 32; e += 2) {
-        const float p0 = ((bits >> e) & 1u) ? fast_exp2(__uint_as_float(sv[e]) * scale_log2 - lse2) : 0.f;
-        const float p1 = ((bits >> (e + 1)) & 1u) ? fast_exp2(__uint_as_float(sv[e + 1]) * scale_log2 - lse2) : 0.f;
-        pk[e >> 1] = pack2<T>(p0 * (__uint_as_float(dv[e]) - dl) * scale, p1 * (__uint_as_float(dv[e + 1]) - dl) * scale);
+        for (int e = 0; e < 32; e += 2)
+          ew_pair<T, true>(((e >> 1) & 3) < kPolyPairs, sv[e], sv[e + 1], dv[e], dv[e + 1], sl2, nlse2, sc2, ndls2, bits, e, unused, pk[e >> 1]);
+      } else {
+#pragma unroll
+        for (int e = 0; e < 32; e += 2)
+          ew_pair<T, false>(((e >> 1) & 3) < kPolyPairs, sv[e], sv[e + 1], dv[e], dv[e + 1], sl2, nlse2, sc2, ndls2, 0u, e, unused, pk[e >> 1]);
       }
       if (it > 0 && !mbar_wait(smem_addr(&bar->ds_free), (it - 1) & 1, abort_flag, 79)) { ok = false; break; }
       tc_fence_after();

@@ -178,6 +178,30 @@ __device__ __forceinline__ uint64_t mul_f32x2(uint64_t a, uint64_t b) {
   return d;
 }
 
+// exp2 of two values on the FMA / ALU pipes instead of the special-function unit, which is a
+// co-bottleneck of the attention kernels (16 exponentials per clock per SM against 8192 tensor flops per clock).
+// x = n + f with n = round(x), f in [-0.5, 0.5]; 2^f by a degree-4 minimax polynomial (relative
+// error 2.7e-6, far below the rounding of P to 16 bits); n is added to the exponent field.
+__device__ __forceinline__ void poly_exp2_x2(uint64_t x2, float& p0, float& p1) {
+  float x0, x1;
+  unpack_f32x2(x2, x0, x1);
+  x2 = pack_f32x2(fmaxf(x0, -126.f), fmaxf(x1, -126.f));
+  const uint64_t magic2 = pack_f32x2(12582912.f, 12582912.f);  // 1.5 * 2^23: adds round(x) into the mantissa
+  const uint64_t xf2 = add_f32x2(x2, magic2);
+  const uint64_t xi2 = add_f32x2(xf2, pack_f32x2(-12582912.f, -12582912.f));
+  const uint64_t f2 = fma_f32x2(xi2, pack_f32x2(-1.f, -1.f), x2);
+  uint64_t r2 = pack_f32x2(0.009570096619427204f, 0.009570096619427204f);
+  r2 = fma_f32x2(r2, f2, pack_f32x2(0.05591785907745361f, 0.05591785907745361f));
+  r2 = fma_f32x2(r2, f2, pack_f32x2(0.240247443318367f, 0.240247443318367f));
+  r2 = fma_f32x2(r2, f2, pack_f32x2(0.6931217908859253f, 0.6931217908859253f));
+  r2 = fma_f32x2(r2, f2, pack_f32x2(0.9999992847442627f, 0.9999992847442627f));
+  float r0, r1, n0, n1;
+  unpack_f32x2(r2, r0, r1);
+  unpack_f32x2(xf2, n0, n1);
+  p0 = __uint_as_float(__float_as_uint(r0) + (__float_as_uint(n0) << 23));
+  p1 = __uint_as_float(__float_as_uint(r1) + (__float_as_uint(n1) << 23));
+}
+
 // ---------------- tcgen05.mma ----------------
 // Shared-memory matrix descriptor (sm_100 format): start address, leading / stride byte offsets
 // (all >> 4), descriptor version 1 at bit 46, swizzle mode at bits 61-63 (2 = 128-byte swizzle).
