@@ -24,31 +24,33 @@ int bwd_tc5_launch(const BwdParams& p, const fa_bwd_params& a, cudaStream_t st, 
   const bool varlen = a.cu_seqlens_q != nullptr;
   const int64_t q_rows = varlen ? a.total_q : a.seqlen_q, k_rows = varlen ? a.total_k : a.seqlen_k;
   const int64_t outer = varlen ? 1 : a.b;
-  CUtensorMap tq, tdo, tk, tv;
+  CUtensorMap tq, tdo, tk, tv, tq_u, tdo_u;  // _u: 64-row boxes (the units of the dK / dV kernel)
   // Packed sequences: one row axis for the whole tensor.  A tile that runs past the end of its sequence reads rows of
   // the next one (their P is 0 by the mask or by LSE = +inf), past the end of the tensor it reads zeros.
   const bool ok =
       tma_encode_rows(&tq, a.q, a.dtype, a.d, a.h, q_rows, outer, a.q_head_stride, a.q_row_stride, a.q_batch_stride, kBlk) &&
       tma_encode_rows(&tdo, a.dout, a.dtype, a.d, a.h, q_rows, outer, a.do_head_stride, a.do_row_stride, a.do_batch_stride, kBlk) &&
       tma_encode_rows(&tk, a.k, a.dtype, a.d, a.h_k, k_rows, outer, a.k_head_stride, a.k_row_stride, a.k_batch_stride, kBlk) &&
-      tma_encode_rows(&tv, a.v, a.dtype, a.d, a.h_k, k_rows, outer, a.v_head_stride, a.v_row_stride, a.v_batch_stride, kBlk);
+      tma_encode_rows(&tv, a.v, a.dtype, a.d, a.h_k, k_rows, outer, a.v_head_stride, a.v_row_stride, a.v_batch_stride, kBlk) &&
+      tma_encode_rows(&tq_u, a.q, a.dtype, a.d, a.h, q_rows, outer, a.q_head_stride, a.q_row_stride, a.q_batch_stride, kUnit) &&
+      tma_encode_rows(&tdo_u, a.dout, a.dtype, a.d, a.h, q_rows, outer, a.do_head_stride, a.do_row_stride, a.do_batch_stride, kUnit);
   if (!ok) { *err = "cuTensorMapEncodeTiled failed"; return FA_ERR_CUDA; }
   const dim3 grid_kv((a.seqlen_k + kBlk - 1) / kBlk, a.h_k, a.b), grid_q((a.seqlen_q + kBlk - 1) / kBlk, a.h, a.b);
   cudaError_t e = cudaSuccess;
-  auto launch = [&](auto kern, dim3 grid) {
+  auto launch = [&](auto kern, dim3 grid, const CUtensorMap& mq, const CUtensorMap& mdo) {
     if (e != cudaSuccess) return;
     e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
     if (e == cudaSuccess) {
-      kern<<<grid, kThreads, kSmemBytes, st>>>(p, tq, tdo, tk, tv, status);
+      kern<<<grid, kThreads, kSmemBytes, st>>>(p, mq, mdo, tk, tv, status);
       e = cudaGetLastError();
     }
   };
   if (a.dtype == FA_BF16) {
-    launch(bwd_dkv_kernel<__nv_bfloat16, 1>, grid_kv);
-    launch(bwd_dq_kernel<__nv_bfloat16, 1>, grid_q);
+    launch(bwd_dkv_kernel<__nv_bfloat16, 1>, grid_kv, tq_u, tdo_u);
+    launch(bwd_dq_kernel<__nv_bfloat16, 1>, grid_q, tq, tdo);
   } else {
-    launch(bwd_dkv_kernel<__half, 0>, grid_kv);
-    launch(bwd_dq_kernel<__half, 0>, grid_q);
+    launch(bwd_dkv_kernel<__half, 0>, grid_kv, tq_u, tdo_u);
+    launch(bwd_dq_kernel<__half, 0>, grid_q, tq, tdo);
   }
   if (e != cudaSuccess) { *err = std::string("tcgen05 backward launch: ") + cudaGetErrorString(e); return FA_ERR_CUDA; }
   return FA_OK;

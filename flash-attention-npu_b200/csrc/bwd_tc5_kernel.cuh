@@ -8,11 +8,11 @@
 //
 // Two kernels, no atomics (the results do not depend on any order of arrival):
 //   bwd_dkv_kernel  one CTA per 128 keys of a (batch entry, kv head).  K and V stay in shared memory, the query
-//                   blocks that see the keys (of every query head of the group) stream through a two-stage ring.
+//                   rows that see the keys (of every query head of the group) stream through a ring, 64 at a time.
 //                   It computes the TRANSPOSED products S^T = K Q^T and dP^T = V dO^T, so that a TMEM lane is a key:
 //                   P^T and dS^T, written back into the TMEM columns their fp32 sources came from, are the A
 //                   operands of dV += P^T dO and dK += dS^T Q (dO and Q as N-contiguous B operands from the same
-//                   tiles).  TMEM: S^T | dP^T | dV | dK.
+//                   tiles).  TMEM: two buffers of S^T | dP^T (64 rows each), dV, dK.
 //   bwd_dq_kernel   one CTA per 128 query rows of a (batch entry, head).  Q and dO stay in shared memory, K and V
 //                   stream through a ring; S = Q K^T, dP = dO V^T, dS (16-bit) goes to TMEM columns of its own and
 //                   is the A operand of dQ += dS K (K as an N-contiguous B operand from the tile S was computed
@@ -45,7 +45,7 @@ constexpr int kEwWarps = 16, kMmaWarp = 16 /* .. 18 */, kTmaWarp = 19;
 constexpr int kThreads = 20 * 32;
 constexpr int kBarBytes = 3072;
 constexpr int kDqSlots = 5, kDqKSlots = 3;  // rings of bwd_dq_kernel: three K tiles (slots 0-2), two V tiles (slots 3-4)
-constexpr int kSmemBytes = 7 * kTileBytes + kBarBytes;   // both kernels: 2 resident tiles + 5 ring tiles (dQ), 2 + 2 x 2 (dK / dV)
+constexpr int kSmemBytes = 7 * kTileBytes + kBarBytes;   // dQ: 2 resident tiles + 5 ring tiles; dK / dV: 2 + 4 stages of 32 KiB (6 tiles' worth)
 static_assert(kSmemBytes <= 232448, "more than the 227 KiB a CTA can have");
 
 // 16 columns / 8 columns of one TMEM lane per thread
@@ -156,17 +156,24 @@ __device__ __forceinline__ void finish(int32_t* status, int aborted, int tid) {
 }
 
 // =================================================================================================
-// dK, dV
+// dK, dV.  The query rows stream through in units of 64; S^T / dP^T of a unit are 64 TMEM columns each and there are
+// two such buffers, so the products of unit u + 1 run while the elementwise warps work on unit u.
+// TMEM: buffer 0 [S^T 0-63 | dP^T 64-127]  buffer 1 [128-255]  dV 256-383  dK 384-511.
 // =================================================================================================
+constexpr int kUnit = 64;                    // query rows per unit
+constexpr int kUnitHalf = kUnit * 128;       // one 64-column half of a [64 x 128] 16-bit tile: 8 KiB
+constexpr int kUnitTile = 2 * kUnitHalf;     // 16 KiB
+constexpr int kStages = 4;                   // ring stages, each Q (16 KiB) then dO (16 KiB)
+
 struct BarA {
-  uint64_t kv_full, qdo_full[2], qdo_empty[2];
-  uint64_t st_full;   // MMA -> elementwise: S^T and dP^T are in TMEM
-  uint64_t pds_full;  // elementwise -> MMA: P^T and dS^T are in TMEM
-  uint64_t acc_done;  // MMA -> epilogue
+  uint64_t kv_full, qdo_full[kStages], qdo_empty[kStages];
+  uint64_t st_full[2];   // MMA -> elementwise: S^T and dP^T of the buffer are in TMEM
+  uint64_t pds_full[2];  // elementwise -> MMA: P^T and dS^T of the buffer are in TMEM
+  uint64_t acc_done;     // MMA -> epilogue
   uint32_t tmem_base;
   int abort_flag;
-  alignas(16) float nlse2[2][kBlk];  // per ring stage: -LSE * log2(e) and -D * scale of the stage's query rows (read 4 at a time)
-  alignas(16) float ndls[2][kBlk];
+  alignas(16) float nlse2[kStages][kUnit];  // per ring stage: -LSE * log2(e) and -D * scale of the unit's query rows (read 4 at a time)
+  alignas(16) float ndls[kStages][kUnit];
 };
 static_assert(sizeof(BarA) <= kBarBytes, "barrier block does not fit");
 
@@ -192,9 +199,9 @@ bwd_dkv_kernel(const __grid_constant__ BwdParams p, const __grid_constant__ CUte
   const int k1 = min(sq.k_len, key0 + kBlk) - 1;
   const int i_lo = sq.wr >= 0 ? max(0, key0 - sq.koff - sq.wr) : 0;
   const int i_hi = sq.wl >= 0 ? min(sq.q_len - 1, k1 - sq.koff + sq.wl) : sq.q_len - 1;  // inclusive
-  const int m_lo = i_lo / kBlk;
-  const int nm = i_hi >= i_lo ? i_hi / kBlk + 1 - m_lo : 0;
-  const int iters = nm * group;
+  const int u_lo = i_lo / kUnit;
+  const int nu = i_hi >= i_lo ? i_hi / kUnit + 1 - u_lo : 0;
+  const int iters = nu * group;
 
   T* dk_base = reinterpret_cast<T*>(p.dk) + (int64_t)sq.bq * p.dk_batch_stride + (int64_t)(sq.k_row0 + key0) * p.dk_row_stride +
                (int64_t)hk * p.dk_head_stride;
@@ -211,16 +218,18 @@ bwd_dkv_kernel(const __grid_constant__ BwdParams p, const __grid_constant__ CUte
     return;
   }
 
-  const uint32_t k_smem = base, v_smem = base + kTileBytes, ring = base + 2 * kTileBytes;  // stage s: Q at ring + s * 64 KiB, dO behind it
+  const uint32_t k_smem = base, v_smem = base + kTileBytes, ring = base + 2 * kTileBytes;  // stage s: Q at ring + s * 32 KiB, dO behind it
   BarA* bar = reinterpret_cast<BarA*>(smem + 7 * kTileBytes);
   if (tid == 0) {
     mbar_init(smem_addr(&bar->kv_full), 1);
-    for (int s = 0; s < 2; ++s) {
+    for (int s = 0; s < kStages; ++s) {
       mbar_init(smem_addr(&bar->qdo_full[s]), 1);
       mbar_init(smem_addr(&bar->qdo_empty[s]), 2);  // one commit per issuing warp
     }
-    mbar_init(smem_addr(&bar->st_full), 2);
-    mbar_init(smem_addr(&bar->pds_full), kEwWarps);
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(smem_addr(&bar->st_full[b]), 2);
+      mbar_init(smem_addr(&bar->pds_full[b]), kEwWarps);
+    }
     mbar_init(smem_addr(&bar->acc_done), 2);
     bar->abort_flag = 0;
     fence_barrier_init();
@@ -253,9 +262,9 @@ bwd_dkv_kernel(const __grid_constant__ BwdParams p, const __grid_constant__ CUte
     }
     __syncwarp();
     for (int it = 0; it < iters; ++it) {
-      const int s = it & 1, head = hk * group + it / nm, row0 = (m_lo + it % nm) * kBlk;
-      if (!mbar_wait(smem_addr(&bar->qdo_empty[s]), ((it >> 1) & 1) ^ 1, abort_flag, 61)) break;
-      for (int r = lane; r < kBlk; r += 32) {
+      const int s = it % kStages, head = hk * group + it / nu, row0 = (u_lo + it % nu) * kUnit;
+      if (!mbar_wait(smem_addr(&bar->qdo_empty[s]), ((it / kStages) & 1) ^ 1, abort_flag, 61)) break;
+      for (int r = lane; r < kUnit; r += 32) {
         const int i = row0 + r;
         const int64_t li = (int64_t)sq.bq * p.lse_batch_stride + (int64_t)head * p.lse_head_stride + sq.q_row0 + i;
         bar->nlse2[s][r] = i < sq.q_len ? -p.lse[li] * kLog2e : -INFINITY;  // rows beyond the sequence: P = 0
@@ -264,109 +273,114 @@ bwd_dkv_kernel(const __grid_constant__ BwdParams p, const __grid_constant__ CUte
       __syncwarp();
       if (elect_one()) {
         const uint32_t full = smem_addr(&bar->qdo_full[s]);
-        const uint32_t q_dst = ring + s * 2 * kTileBytes, do_dst = q_dst + kTileBytes;
-        mbar_arrive_expect_tx(full, 2 * kTileBytes);
+        const uint32_t q_dst = ring + s * 2 * kUnitTile, do_dst = q_dst + kUnitTile;
+        mbar_arrive_expect_tx(full, 2 * kUnitTile);
         tma_load_4d(q_dst, &tm_q, full, 0, head, sq.q_row0 + row0, sq.bq);
-        tma_load_4d(q_dst + kHalfBytes, &tm_q, full, 64, head, sq.q_row0 + row0, sq.bq);
+        tma_load_4d(q_dst + kUnitHalf, &tm_q, full, 64, head, sq.q_row0 + row0, sq.bq);
         tma_load_4d(do_dst, &tm_do, full, 0, head, sq.q_row0 + row0, sq.bq);
-        tma_load_4d(do_dst + kHalfBytes, &tm_do, full, 64, head, sq.q_row0 + row0, sq.bq);
+        tma_load_4d(do_dst + kUnitHalf, &tm_do, full, 64, head, sq.q_row0 + row0, sq.bq);
       }
       __syncwarp();
     }
   } else if (warp == kMmaWarp || warp == kMmaWarp + 1) {
     // ------------------------------------------------------------------ MMA issuers: chain 0 = S^T, dV; chain 1 = dP^T, dK
+    // Issue order of a chain:  ST(0) | ST(1) DV(0) | ST(2) DV(1) | ...  ST(u + 2) overwrites the buffer whose P^T / dS^T
+    // DV(u) reads: both come from this warp, in this order, and the tensor pipe keeps the order.
     const int r = warp - kMmaWarp;
-    constexpr uint32_t idesc_kk = make_idesc(AB_FMT, kBlk, kBlk, 0);  // both operands K-major
-    constexpr uint32_t idesc_nn = make_idesc(AB_FMT, kBlk, kBlk, 1);  // B N-contiguous
-    // descriptors are built once, a stage is one constant added, the accumulate flags are compile-time
+    constexpr uint32_t idesc_st = make_idesc(AB_FMT, kBlk, kUnit, 0);  // [128 keys] x [64 rows], both operands K-major
+    constexpr uint32_t idesc_acc = make_idesc(AB_FMT, kBlk, kBlk, 1);  // [128 keys] x [128 head dim], B N-contiguous
     const uint64_t a_desc = make_smem_desc(r ? v_smem : k_smem, 16, 1024);                    // K (S^T = K Q^T) or V (dP^T = V dO^T)
-    const uint64_t b_desc0 = make_smem_desc(ring + (r ? kTileBytes : 0), 16, 1024);           // Q or dO, K-major
-    const uint64_t b_nd0 = make_smem_desc(ring + (r ? 0 : kTileBytes), kHalfBytes, 1024);     // dO (dV += P^T dO) or Q (dK += dS^T Q), N-contiguous
-    constexpr uint64_t kStageStep = (2 * kTileBytes) >> 4;
-    const uint32_t src_tmem = tmem + 128 * r, acc_tmem = tmem + 256 + 128 * r;
-    const uint32_t bar_stfull = smem_addr(&bar->st_full), bar_pds = smem_addr(&bar->pds_full);
+    const uint64_t b_desc0 = make_smem_desc(ring + (r ? kUnitTile : 0), 16, 1024);            // Q or dO of stage 0, K-major
+    const uint64_t b_nd0 = make_smem_desc(ring + (r ? 0 : kUnitTile), kUnitHalf, 1024);       // dO (dV += P^T dO) or Q (dK += dS^T Q), N-contiguous
+    constexpr uint64_t kStageStep = (2 * kUnitTile) >> 4;
+    // K-major unit tile: k-step ks (16 columns) at (ks >> 2) * 8 KiB + (ks & 3) * 32 bytes
+    auto unit_off = [](int ks) { return (uint64_t)(((ks >> 2) * kUnitHalf + (ks & 3) * 32) >> 4); };
+    const uint32_t acc_tmem = tmem + 256 + 128 * r;
+    const uint32_t bar_stfull0 = smem_addr(&bar->st_full[0]), bar_pds0 = smem_addr(&bar->pds_full[0]);
     const uint32_t bar_full0 = smem_addr(&bar->qdo_full[0]), bar_empty0 = smem_addr(&bar->qdo_empty[0]);
-    bool ok = mbar_wait(smem_addr(&bar->kv_full), 0, abort_flag, 62);
-    for (int it = 0; ok && it < iters; ++it) {
-      const int s = it & 1;
-      const uint64_t st = (uint64_t)s * kStageStep;
-      if (!mbar_wait(bar_full0 + 8 * s, (it >> 1) & 1, abort_flag, 63)) break;
+    auto issue_st = [&](int u) -> bool {
+      const int s = u % kStages, b = u & 1;
+      if (!mbar_wait(bar_full0 + 8 * s, (u / kStages) & 1, abort_flag, 63)) return false;
       tc_fence_after();
       if (elect_one()) {
-        const uint64_t b_desc = b_desc0 + st;
-        mma_ss_c<false>(src_tmem, a_desc, b_desc, idesc_kk);
+        const uint64_t b_desc = b_desc0 + (uint64_t)s * kStageStep;
+        const uint32_t d_tmem = tmem + 128 * b + 64 * r;
+        mma_ss_c<false>(d_tmem, a_desc, b_desc, idesc_st);
 #pragma unroll
-        for (int ks = 1; ks < 8; ++ks) mma_ss_c<true>(src_tmem, a_desc + kmaj_off(ks), b_desc + kmaj_off(ks), idesc_kk);
-        mma_commit(bar_stfull);
+        for (int ks = 1; ks < 8; ++ks) mma_ss_c<true>(d_tmem, a_desc + kmaj_off(ks), b_desc + unit_off(ks), idesc_st);
+        mma_commit(bar_stfull0 + 8 * b);
       }
       __syncwarp();
-      if (!mbar_wait(bar_pds, it & 1, abort_flag, 64)) break;
+      return true;
+    };
+    bool ok = mbar_wait(smem_addr(&bar->kv_full), 0, abort_flag, 62);
+    ok = ok && issue_st(0);
+    for (int u = 0; ok && u < iters; ++u) {
+      if (u + 1 < iters && !issue_st(u + 1)) break;
+      const int s = u % kStages, b = u & 1;
+      if (!mbar_wait(bar_pds0 + 8 * b, (u >> 1) & 1, abort_flag, 64)) break;
       tc_fence_after();
       if (elect_one()) {
-        const uint64_t b_nd = b_nd0 + st;
-        // k-step ks = query rows 16 ks .. 16 ks + 15: the 8 packed columns the owning thread wrote inside its own 32
-        if (it == 0) mma_ts_c<false>(acc_tmem, src_tmem, b_nd, idesc_nn);
-        else mma_ts_c<true>(acc_tmem, src_tmem, b_nd, idesc_nn);
+        const uint64_t b_nd = b_nd0 + (uint64_t)s * kStageStep;
+        const uint32_t src = tmem + 128 * b + 64 * r;
+        // k-step ks = query rows 16 ks .. 16 ks + 15 of the unit: the 8 packed columns their thread wrote inside its own 16
+        if (u == 0) mma_ts_c<false>(acc_tmem, src, b_nd, idesc_acc);
+        else mma_ts_c<true>(acc_tmem, src, b_nd, idesc_acc);
 #pragma unroll
-        for (int ks = 1; ks < 8; ++ks) mma_ts_c<true>(acc_tmem, src_tmem + 32 * (ks >> 1) + 8 * (ks & 1), b_nd + nmaj_off(ks), idesc_nn);
+        for (int ks = 1; ks < 4; ++ks) mma_ts_c<true>(acc_tmem, src + 16 * ks, b_nd + nmaj_off(ks), idesc_acc);
         mma_commit(bar_empty0 + 8 * s);
-        if (it == iters - 1) mma_commit(smem_addr(&bar->acc_done));
+        if (u == iters - 1) mma_commit(smem_addr(&bar->acc_done));
       }
       __syncwarp();
     }
   } else if (warp > kMmaWarp + 1) {
     // spare issuing warp of the dQ kernel's layout: nothing to do here
   } else {
-    // ------------------------------------------------------------------ elementwise: lane = key, 32 query rows per thread
+    // ------------------------------------------------------------------ elementwise: lane = key, 16 query rows per thread
     const int kr = (warp & 3) * 32 + lane, jk = key0 + kr, q4 = warp >> 2;
     const uint32_t lane_addr = (uint32_t)((warp & 3) * 32) << 16;
-    const uint32_t st_tmem = tmem + lane_addr + 32 * q4, dp_tmem = tmem + lane_addr + 128 + 32 * q4;
     // query rows that see this key
     const int vis_lo = sq.wr >= 0 ? jk - sq.koff - sq.wr : -0x40000000;
     const int vis_hi = jk < sq.k_len ? (sq.wl >= 0 ? jk - sq.koff + sq.wl : 0x40000000) : -0x40000001;
     const uint64_t sl2 = pack_f32x2(p.scale_log2, p.scale_log2), sc2 = pack_f32x2(p.softmax_scale, p.softmax_scale);
-    // one block of the loop body: 2 x 16 query rows of this key
-    auto block = [&](auto mask_tag, int s, uint32_t bits) {
+    auto unit = [&](auto mask_tag, int s, uint32_t st_tmem, uint32_t bits) {
       constexpr bool MASK = decltype(mask_tag)::value;
+      uint32_t sv[16], dv[16];
+      tmem_ld16(st_tmem, sv);
+      tmem_ld16(st_tmem + 64, dv);
+      tmem_wait_ld();
+      uint32_t pk_p[8], pk_ds[8];
 #pragma unroll
-      for (int hf = 0; hf < 2; ++hf) {
-        uint32_t sv[16], dv[16];
-        tmem_ld16(st_tmem + 16 * hf, sv);
-        tmem_ld16(dp_tmem + 16 * hf, dv);
-        tmem_wait_ld();
-        uint32_t pk_p[8], pk_ds[8];
-#pragma unroll
-        for (int e4 = 0; e4 < 16; e4 += 4) {
-          const float4 l4 = *reinterpret_cast<const float4*>(&bar->nlse2[s][32 * q4 + 16 * hf + e4]);
-          const float4 d4 = *reinterpret_cast<const float4*>(&bar->ndls[s][32 * q4 + 16 * hf + e4]);
-          ew_pair<T, MASK>(((e4 >> 1) & 3) < kPolyPairs, sv[e4], sv[e4 + 1], dv[e4], dv[e4 + 1], sl2, pack_f32x2(l4.x, l4.y), sc2,
-                                                          pack_f32x2(d4.x, d4.y), bits, 16 * hf + e4, pk_p[e4 >> 1], pk_ds[e4 >> 1]);
-          ew_pair<T, MASK>((((e4 >> 1) + 1) & 3) < kPolyPairs, sv[e4 + 2], sv[e4 + 3], dv[e4 + 2], dv[e4 + 3], sl2,
-                                                                pack_f32x2(l4.z, l4.w), sc2, pack_f32x2(d4.z, d4.w), bits,
-                                                                16 * hf + e4 + 2, pk_p[(e4 >> 1) + 1], pk_ds[(e4 >> 1) + 1]);
-        }
-        // into the columns this thread has just read (the first 16 of its 32): nobody else's data
-        tmem_st8(st_tmem + 8 * hf, pk_p);
-        tmem_st8(dp_tmem + 8 * hf, pk_ds);
+      for (int e4 = 0; e4 < 16; e4 += 4) {
+        const float4 l4 = *reinterpret_cast<const float4*>(&bar->nlse2[s][16 * q4 + e4]);
+        const float4 d4 = *reinterpret_cast<const float4*>(&bar->ndls[s][16 * q4 + e4]);
+        ew_pair<T, MASK>(((e4 >> 1) & 3) < kPolyPairs, sv[e4], sv[e4 + 1], dv[e4], dv[e4 + 1], sl2, pack_f32x2(l4.x, l4.y), sc2,
+                         pack_f32x2(d4.x, d4.y), bits, e4, pk_p[e4 >> 1], pk_ds[e4 >> 1]);
+        ew_pair<T, MASK>((((e4 >> 1) + 1) & 3) < kPolyPairs, sv[e4 + 2], sv[e4 + 3], dv[e4 + 2], dv[e4 + 3], sl2, pack_f32x2(l4.z, l4.w),
+                         sc2, pack_f32x2(d4.z, d4.w), bits, e4 + 2, pk_p[(e4 >> 1) + 1], pk_ds[(e4 >> 1) + 1]);
       }
+      // into the columns this thread has just read (the first 8 of its 16): nobody else's data
+      tmem_st8(st_tmem, pk_p);
+      tmem_st8(st_tmem + 64, pk_ds);
     };
     bool ok = true;
-    for (int it = 0; ok && it < iters; ++it) {
-      const int s = it & 1, r0 = (m_lo + it % nm) * kBlk, i0 = r0 + 32 * q4;
-      if (!mbar_wait(smem_addr(&bar->qdo_full[s]), (it >> 1) & 1, abort_flag, 65)) { ok = false; break; }  // LSE / D of the stage
-      if (!mbar_wait(smem_addr(&bar->st_full), it & 1, abort_flag, 66)) { ok = false; break; }
+    for (int u = 0; ok && u < iters; ++u) {
+      const int s = u % kStages, b = u & 1, r0 = (u_lo + u % nu) * kUnit, i0 = r0 + 16 * q4;
+      if (!mbar_wait(smem_addr(&bar->qdo_full[s]), (u / kStages) & 1, abort_flag, 65)) { ok = false; break; }  // LSE / D of the stage
+      if (!mbar_wait(smem_addr(&bar->st_full[b]), (u >> 1) & 1, abort_flag, 66)) { ok = false; break; }
       tc_fence_after();
-      // does any (key of the block, query row of the block) pair fall outside the mask?  (the same answer in every thread;
+      // does any (key of the block, query row of the unit) pair fall outside the mask?  (the same answer in every thread;
       // rows beyond the sequence need no mask: their -LSE is -inf)
       bool need_mask = key0 + kBlk > sq.k_len;
       if (sq.wr >= 0) need_mask = need_mask || (key0 + kBlk - 1 > r0 + sq.koff + sq.wr);
-      if (sq.wl >= 0) need_mask = need_mask || (key0 < min(sq.q_len, r0 + kBlk) - 1 + sq.koff - sq.wl);
-      if (need_mask) block(std::true_type{}, s, range_bits(i0, vis_lo, vis_hi));
-      else block(std::false_type{}, s, 0xffffffffu);
+      if (sq.wl >= 0) need_mask = need_mask || (key0 < min(sq.q_len, r0 + kUnit) - 1 + sq.koff - sq.wl);
+      const uint32_t st_tmem = tmem + lane_addr + 128 * b + 16 * q4;
+      if (need_mask) unit(std::true_type{}, s, st_tmem, range_bits(i0, vis_lo, vis_hi));
+      else unit(std::false_type{}, s, st_tmem, 0xffffffffu);
       tmem_wait_st();
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(smem_addr(&bar->pds_full));
+      if (lane == 0) mbar_arrive(smem_addr(&bar->pds_full[b]));
     }
     // ---- epilogue: dV, dK of this key, 32 columns of the head dim
     if (ok && mbar_wait(smem_addr(&bar->acc_done), 0, abort_flag, 67)) {
