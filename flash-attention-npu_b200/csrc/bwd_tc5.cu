@@ -2,6 +2,7 @@
 #include <cuda.h>
 #include <cuda_runtime.h>
 
+#include <algorithm>
 #include <string>
 
 #include "bwd_tc5_kernel.cuh"
@@ -35,22 +36,30 @@ int bwd_tc5_launch(const BwdParams& p, const fa_bwd_params& a, cudaStream_t st, 
       tma_encode_rows(&tq_u, a.q, a.dtype, a.d, a.h, q_rows, outer, a.q_head_stride, a.q_row_stride, a.q_batch_stride, kUnit) &&
       tma_encode_rows(&tdo_u, a.dout, a.dtype, a.d, a.h, q_rows, outer, a.do_head_stride, a.do_row_stride, a.do_batch_stride, kUnit);
   if (!ok) { *err = "cuTensorMapEncodeTiled failed"; return FA_ERR_CUDA; }
-  const dim3 grid_kv((a.seqlen_k + kBlk - 1) / kBlk, a.h_k, a.b), grid_q((a.seqlen_q + kBlk - 1) / kBlk, a.h, a.b);
-  cudaError_t e = cudaSuccess;
-  auto launch = [&](auto kern, dim3 grid, const CUtensorMap& mq, const CUtensorMap& mdo) {
+  // persistent kernels: one CTA per SM (or per work item when there are fewer)
+  int dev = 0, num_sm = 148;
+  cudaGetDevice(&dev);
+  cudaDeviceGetAttribute(&num_sm, cudaDevAttrMultiProcessorCount, dev);
+  const long long items_kv = (long long)((a.seqlen_k + kBlk - 1) / kBlk) * a.h_k * a.b;
+  const long long items_q = (long long)((a.seqlen_q + kBlk - 1) / kBlk) * a.h * a.b;
+  const dim3 grid_kv((unsigned)std::min<long long>(items_kv, num_sm)), grid_q((unsigned)std::min<long long>(items_q, num_sm));
+  // the two item counters: the first words of the fp32 dQ accumulator, which these kernels do not use
+  int32_t* counters = reinterpret_cast<int32_t*>(p.dq_accum);
+  cudaError_t e = cudaMemsetAsync(counters, 0, 2 * sizeof(int32_t), st);
+  auto launch = [&](auto kern, dim3 grid, const CUtensorMap& mq, const CUtensorMap& mdo, int32_t* counter) {
     if (e != cudaSuccess) return;
     e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
     if (e == cudaSuccess) {
-      kern<<<grid, kThreads, kSmemBytes, st>>>(p, mq, mdo, tk, tv, status);
+      kern<<<grid, kThreads, kSmemBytes, st>>>(p, mq, mdo, tk, tv, status, counter);
       e = cudaGetLastError();
     }
   };
   if (a.dtype == FA_BF16) {
-    launch(bwd_dkv_kernel<__nv_bfloat16, 1>, grid_kv, tq_u, tdo_u);
-    launch(bwd_dq_kernel<__nv_bfloat16, 1>, grid_q, tq, tdo);
+    launch(bwd_dkv_kernel<__nv_bfloat16, 1>, grid_kv, tq_u, tdo_u, counters);
+    launch(bwd_dq_kernel<__nv_bfloat16, 1>, grid_q, tq, tdo, counters + 1);
   } else {
-    launch(bwd_dkv_kernel<__half, 0>, grid_kv, tq_u, tdo_u);
-    launch(bwd_dq_kernel<__half, 0>, grid_q, tq, tdo);
+    launch(bwd_dkv_kernel<__half, 0>, grid_kv, tq_u, tdo_u, counters);
+    launch(bwd_dq_kernel<__half, 0>, grid_q, tq, tdo, counters + 1);
   }
   if (e != cudaSuccess) { *err = std::string("tcgen05 backward launch: ") + cudaGetErrorString(e); return FA_ERR_CUDA; }
   return FA_OK;
