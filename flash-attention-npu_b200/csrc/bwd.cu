@@ -111,7 +111,7 @@ int fa_b200_bwd(const fa_bwd_params* a, void* workspace, size_t workspace_bytes,
   if (!tc5) e = cudaMemsetAsync(p.dq_accum, 0, acc_bytes, cs);
   if (e != cudaSuccess) return fail_bwd(FA_ERR_CUDA, std::string("cudaMemsetAsync: ") + cudaGetErrorString(e));
   const bool bf = a->dtype == FA_BF16;
-  const int delta_grid = (int)((rows * a->h + 3) / 4);
+  const int delta_grid = (int)((rows * a->h + 7) / 8);  // 4 warps x 2 rows per block
   if (bf) bwd_delta_kernel<__nv_bfloat16><<<delta_grid, 128, 0, cs>>>(p);
   else bwd_delta_kernel<__half><<<delta_grid, 128, 0, cs>>>(p);
   e = cudaGetLastError();

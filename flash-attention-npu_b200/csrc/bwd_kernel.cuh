@@ -55,25 +55,36 @@ struct BwdSmem {
   static constexpr int BYTES = DELTA_OFF + 64 * 4;
 };
 
-// D_i = sum_d dO_id * O_id, one warp per (row, head).
+// D_i = sum_d dO_id * O_id.  Half a warp per (row, head): 16 lanes x 16 bytes cover 128 columns per step, so a row of
+// O and of dO is one 256-byte transaction each (the head dim is a multiple of 8, rows are 16-byte aligned).
 template <typename T>
 __global__ void __launch_bounds__(128) bwd_delta_kernel(const __grid_constant__ BwdParams p) {
-  const int lane = threadIdx.x & 31;
-  const int64_t idx = (int64_t)blockIdx.x * 4 + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31, l16 = lane & 15;
+  const int64_t idx = ((int64_t)blockIdx.x * 4 + (threadIdx.x >> 5)) * 2 + (lane >> 4);
   const bool varlen = p.cu_seqlens_q != nullptr;
   const int64_t rows = varlen ? p.total_q : (int64_t)p.b * p.seqlen_q;
-  if (idx >= rows * p.h) return;
-  const int head = (int)(idx % p.h);
-  const int64_t row = idx / p.h;
+  const bool live = idx < rows * p.h;
+  const int head = live ? (int)(idx % p.h) : 0;
+  const int64_t row = live ? idx / p.h : 0;
   const int bi = varlen ? 0 : (int)(row / p.seqlen_q);
   const int64_t i = varlen ? row : row % p.seqlen_q;
   const T* o = reinterpret_cast<const T*>(p.o) + bi * p.o_batch_stride + i * p.o_row_stride + head * p.o_head_stride;
   const T* g = reinterpret_cast<const T*>(p.dout) + bi * p.do_batch_stride + i * p.do_row_stride + head * p.do_head_stride;
   float acc = 0.f;
-  for (int c = lane; c < p.d; c += 32) acc += to_f32<T>(o[c]) * to_f32<T>(g[c]);
+  if (live) {
+    for (int c = l16 * 8; c < p.d; c += 128) {
+      Vec16 a, b;
+      a.u = *reinterpret_cast<const uint4*>(o + c);
+      b.u = *reinterpret_cast<const uint4*>(g + c);
+      const T* av = reinterpret_cast<const T*>(&a);
+      const T* bv = reinterpret_cast<const T*>(&b);
 #pragma unroll
-  for (int s = 16; s > 0; s >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, s);
-  if (lane == 0) p.delta[bi * p.lse_batch_stride + head * p.lse_head_stride + i] = acc;
+      for (int e = 0; e < 8; ++e) acc += to_f32<T>(av[e]) * to_f32<T>(bv[e]);
+    }
+  }
+#pragma unroll
+  for (int s = 8; s > 0; s >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, s);
+  if (live && l16 == 0) p.delta[bi * p.lse_batch_stride + head * p.lse_head_stride + i] = acc;
 }
 
 // fp32 dQ accumulator -> dq in the output dtype.
