@@ -43,7 +43,7 @@ FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustain
 # processes, so a full launch is  bytes * units / units_of_the_case.
 NCU_TRAFFIC = {
     "c2": (586.76e6 + 129.76e6, 549755813888.0, "ncu, full size (profiles/fwd_tc5_kernel_c2_full_traffic.md), scaled by FLOPs"),
-    "c2_bwd": (202.64e6 + 90.51e6, 343597383680.0, "ncu, batch 1 of 4 (profiles/bwd_kernel_c2_shrink4.md), scaled by FLOPs"),
+    "c2_bwd": (135.32e6 + 38.92e6, 343597383680.0, "ncu, dK / dV kernel at batch 1 of 4 (profiles/bwd_dkv_dq_kernels_c2_shrink4.md), scaled by FLOPs"),
     "c3": (255.98e6 + 4.84e6, 253687872.0, "ncu, batch 16 of 64 (profiles/fwd_decode_kernel_c3_shrink4.md), scaled by bytes"),
     "c4": (132.48e6 + 3.92e6, 130785280.0, "ncu, batch 8 of 32 (profiles/fwd_decode_kernel_c4_shrink4.md), scaled by bytes"),
     "c5": (537.13e6 + 3.56e6, 537135104.0, "ncu, key length / 8 (profiles/fwd_decode_kernel_c5_shrink8.md), scaled by bytes"),

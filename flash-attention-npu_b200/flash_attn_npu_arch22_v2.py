@@ -82,7 +82,9 @@ def _check_bwd_features(alibi_slopes_, p_dropout, softcap):
 def bwd(dout, q, k, v, out, softmax_lse, dq_, dk_, dv_, alibi_slopes_, p_dropout, softmax_scale, is_causal,
         window_size_left, window_size_right, softcap, deterministic, gen_=None, rng_state=None):
     """Backward of ``fwd`` (argument order of the reference's pybind ``bwd``,
-    flash_attn_npu_v2/interface_arch22.py:232-252).  Returns [dq, dk, dv, softmax_d]."""
+    flash_attn_npu_v2/interface_arch22.py:232-252).  Returns [dq, dk, dv, softmax_d].
+    ``deterministic``: head dim 128 without softcap runs on kernels without atomics (bit-reproducible whatever the flag
+    says); the other shapes accumulate dQ with atomic adds and the flag does not change that."""
     _check_bwd_features(alibi_slopes_, p_dropout, softcap)
     dq, dk, dv = ops.attention_backward(dout, q, k, v, out, softmax_lse, dq=dq_, dk=dk_, dv=dv_,
                                         softmax_scale=softmax_scale, causal=is_causal,
