@@ -10,10 +10,10 @@
 
 namespace fa {
 
-// Head dim 128 without softcap; packed input needs the number of k / v rows for the TMA bounds.  Alignment and
-// stride rules are those fa_b200_bwd has already checked (16-byte rows).
+// Head dim 128; packed input needs the number of k / v rows for the TMA bounds.  Alignment and stride rules are
+// those fa_b200_bwd has already checked (16-byte rows).
 bool bwd_tc5_eligible(const fa_bwd_params& a) {
-  if (a.d != 128 || a.softcap > 0.f) return false;
+  if (a.d != 128) return false;
   if (a.cu_seqlens_q && a.total_k <= 0) return false;
   return true;
 }
@@ -54,12 +54,23 @@ int bwd_tc5_launch(const BwdParams& p, const fa_bwd_params& a, cudaStream_t st, 
       e = cudaGetLastError();
     }
   };
+  const bool cap = a.softcap > 0.f;
   if (a.dtype == FA_BF16) {
-    launch(bwd_dkv_kernel<__nv_bfloat16, 1>, grid_kv, tq_u, tdo_u, counters);
-    launch(bwd_dq_kernel<__nv_bfloat16, 1>, grid_q, tq, tdo, counters + 1);
+    if (cap) {
+      launch(bwd_dkv_kernel<__nv_bfloat16, 1, true>, grid_kv, tq_u, tdo_u, counters);
+      launch(bwd_dq_kernel<__nv_bfloat16, 1, true>, grid_q, tq, tdo, counters + 1);
+    } else {
+      launch(bwd_dkv_kernel<__nv_bfloat16, 1, false>, grid_kv, tq_u, tdo_u, counters);
+      launch(bwd_dq_kernel<__nv_bfloat16, 1, false>, grid_q, tq, tdo, counters + 1);
+    }
   } else {
-    launch(bwd_dkv_kernel<__half, 0>, grid_kv, tq_u, tdo_u, counters);
-    launch(bwd_dq_kernel<__half, 0>, grid_q, tq, tdo, counters + 1);
+    if (cap) {
+      launch(bwd_dkv_kernel<__half, 0, true>, grid_kv, tq_u, tdo_u, counters);
+      launch(bwd_dq_kernel<__half, 0, true>, grid_q, tq, tdo, counters + 1);
+    } else {
+      launch(bwd_dkv_kernel<__half, 0, false>, grid_kv, tq_u, tdo_u, counters);
+      launch(bwd_dq_kernel<__half, 0, false>, grid_q, tq, tdo, counters + 1);
+    }
   }
   if (e != cudaSuccess) { *err = std::string("tcgen05 backward launch: ") + cudaGetErrorString(e); return FA_ERR_CUDA; }
   return FA_OK;

@@ -86,13 +86,26 @@ constexpr int kPolyPairs = FA_BWD_POLY;
 
 // Two elements:  P = exp2(s * scale_log2 - lse2)  (0 where masked),  dS = P * (dP - D) * scale, both as packed 16-bit
 // pairs.  nlse2 = -lse2 and ndls2 = -D * scale per element, so the arithmetic is two packed fused multiply-adds, two
-// exponentials and one packed multiply.
+// exponentials and one packed multiply.  With softcap the capped score c * tanh(s * scale / c) replaces s * scale and
+// dS gets the factor 1 - tanh^2 (tests/fa_small_op_golden.py:80-89,124-125); a2 is then scale / c instead of
+// scale * log2(e), cap2 = c * log2(e).
 // (poly is a constant after unrolling: pair number & 3 < kPolyPairs)
-template <typename T, bool MASK>
-__device__ __forceinline__ void ew_pair(const bool poly, uint32_t s0, uint32_t s1, uint32_t d0, uint32_t d1, uint64_t scale_log2_2,
-                                        uint64_t nlse2, uint64_t scale2, uint64_t ndls2, uint32_t bits, int e,
+template <typename T, bool MASK, bool SOFTCAP>
+__device__ __forceinline__ void ew_pair(const bool poly, uint32_t s0, uint32_t s1, uint32_t d0, uint32_t d1, uint64_t a2,
+                                        uint64_t cap2, uint64_t nlse2, uint64_t scale2, uint64_t ndls2, uint32_t bits, int e,
                                         uint32_t& pk_p, uint32_t& pk_ds) {
-  const uint64_t x2 = fma_f32x2(pack_f32x2(__uint_as_float(s0), __uint_as_float(s1)), scale_log2_2, nlse2);
+  uint64_t x2, g2 = 0;
+  if (SOFTCAP) {
+    float y0, y1, t0, t1;
+    unpack_f32x2(mul_f32x2(pack_f32x2(__uint_as_float(s0), __uint_as_float(s1)), a2), y0, y1);
+    asm("tanh.approx.f32 %0, %1;\n" : "=f"(t0) : "f"(y0));
+    asm("tanh.approx.f32 %0, %1;\n" : "=f"(t1) : "f"(y1));
+    const uint64_t th2 = pack_f32x2(t0, t1);
+    x2 = fma_f32x2(th2, cap2, nlse2);
+    g2 = fma_f32x2(th2, pack_f32x2(-t0, -t1), pack_f32x2(1.f, 1.f));  // 1 - tanh^2
+  } else {
+    x2 = fma_f32x2(pack_f32x2(__uint_as_float(s0), __uint_as_float(s1)), a2, nlse2);
+  }
   float p0, p1;
   if (poly) {
     poly_exp2_x2(x2, p0, p1);
@@ -106,7 +119,8 @@ __device__ __forceinline__ void ew_pair(const bool poly, uint32_t s0, uint32_t s
     p0 = ((bits >> e) & 1u) ? p0 : 0.f;
     p1 = ((bits >> (e + 1)) & 1u) ? p1 : 0.f;
   }
-  const uint64_t t2 = fma_f32x2(pack_f32x2(__uint_as_float(d0), __uint_as_float(d1)), scale2, ndls2);
+  uint64_t t2 = fma_f32x2(pack_f32x2(__uint_as_float(d0), __uint_as_float(d1)), scale2, ndls2);
+  if (SOFTCAP) t2 = mul_f32x2(t2, g2);
   float ds0, ds1;
   unpack_f32x2(mul_f32x2(pack_f32x2(p0, p1), t2), ds0, ds1);
   pk_p = pack2<T>(p0, p1);
@@ -247,7 +261,7 @@ __device__ __forceinline__ ItemA item_a(const BwdParams& p, int t) {
   return w;
 }
 
-template <typename T, uint32_t AB_FMT>
+template <typename T, uint32_t AB_FMT, bool SOFTCAP>
 __global__ void __launch_bounds__(kThreads, 1)
 bwd_dkv_kernel(const __grid_constant__ BwdParams p, const __grid_constant__ CUtensorMap tm_q,
                const __grid_constant__ CUtensorMap tm_do, const __grid_constant__ CUtensorMap tm_k,
@@ -434,7 +448,8 @@ bwd_dkv_kernel(const __grid_constant__ BwdParams p, const __grid_constant__ CUte
     // wait / load / compute / store / signal, so that one's latencies lie under the other's arithmetic.
     const int kr = (warp & 3) * 32 + lane, q2 = (warp >> 2) & 1, grp = warp >> 3, q4 = warp >> 2;
     const uint32_t lane_addr = (uint32_t)((warp & 3) * 32) << 16;
-    const uint64_t sl2 = pack_f32x2(p.scale_log2, p.scale_log2), sc2 = pack_f32x2(p.softmax_scale, p.softmax_scale);
+    const float a1 = SOFTCAP ? p.softmax_scale / p.softcap : p.scale_log2, cap1 = p.softcap * kLog2e;
+    const uint64_t sl2 = pack_f32x2(a1, a1), cap2 = pack_f32x2(cap1, cap1), sc2 = pack_f32x2(p.softmax_scale, p.softmax_scale);
     const uint32_t st_tmem = tmem + lane_addr + 128 * grp + 32 * q2;  // this thread's 32 columns of S^T; dP^T 64 columns on
     auto unit = [&](auto mask_tag, int s, uint32_t bits) {
       constexpr bool MASK = decltype(mask_tag)::value;
@@ -449,9 +464,9 @@ bwd_dkv_kernel(const __grid_constant__ BwdParams p, const __grid_constant__ CUte
         for (int e4 = 0; e4 < 16; e4 += 4) {
           const float4 l4 = *reinterpret_cast<const float4*>(&bar->nlse2[s][32 * q2 + 16 * hf + e4]);
           const float4 d4 = *reinterpret_cast<const float4*>(&bar->ndls[s][32 * q2 + 16 * hf + e4]);
-          ew_pair<T, MASK>(((e4 >> 1) & 3) < kPolyPairs, sv[e4], sv[e4 + 1], dv[e4], dv[e4 + 1], sl2, pack_f32x2(l4.x, l4.y), sc2,
+          ew_pair<T, MASK, SOFTCAP>(((e4 >> 1) & 3) < kPolyPairs, sv[e4], sv[e4 + 1], dv[e4], dv[e4 + 1], sl2, cap2, pack_f32x2(l4.x, l4.y), sc2,
                            pack_f32x2(d4.x, d4.y), bits, 16 * hf + e4, pk_p[e4 >> 1], pk_ds[e4 >> 1]);
-          ew_pair<T, MASK>((((e4 >> 1) + 1) & 3) < kPolyPairs, sv[e4 + 2], sv[e4 + 3], dv[e4 + 2], dv[e4 + 3], sl2,
+          ew_pair<T, MASK, SOFTCAP>((((e4 >> 1) + 1) & 3) < kPolyPairs, sv[e4 + 2], sv[e4 + 3], dv[e4 + 2], dv[e4 + 3], sl2, cap2,
                            pack_f32x2(l4.z, l4.w), sc2, pack_f32x2(d4.z, d4.w), bits, 16 * hf + e4 + 2, pk_p[(e4 >> 1) + 1],
                            pk_ds[(e4 >> 1) + 1]);
         }
@@ -570,7 +585,7 @@ __device__ __forceinline__ ItemB item_b(const BwdParams& p, int t) {
   return w;
 }
 
-template <typename T, uint32_t AB_FMT>
+template <typename T, uint32_t AB_FMT, bool SOFTCAP>
 __global__ void __launch_bounds__(kThreads, 1)
 bwd_dq_kernel(const __grid_constant__ BwdParams p, const __grid_constant__ CUtensorMap tm_q,
               const __grid_constant__ CUtensorMap tm_do, const __grid_constant__ CUtensorMap tm_k,
@@ -757,7 +772,8 @@ bwd_dq_kernel(const __grid_constant__ BwdParams p, const __grid_constant__ CUten
     // ------------------------------------------------------------------ elementwise: lane = query row, 32 keys per thread
     const int r = (warp & 3) * 32 + lane, q4 = warp >> 2;
     const uint32_t lane_addr = (uint32_t)((warp & 3) * 32) << 16;
-    const uint64_t sl2 = pack_f32x2(p.scale_log2, p.scale_log2), sc2 = pack_f32x2(p.softmax_scale, p.softmax_scale);
+    const float a1 = SOFTCAP ? p.softmax_scale / p.softcap : p.scale_log2, cap1 = p.softcap * kLog2e;
+    const uint64_t sl2 = pack_f32x2(a1, a1), cap2 = pack_f32x2(cap1, cap1), sc2 = pack_f32x2(p.softmax_scale, p.softmax_scale);
     bool ok = true;
     while (ok) {
       const int t = queue_get(&bar->queue, wi, abort_flag);
@@ -795,11 +811,11 @@ bwd_dq_kernel(const __grid_constant__ BwdParams p, const __grid_constant__ CUten
           const uint32_t bits = range_bits(c0 + 32 * q4, lo, hi);
 #pragma unroll
           for (int e = 0; e < 32; e += 2)
-            ew_pair<T, true>(((e >> 1) & 3) < kPolyPairs, sv[e], sv[e + 1], dv[e], dv[e + 1], sl2, nlse2, sc2, ndls2, bits, e, unused, pk[e >> 1]);
+            ew_pair<T, true, SOFTCAP>(((e >> 1) & 3) < kPolyPairs, sv[e], sv[e + 1], dv[e], dv[e + 1], sl2, cap2, nlse2, sc2, ndls2, bits, e, unused, pk[e >> 1]);
         } else {
 #pragma unroll
           for (int e = 0; e < 32; e += 2)
-            ew_pair<T, false>(((e >> 1) & 3) < kPolyPairs, sv[e], sv[e + 1], dv[e], dv[e + 1], sl2, nlse2, sc2, ndls2, 0u, e, unused, pk[e >> 1]);
+            ew_pair<T, false, SOFTCAP>(((e >> 1) & 3) < kPolyPairs, sv[e], sv[e + 1], dv[e], dv[e + 1], sl2, cap2, nlse2, sc2, ndls2, 0u, e, unused, pk[e >> 1]);
         }
         if (g > 0 && !mbar_wait(smem_addr(&bar->ds_free), (g - 1) & 1, abort_flag, 79)) { ok = false; break; }
         tc_fence_after();

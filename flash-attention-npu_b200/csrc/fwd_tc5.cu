@@ -8,6 +8,7 @@
 #include <cstring>
 #include <mutex>
 #include <string>
+#include <type_traits>
 
 #include "fwd_tc5_roles.cuh"
 #include "fwd_tc5_softmax.cuh"
@@ -20,7 +21,7 @@ namespace tc5 {
 // data: warp 15 clears them in the last V tile (tail_fix_loop) and the producer checks the index tensors.  Dense
 // input needs neither, and its instance carries none of that code (the issuing warps' instruction stream is on
 // the kernel's critical path: measured 3-8 % on causal 4K).
-template <typename T, uint32_t AB_FMT, bool FIX>
+template <typename T, uint32_t AB_FMT, bool FIX, bool SOFTCAP>
 __global__ void __launch_bounds__(kThreads, 1)
 fwd_tc5_kernel(const __grid_constant__ Tc5Params p, const __grid_constant__ CUtensorMap tm_q,
                const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v) {
@@ -84,7 +85,7 @@ fwd_tc5_kernel(const __grid_constant__ Tc5Params p, const __grid_constant__ CUte
   // scores of a row plus working set, the other roles need far fewer.
   if (warp < 8) {
     asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;\n" ::"n"(kRegsSoftmax));
-    softmax_loop<T>(p, bar, tmem, p_smem, warp >> 2, warp & 3, lane);
+    softmax_loop<T, SOFTCAP>(p, bar, tmem, p_smem, warp >> 2, warp & 3, lane);
   } else if (warp < 12) {
     asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;\n" ::"n"(kRegsCorr));
     correction_loop<T>(p, bar, tmem, warp & 3, lane);
@@ -186,7 +187,7 @@ bool tc5_eligible(const fa_fwd_params& a, bool is_causal, bool is_local, int wl_
   // With rotary tables the mode also decides where q is rotated (per token or all at the cache length), and the
   // other kernels decide that on the device: such calls are left to them so that every kernel gives one answer.
   if (wl_on_device && a.rotary_cos) return false;
-  if (a.softcap > 0.f || a.partial_out || a.kv_total > 0) return false;
+  if (a.partial_out || a.kv_total > 0) return false;
   // TMA: 16-byte aligned bases and strides
   auto al = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; };
   if (!al(a.q) || !al(a.k) || !al(a.v) || !al(a.o)) return false;
@@ -235,6 +236,10 @@ int tc5_launch(const fa_fwd_params& a, const fa_fwd_plan& pl, cudaStream_t st, s
   p.m_tiles = pl.m_blocks;
   p.total_tiles = pl.m_blocks * a.b * a.h;
   p.scale_log2 = a.softmax_scale * kLog2e;
+  if (a.softcap > 0.f) {
+    p.softcap_mul = a.softmax_scale / a.softcap;
+    p.softcap_l2 = a.softcap * kLog2e;
+  }
   p.fix_tail = (a.seqused_k || a.cu_seqlens_k) ? 1 : 0;
   {
     // L2 chunks of the tile order (tile_info).  A chunk is 2 * grid / gcd(2 * grid, m_tiles) pairs: a whole
@@ -284,13 +289,18 @@ int tc5_launch(const fa_fwd_params& a, const fa_fwd_plan& pl, cudaStream_t st, s
       e = cudaGetLastError();
     }
   };
-  const bool bf = a.dtype == FA_BF16;
+  const bool bf = a.dtype == FA_BF16, cap = a.softcap > 0.f;
+  auto pick = [&](auto fix_tag, auto cap_tag) {
+    constexpr bool F = decltype(fix_tag)::value, C = decltype(cap_tag)::value;
+    if (bf) launch(fwd_tc5_kernel<__nv_bfloat16, 1, F, C>);
+    else launch(fwd_tc5_kernel<__half, 0, F, C>);
+  };
   if (p.fix_tail) {
-    if (bf) launch(fwd_tc5_kernel<__nv_bfloat16, 1, true>);
-    else launch(fwd_tc5_kernel<__half, 0, true>);
+    if (cap) pick(std::true_type{}, std::true_type{});
+    else pick(std::true_type{}, std::false_type{});
   } else {
-    if (bf) launch(fwd_tc5_kernel<__nv_bfloat16, 1, false>);
-    else launch(fwd_tc5_kernel<__half, 0, false>);
+    if (cap) pick(std::false_type{}, std::true_type{});
+    else pick(std::false_type{}, std::false_type{});
   }
   if (e != cudaSuccess) { *err = std::string("tcgen05 kernel launch: ") + cudaGetErrorString(e); return FA_ERR_CUDA; }
   return FA_OK;

@@ -61,6 +61,7 @@ struct Tc5Params {
   int32_t m_tiles;  // ceil(max seqlen_q / 256)
   int32_t total_tiles;
   float scale_log2;
+  float softcap_mul, softcap_l2;  // softcap: scores become softcap_l2 * tanh(s * softcap_mul) in the log2 domain (scale / softcap, softcap * log2 e)
   int32_t chunk_bh;          // (batch, head) pairs per L2 chunk of the tile order (tile_info)
   // 1: the rows behind the last key of a sequence hold foreign data (the unused tail of a KV cache or of a page,
   // the next sequence of a packed tensor) and must be cleared in V before P.V: P is 0 there, but 0 x NaN is NaN.

@@ -47,6 +47,17 @@ __device__ __forceinline__ void chunk_mask(uint32_t (&a)[32], int col_first, int
     if (!((valid >> e) & 1u)) a[e] = 0xff800000u;  // -inf
 }
 
+// softcap: s -> softcap * tanh(s * scale / softcap), here straight into the log2 domain (tests/test_flash_attn_npu_v2.py:
+// the golden applies it to the scaled scores before the mask).  tanh.approx has a relative error of 2^-11.
+__device__ __forceinline__ void chunk_softcap(uint32_t (&a)[32], float mul, float cap_l2) {
+#pragma unroll
+  for (int e = 0; e < 32; ++e) {
+    float th;
+    asm("tanh.approx.f32 %0, %1;\n" : "=f"(th) : "f"(__uint_as_float(a[e]) * mul));
+    a[e] = __float_as_uint(th * cap_l2);
+  }
+}
+
 // Build-time tuning constants of the softmax role.
 #ifndef FA_TC5_POLY
 #define FA_TC5_POLY 0
@@ -91,7 +102,7 @@ __device__ __forceinline__ void store_p_chunk(uint32_t p_row, uint32_t p_xor, in
   }
 }
 
-template <typename T>
+template <typename T, bool SOFTCAP>
 __device__ __forceinline__ void softmax_loop(const Tc5Params& p, Barriers* bar, uint32_t tmem, uint32_t p_smem, int t,
                                              int warp_in_wg, int lane) {
   volatile int* abort_flag = &bar->abort_flag;
@@ -104,7 +115,9 @@ __device__ __forceinline__ void softmax_loop(const Tc5Params& p, Barriers* bar, 
   const uint32_t p_xor = (uint32_t)(row & 7);
   const uint32_t bar_sfree = smem_addr(&bar->s_free[t]), bar_odone = smem_addr(&bar->o_done[t]);
   const uint32_t bar_oready = smem_addr(&bar->o_ready[t]), bar_ofree = smem_addr(&bar->o_free[t]);
-  const float scale_log2 = p.scale_log2;
+  // with softcap the scores are in the log2 domain once they have been capped: the scale is part of the cap
+  const float scale_log2 = SOFTCAP ? 1.f : p.scale_log2;
+  const float lse_scale = SOFTCAP ? 0.6931471805599453f : p.a.softmax_scale;  // running maximum -> natural log
   const uint64_t scale2 = pack_f32x2(scale_log2, scale_log2);
 
   TileSched sched(p);
@@ -150,6 +163,10 @@ __device__ __forceinline__ void softmax_loop(const Tc5Params& p, Barriers* bar, 
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(bar_sfree);
+      if (SOFTCAP) {
+#pragma unroll
+        for (int c = 0; c < 4; ++c) chunk_softcap(sc[c], p.softcap_mul, p.softcap_l2);
+      }
       if (need_mask) {
 #pragma unroll
         for (int c = 0; c < 4; ++c) chunk_mask(sc[c], col0 + c * 32, lo, hi);
@@ -212,7 +229,7 @@ __device__ __forceinline__ void softmax_loop(const Tc5Params& p, Barriers* bar, 
     if (lane == 0) mbar_arrive(smem_addr(&bar->stats_ready[t]));
     if (i < ti.q_len)
       p.a.lse[(int64_t)ti.bi * p.a.lse_batch_stride + (int64_t)ti.hh * p.a.lse_head_stride + ti.q_row0 + i] =
-          l_run > 0.f ? (m_run * p.a.softmax_scale + __logf(l_run)) : INFINITY;
+          l_run > 0.f ? (m_run * lse_scale + __logf(l_run)) : INFINITY;
   }
 }
 
