@@ -6,8 +6,9 @@
 Prints ONE JSON line (rank 0).  The headline (metric, value, ...) is the causal-prefill configuration the
 metric's TFLOP/s half is quoted on (c2: bf16, batch 4, seqlen 4096, 32 heads, head dim 128); the decode half of
 the metric (HBM GB/s on c3 contiguous decode, c4 paged windowed decode and c5 long-context sequence-sharded
-decode) is measured in the same run and reported, entry by entry with the same keys, under "workloads".
---workload X measures X alone.  A "step" is one forward over one batch of seeded synthetic inputs.
+decode) is measured in the same run and reported, entry by entry with the same keys, under "workloads", and so is
+the backward at the headline shape (c2_bwd: dQ, dK, dV from the forward's out and lse).
+--workload X measures X alone.  A "step" is one forward (c2_bwd: one backward) over one batch of seeded synthetic inputs.
 
 * value        whole-job throughput with inputs resident in HBM, timed with CUDA events on the
                launching stream (barrier + synchronize on both sides, max over ranks).
@@ -462,7 +463,7 @@ WORKLOADS = {"c2": Prefill, "c2_bwd": PrefillBackward, "c3": DecodeContiguous, "
 # driver
 # ------------------------------------------------------------------------------------------------
 HEADLINE = "c2"
-DECODE_HALF = ("c3", "c4", "c5")  # the decode half of the metric: entries of the default line's "workloads" object
+DECODE_HALF = ("c3", "c4", "c5", "c2_bwd")  # entries of the default line's "workloads" object: the decode half of the metric, and the backward at the headline shape
 DEFAULT_STEPS = {"c2": (20, 5), "c2_bwd": (10, 3)}  # (steps, warm-up); decode steps are 0.1-0.6 ms, so they run (200, 50)
 
 
@@ -648,7 +649,7 @@ def main():
     ap.add_argument("--steps", type=int, default=None, help="default: 20 (c2), 10 (c2_bwd), 200 (decode workloads)")
     ap.add_argument("--warmup", type=int, default=None, help="default: 5 (c2), 3 (c2_bwd), 50 (decode workloads)")
     ap.add_argument("--workload", default=None, choices=sorted(WORKLOADS),
-                    help="one workload only; default: c2 as the headline plus c3, c4, c5 under \"workloads\"")
+                    help="one workload only; default: c2 as the headline plus c3, c4, c5, c2_bwd under \"workloads\"")
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--cpu-budget", type=float, default=12.0)
