@@ -21,7 +21,7 @@ namespace tc5 {
 // data: warp 15 clears them in the last V tile (tail_fix_loop) and the producer checks the index tensors.  Dense
 // input needs neither, and its instance carries none of that code (the issuing warps' instruction stream is on
 // the kernel's critical path: measured 3-8 % on causal 4K).
-template <typename T, uint32_t AB_FMT, bool FIX, bool SOFTCAP>
+template <typename T, uint32_t AB_FMT, bool FIX, bool SOFTCAP, int HD>
 __global__ void __launch_bounds__(kThreads, 1)
 fwd_tc5_kernel(const __grid_constant__ Tc5Params p, const __grid_constant__ CUtensorMap tm_q,
                const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v) {
@@ -88,13 +88,13 @@ fwd_tc5_kernel(const __grid_constant__ Tc5Params p, const __grid_constant__ CUte
     softmax_loop<T, SOFTCAP>(p, bar, tmem, p_smem, warp >> 2, warp & 3, lane);
   } else if (warp < 12) {
     asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;\n" ::"n"(kRegsCorr));
-    correction_loop<T>(p, bar, tmem, warp & 3, lane);
+    correction_loop<T, HD>(p, bar, tmem, warp & 3, lane);
   } else {
     asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;\n" ::"n"(kRegsMma));
     // warp-uniform role code; one elected lane issues
-    if (warp == kMmaWarp || warp == kMmaWarp + 1) mma_loop<AB_FMT, FIX>(p, bar, q_smem, p_smem, kv_smem, tmem, warp - kMmaWarp);
-    else if (warp == kTmaWarp) producer_loop<FIX>(p, &tm_q, &tm_k, &tm_v, bar, q_smem, kv_smem);
-    else if (FIX) tail_fix_loop(p, bar, kv_smem, lane);
+    if (warp == kMmaWarp || warp == kMmaWarp + 1) mma_loop<AB_FMT, FIX, HD>(p, bar, q_smem, p_smem, kv_smem, tmem, warp - kMmaWarp);
+    else if (warp == kTmaWarp) producer_loop<FIX, HD>(p, &tm_q, &tm_k, &tm_v, bar, q_smem, kv_smem);
+    else if (FIX) tail_fix_loop<HD>(p, bar, kv_smem, lane);
   }
 
   tc_fence_before();
@@ -172,7 +172,7 @@ static int32_t* status_word() {
 bool tc5_eligible(const fa_fwd_params& a, bool is_causal, bool is_local, int wl_on_device) {
   (void)is_causal;
   (void)is_local;
-  if (a.d != 128 || a.seqlen_q < 128) return false;
+  if ((a.d != 128 && a.d != 64) || a.seqlen_q < 128) return false;
   // varlen: both sides packed, and the number of k / v rows known (TMA bound)
   if ((a.cu_seqlens_q != nullptr) != (a.cu_seqlens_k != nullptr)) return false;
   if (a.cu_seqlens_k && a.total_k <= 0) return false;
@@ -290,17 +290,22 @@ int tc5_launch(const fa_fwd_params& a, const fa_fwd_plan& pl, cudaStream_t st, s
     }
   };
   const bool bf = a.dtype == FA_BF16, cap = a.softcap > 0.f;
-  auto pick = [&](auto fix_tag, auto cap_tag) {
+  auto pick = [&](auto fix_tag, auto cap_tag, auto hd_tag) {
     constexpr bool F = decltype(fix_tag)::value, C = decltype(cap_tag)::value;
-    if (bf) launch(fwd_tc5_kernel<__nv_bfloat16, 1, F, C>);
-    else launch(fwd_tc5_kernel<__half, 0, F, C>);
+    constexpr int HD = decltype(hd_tag)::value;
+    if (bf) launch(fwd_tc5_kernel<__nv_bfloat16, 1, F, C, HD>);
+    else launch(fwd_tc5_kernel<__half, 0, F, C, HD>);
+  };
+  auto pick_hd = [&](auto fix_tag, auto cap_tag) {
+    if (a.d == 64) pick(fix_tag, cap_tag, std::integral_constant<int, 64>{});
+    else pick(fix_tag, cap_tag, std::integral_constant<int, 128>{});
   };
   if (p.fix_tail) {
-    if (cap) pick(std::true_type{}, std::true_type{});
-    else pick(std::true_type{}, std::false_type{});
+    if (cap) pick_hd(std::true_type{}, std::true_type{});
+    else pick_hd(std::true_type{}, std::false_type{});
   } else {
-    if (cap) pick(std::false_type{}, std::true_type{});
-    else pick(std::false_type{}, std::false_type{});
+    if (cap) pick_hd(std::false_type{}, std::true_type{});
+    else pick_hd(std::false_type{}, std::false_type{});
   }
   if (e != cudaSuccess) { *err = std::string("tcgen05 kernel launch: ") + cudaGetErrorString(e); return FA_ERR_CUDA; }
   return FA_OK;

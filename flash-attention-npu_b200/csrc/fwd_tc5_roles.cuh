@@ -28,7 +28,8 @@ struct RingPos {
 // pages hold whole 128-key blocks, the page of a block comes from the block table (the warp keeps
 // 32 consecutive entries in registers, one per lane).
 // ---------------------------------------------------------------------------------------------
-template <bool FIX>
+// HD (64 or 128) is the head dim: with 64 a Q / K / V tile is the first 64-column half of its 32 KiB slot only.
+template <bool FIX, int HD>
 __device__ __forceinline__ void producer_loop(const Tc5Params& p, const CUtensorMap* tm_q, const CUtensorMap* tm_k,
                                               const CUtensorMap* tm_v, Barriers* bar, uint32_t q_smem, uint32_t kv_smem) {
   volatile int* abort_flag = &bar->abort_flag;
@@ -52,9 +53,9 @@ __device__ __forceinline__ void producer_loop(const Tc5Params& p, const CUtensor
       const int row = ti.q_row0 + ti.row0[t];
       const int bq = varlen_q ? 0 : ti.bi;
       if (elect_one()) {
-        mbar_arrive_expect_tx(full, kTileBytes);
+        mbar_arrive_expect_tx(full, (HD / 64) * kHalfBytes);
         tma_load_4d_hint(q_smem + t * kTileBytes, tm_q, full, 0, ti.hh, row, bq, q_policy);
-        tma_load_4d_hint(q_smem + t * kTileBytes + kHalfBytes, tm_q, full, 64, ti.hh, row, bq, q_policy);
+        if (HD > 64) tma_load_4d_hint(q_smem + t * kTileBytes + kHalfBytes, tm_q, full, 64, ti.hh, row, bq, q_policy);
       }
       __syncwarp();
     }
@@ -83,9 +84,9 @@ __device__ __forceinline__ void producer_loop(const Tc5Params& p, const CUtensor
       if (!mbar_wait(smem_addr(&bar->kv_empty[slot]), par ^ 1, abort_flag, 12)) return false;
       const uint32_t full = smem_addr(&bar->kv_full[slot]);
       if (elect_one()) {
-        mbar_arrive_expect_tx(full, kTileBytes);
+        mbar_arrive_expect_tx(full, (HD / 64) * kHalfBytes);
         tma_load_4d(kv_smem + slot * kTileBytes, tm, full, 0, ti.hk, row, outer);
-        tma_load_4d(kv_smem + slot * kTileBytes + kHalfBytes, tm, full, 64, ti.hk, row, outer);
+        if (HD > 64) tma_load_4d(kv_smem + slot * kTileBytes + kHalfBytes, tm, full, 64, ti.hk, row, outer);
       }
       __syncwarp();
       return true;
@@ -112,6 +113,7 @@ __device__ __forceinline__ bool tile_needs_tail_fix(const Tc5Params& p, const Ti
   return p.fix_tail && ti.uhi > ti.ulo && ti.uhi * kBlockN > ti.k_len;
 }
 
+template <int HD>
 __device__ __forceinline__ void tail_fix_loop(const Tc5Params& p, Barriers* bar, uint32_t kv_smem, int lane) {
   if (!p.fix_tail) return;
   volatile int* abort_flag = &bar->abort_flag;
@@ -127,7 +129,7 @@ __device__ __forceinline__ void tail_fix_loop(const Tc5Params& p, Barriers* bar,
     const int r0 = ti.k_len - (ti.uhi - 1) * kBlockN;  // first row without a key, 1 .. 127
     // a row is 128 bytes in each 64-column half of the tile (the swizzle only permutes inside a row)
 #pragma unroll
-    for (int half = 0; half < 2; ++half) {
+    for (int half = 0; half < HD / 64; ++half) {
       const uint32_t base = kv_smem + slot * kTileBytes + half * kHalfBytes;
       for (int off = r0 * 128 + lane * 16; off < kHalfBytes; off += 32 * 16)
         asm volatile("st.shared.v4.b32 [%0], {%1,%1,%1,%1};\n" ::"r"(base + off), "r"(0) : "memory");
@@ -146,12 +148,12 @@ __device__ __forceinline__ void tail_fix_loop(const Tc5Params& p, Barriers* bar,
 // threads to have copied S_t into registers, so it runs under this block's exponentials.
 // A K / V slot is released by two arrivals: one per sub-tile, or both from the only user.
 // ---------------------------------------------------------------------------------------------
-template <uint32_t AB_FMT, bool FIX>
+template <uint32_t AB_FMT, bool FIX, int HD>
 __device__ __forceinline__ void mma_loop(const Tc5Params& p, Barriers* bar, uint32_t q_smem, uint32_t p_smem,
                                          uint32_t kv_smem, uint32_t tmem, const int t) {
   volatile int* abort_flag = &bar->abort_flag;
   constexpr uint32_t idesc_qk = make_idesc(AB_FMT, kBlockM, kBlockN, 0);
-  constexpr uint32_t idesc_pv = make_idesc(AB_FMT, kBlockM, 128, 1);
+  constexpr uint32_t idesc_pv = make_idesc(AB_FMT, kBlockM, HD, 1);
   RingPos ring;
   uint32_t q_cnt = 0, qk_cnt = 0, p_cnt = 0, ofree_cnt = 0, oready_cnt = 0;
   // Descriptor bases are built once; inside the loops a descriptor is base + a small constant.
@@ -214,7 +216,7 @@ __device__ __forceinline__ void mma_loop(const Tc5Params& p, Barriers* bar, uint
       if (elect_one()) {
         mma_ss_c<false>(s_tmem, q_desc, k_desc, idesc_qk);
 #pragma unroll
-        for (int ks = 1; ks < 8; ++ks) mma_ss_c<true>(s_tmem, q_desc + k_off(ks), k_desc + k_off(ks), idesc_qk);
+        for (int ks = 1; ks < HD / 16; ++ks) mma_ss_c<true>(s_tmem, q_desc + k_off(ks), k_desc + k_off(ks), idesc_qk);
         mma_commit(bar_sfull);
         if (j == jhi_t - 1) mma_commit(smem_addr(&bar->q_empty[t]));
         mma_commit(bar_kvempty0 + slot * 8);

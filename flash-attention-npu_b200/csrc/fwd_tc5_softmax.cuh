@@ -233,7 +233,8 @@ __device__ __forceinline__ void softmax_loop(const Tc5Params& p, Barriers* bar, 
   }
 }
 
-// Multiplies the 128 fp32 columns of one TMEM lane by f (two chunks in flight).
+// Multiplies the HD fp32 columns of one TMEM lane by f (two chunks in flight).
+template <int HD>
 __device__ __forceinline__ void rescale_o(uint32_t o_tmem, float f) {
   const uint64_t f2 = pack_f32x2(f, f);
   uint32_t a[32], b[32];
@@ -241,7 +242,7 @@ __device__ __forceinline__ void rescale_o(uint32_t o_tmem, float f) {
   tmem_ld32(o_tmem + 32, b);
   tmem_wait_ld();
 #pragma unroll
-  for (int half = 0; half < 2; ++half) {
+  for (int half = 0; half < HD / 64; ++half) {
 #pragma unroll
     for (int e = 0; e < 32; e += 2) {
       float x0, x1;
@@ -254,7 +255,7 @@ __device__ __forceinline__ void rescale_o(uint32_t o_tmem, float f) {
     }
     tmem_st32(o_tmem + half * 64, a);
     tmem_st32(o_tmem + half * 64 + 32, b);
-    if (half == 0) {
+    if (half == 0 && HD > 64) {
       tmem_ld32(o_tmem + 64, a);
       tmem_ld32(o_tmem + 96, b);
       tmem_wait_ld();
@@ -263,7 +264,7 @@ __device__ __forceinline__ void rescale_o(uint32_t o_tmem, float f) {
   tmem_wait_st();
 }
 
-template <typename T>
+template <typename T, int HD>
 __device__ __forceinline__ void correction_loop(const Tc5Params& p, Barriers* bar, uint32_t tmem, int warp_in_wg,
                                                 int lane) {
   volatile int* abort_flag = &bar->abort_flag;
@@ -287,7 +288,7 @@ __device__ __forceinline__ void correction_loop(const Tc5Params& p, Barriers* ba
         ++od_cnt[t];
         if (__any_sync(0xffffffffu, f != 1.f)) {
           tc_fence_after();
-          rescale_o(tmem + lane_addr + 256 + t * 128, f);
+          rescale_o<HD>(tmem + lane_addr + 256 + t * 128, f);
           tc_fence_before();
         }
         __syncwarp();
@@ -313,7 +314,7 @@ __device__ __forceinline__ void correction_loop(const Tc5Params& p, Barriers* ba
       tmem_ld32(o_tmem, a);
       tmem_ld32(o_tmem + 32, b);
 #pragma unroll
-      for (int half = 0; half < 2; ++half) {
+      for (int half = 0; half < HD / 64; ++half) {
         tmem_wait_ld();
         if (row_valid) {
 #pragma unroll
@@ -335,7 +336,7 @@ __device__ __forceinline__ void correction_loop(const Tc5Params& p, Barriers* ba
             __stcs(reinterpret_cast<uint4*>(o_ptr + half * 64 + 32 + e), w);
           }
         }
-        if (half == 0) {
+        if (half == 0 && HD > 64) {
           tmem_ld32(o_tmem + 64, a);
           tmem_ld32(o_tmem + 96, b);
         }
