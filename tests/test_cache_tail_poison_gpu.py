@@ -75,12 +75,13 @@ def _check(q, kc, vc, kn, vn, lens, bt, idx, kernel, tag, causal=True, window=(-
 
 
 @pytest.mark.parametrize("append", [False, True], ids=["read", "append"])
-@pytest.mark.parametrize("layout", ["contiguous", "page128", "page256", "batch_idx"])
-def test_tcgen05_prefill_ignores_the_cache_tail(layout, append):
+@pytest.mark.parametrize("layout,d", [("contiguous", 128), ("page128", 128), ("page256", 128), ("batch_idx", 128),
+                                      ("contiguous", 64), ("page128", 64)])
+def test_tcgen05_prefill_ignores_the_cache_tail(layout, d, append):
     """Chunked prefill (200 query tokens) against a cache: lengths that end inside a 128-key block, exactly on a
-    block boundary, inside a page, an empty entry, a full cache."""
+    block boundary, inside a page, an empty entry, a full cache; head dims 128 and 64."""
     g = torch.Generator().manual_seed(4100 + len(layout) + append)
-    b, s_q, h, hk, d, s_cache = 6, 200, 8, 2, 128, 1536
+    b, s_q, h, hk, s_cache = 6, 200, 8, 2, 1536
     s_new = s_q if append else 0
     lens = torch.tensor([333, 1024, 77, 0, s_cache - s_new, 1281 - s_new if append else 1281], dtype=torch.int32)
     page = {"page128": 128, "page256": 256}.get(layout, 0)
@@ -89,7 +90,7 @@ def test_tcgen05_prefill_ignores_the_cache_tail(layout, append):
     kn = vn = cos = sin = None
     if append:
         kn, vn = U.normal((b, s_new, hk, d), BF, g), U.normal((b, s_new, hk, d), BF, g)
-        cos, sin = U.rotary_tables(s_cache + 8, 64, BF)
+        cos, sin = U.rotary_tables(s_cache + 8, d // 2, BF)
     _check(q, kc, vc, kn, vn, lens, bt, idx, L.KERNEL_TCGEN05, f"tcgen05 {layout} append={append}", cos=cos, sin=sin)
     if not append:  # a sliding window on top: the last block is still the one with the tail
         _check(q, kc, vc, None, None, lens, bt, idx, L.KERNEL_TCGEN05, f"tcgen05 {layout} window", window=(300, 0))

@@ -71,29 +71,31 @@ def test_varlen_ragged_lengths():
         U.check_rules(out, lse, gold_out, gold_lse, tag=f"ragged causal={causal}")
 
 
-def test_varlen_ragged_lengths_tcgen05():
-    """Ragged packed sequences on the tcgen05 kernel: tiles that run into the next sequence, an empty
-    sequence, queries longer than the keys (rows without a visible key), GQA, a sliding window."""
+@pytest.mark.parametrize("d,softcap", [(128, 0.0), (64, 0.0), (128, 30.0), (64, 30.0)])
+def test_varlen_ragged_lengths_tcgen05(d, softcap):
+    """Ragged packed sequences on the tcgen05 kernel (head dims 128 and 64, with and without softcap): tiles that run
+    into the next sequence, an empty sequence, queries longer than the keys (rows without a visible key), GQA, a
+    sliding window."""
     from flash_b200 import lib as L
     from flash_b200 import ops
     g = torch.Generator().manual_seed(123)
     q_lens, k_lens = [300, 0, 77, 513, 700], [300, 40, 77, 900, 100]
     cq = torch.tensor([0] + list(itertools.accumulate(q_lens)), dtype=torch.int32)
     ck = torch.tensor([0] + list(itertools.accumulate(k_lens)), dtype=torch.int32)
-    q = U.normal((sum(q_lens), 4, 128), BF, g)
-    k = U.normal((sum(k_lens), 2, 128), BF, g)
-    v = U.normal((sum(k_lens), 2, 128), BF, g)
-    scale = 1.0 / 128 ** 0.5
+    q = U.normal((sum(q_lens), 4, d), BF, g)
+    k = U.normal((sum(k_lens), 2, d), BF, g)
+    v = U.normal((sum(k_lens), 2, d), BF, g)
+    scale = 1.0 / d ** 0.5
     for causal, window in ((False, (-1, -1)), (True, (-1, -1)), (True, (200, 0))):
         gold_out, gold_lse = OA.flash_attn_varlen_func(q, k, v, cq, ck, max(q_lens), max(k_lens), softmax_scale=scale,
-                                                       causal=causal, window_size=window)
+                                                       causal=causal, window_size=window, softcap=softcap)
         out, lse, plan = ops.attention_forward(q.cuda(), k.cuda(), v.cuda(), softmax_scale=scale, causal=causal,
-                                               window_left=window[0], window_right=window[1],
+                                               window_left=window[0], window_right=window[1], softcap=softcap,
                                                cu_seqlens_q=cq.cuda(), cu_seqlens_k=ck.cuda(),
                                                max_seqlen_q=max(q_lens), max_seqlen_k=max(k_lens), return_plan=True)
         assert plan.kernel == L.KERNEL_TCGEN05
         assert L.load().fa_b200_check_status(torch.cuda.current_stream().cuda_stream) == 0
-        U.check_rules(out, lse, gold_out, gold_lse, tag=f"tcgen05 ragged causal={causal} window={window}")
+        U.check_rules(out, lse, gold_out, gold_lse, tag=f"tcgen05 ragged d={d} softcap={softcap} causal={causal} window={window}")
 
 
 @pytest.mark.gpu
