@@ -172,7 +172,9 @@ static int32_t* status_word() {
 bool tc5_eligible(const fa_fwd_params& a, bool is_causal, bool is_local, int wl_on_device) {
   (void)is_causal;
   (void)is_local;
-  if ((a.d != 128 && a.d != 64) || a.seqlen_q < 128) return false;
+  // any head dim up to 128 that keeps rows 16-byte aligned: the tiles are 64 or 128 columns wide and the TMA unit
+  // fills the columns beyond the head dim with zeros
+  if (a.d < 8 || a.d > 128 || a.d % 8 != 0 || a.seqlen_q < 128) return false;
   // varlen: both sides packed, and the number of k / v rows known (TMA bound)
   if ((a.cu_seqlens_q != nullptr) != (a.cu_seqlens_k != nullptr)) return false;
   if (a.cu_seqlens_k && a.total_k <= 0) return false;
@@ -297,7 +299,7 @@ int tc5_launch(const fa_fwd_params& a, const fa_fwd_plan& pl, cudaStream_t st, s
     else launch(fwd_tc5_kernel<__half, 0, F, C, HD>);
   };
   auto pick_hd = [&](auto fix_tag, auto cap_tag) {
-    if (a.d == 64) pick(fix_tag, cap_tag, std::integral_constant<int, 64>{});
+    if (a.d <= 64) pick(fix_tag, cap_tag, std::integral_constant<int, 64>{});
     else pick(fix_tag, cap_tag, std::integral_constant<int, 128>{});
   };
   if (p.fix_tail) {

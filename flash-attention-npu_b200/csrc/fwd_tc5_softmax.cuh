@@ -271,6 +271,7 @@ __device__ __forceinline__ void correction_loop(const Tc5Params& p, Barriers* ba
   const int row = warp_in_wg * 32 + lane;
   const uint32_t lane_addr = (uint32_t)(warp_in_wg * 32) << 16;
   uint32_t cr_cnt[2] = {0, 0}, od_cnt[2] = {0, 0}, st_cnt[2] = {0, 0};
+  const int d_cols = p.a.d;
 
   TileSched sched(p);
   for (int n = sched.first(); n < p.total_tiles; n = sched.next()) {
@@ -324,7 +325,9 @@ __device__ __forceinline__ void correction_loop(const Tc5Params& p, Barriers* ba
             w.y = pack2<T>(__uint_as_float(a[e + 2]) * inv, __uint_as_float(a[e + 3]) * inv);
             w.z = pack2<T>(__uint_as_float(a[e + 4]) * inv, __uint_as_float(a[e + 5]) * inv);
             w.w = pack2<T>(__uint_as_float(a[e + 6]) * inv, __uint_as_float(a[e + 7]) * inv);
-            __stcs(reinterpret_cast<uint4*>(o_ptr + half * 64 + e), w);  // written once, read by nobody here: streaming
+            // written once, read by nobody here: streaming.  Head dims between the two tile widths: the tiles' columns
+            // beyond the head dim are the zeros the TMA unit fills in, and are not stored.
+            if (half * 64 + e < d_cols) __stcs(reinterpret_cast<uint4*>(o_ptr + half * 64 + e), w);
           }
 #pragma unroll
           for (int e = 0; e < 32; e += 8) {
@@ -333,7 +336,7 @@ __device__ __forceinline__ void correction_loop(const Tc5Params& p, Barriers* ba
             w.y = pack2<T>(__uint_as_float(b[e + 2]) * inv, __uint_as_float(b[e + 3]) * inv);
             w.z = pack2<T>(__uint_as_float(b[e + 4]) * inv, __uint_as_float(b[e + 5]) * inv);
             w.w = pack2<T>(__uint_as_float(b[e + 6]) * inv, __uint_as_float(b[e + 7]) * inv);
-            __stcs(reinterpret_cast<uint4*>(o_ptr + half * 64 + 32 + e), w);
+            if (half * 64 + 32 + e < d_cols) __stcs(reinterpret_cast<uint4*>(o_ptr + half * 64 + 32 + e), w);
           }
         }
         if (half == 0 && HD > 64) {

@@ -10,8 +10,8 @@
 
 namespace fa {
 
-// True when the tcgen05 kernel covers this problem (head dim 128, at least 128 query rows; dense,
-// packed varlen, or a KV cache with per-entry lengths, paged or not; no alibi or softcap).
+// True when the tcgen05 kernel covers this problem (head dim up to 128, at least 128 query rows; dense,
+// packed varlen, or a KV cache with per-entry lengths, paged or not; no alibi).
 bool tc5_eligible(const fa_fwd_params& a, bool is_causal, bool is_local, int wl_on_device);
 // Overwrites the tile fields of the plan for the tcgen05 kernel.
 void tc5_fill_plan(const fa_fwd_params& a, fa_fwd_plan* pl);
