@@ -106,7 +106,7 @@ int fa_b200_bwd(const fa_bwd_params* a, void* workspace, size_t workspace_bytes,
   if (a->kernel < 0 || a->kernel > 2) return fail_bwd(FA_ERR_INVALID, "kernel must be 0 (automatic), 1 (mma.sync) or 2 (tcgen05)");
   const bool tc5 = a->kernel != 1 && bwd_tc5_eligible(*a);
   if (a->kernel == 2 && !tc5)
-    return fail_bwd(FA_ERR_UNSUPPORTED, "the tcgen05 backward covers head dim 128 (packed input: total_k given)");
+    return fail_bwd(FA_ERR_UNSUPPORTED, "the tcgen05 backward covers head dims up to 128 (packed input: total_k given)");
   cudaError_t e = cudaSuccess;
   if (!tc5) e = cudaMemsetAsync(p.dq_accum, 0, acc_bytes, cs);
   if (e != cudaSuccess) return fail_bwd(FA_ERR_CUDA, std::string("cudaMemsetAsync: ") + cudaGetErrorString(e));

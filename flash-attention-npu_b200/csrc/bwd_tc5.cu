@@ -4,16 +4,20 @@
 
 #include <algorithm>
 #include <string>
+#include <type_traits>
 
 #include "bwd_tc5_kernel.cuh"
 #include "tc5_api.cuh"
 
 namespace fa {
 
-// Head dim 128; packed input needs the number of k / v rows for the TMA bounds.  Alignment and stride rules are
-// those fa_b200_bwd has already checked (16-byte rows).
+template <typename T>
+struct TypeTag { using type = T; };
+
+// Head dims up to 128 (tiles of 64 or 128 columns; the TMA unit zero-fills beyond the head dim); packed input needs the
+// number of k / v rows for the TMA bounds.  Alignment and stride rules are those fa_b200_bwd has already checked.
 bool bwd_tc5_eligible(const fa_bwd_params& a) {
-  if (a.d != 128) return false;
+  if (a.d > 128) return false;
   if (a.cu_seqlens_q && a.total_k <= 0) return false;
   return true;
 }
@@ -54,24 +58,24 @@ int bwd_tc5_launch(const BwdParams& p, const fa_bwd_params& a, cudaStream_t st, 
       e = cudaGetLastError();
     }
   };
-  const bool cap = a.softcap > 0.f;
-  if (a.dtype == FA_BF16) {
-    if (cap) {
-      launch(bwd_dkv_kernel<__nv_bfloat16, 1, true>, grid_kv, tq_u, tdo_u, counters);
-      launch(bwd_dq_kernel<__nv_bfloat16, 1, true>, grid_q, tq, tdo, counters + 1);
-    } else {
-      launch(bwd_dkv_kernel<__nv_bfloat16, 1, false>, grid_kv, tq_u, tdo_u, counters);
-      launch(bwd_dq_kernel<__nv_bfloat16, 1, false>, grid_q, tq, tdo, counters + 1);
-    }
-  } else {
-    if (cap) {
-      launch(bwd_dkv_kernel<__half, 0, true>, grid_kv, tq_u, tdo_u, counters);
-      launch(bwd_dq_kernel<__half, 0, true>, grid_q, tq, tdo, counters + 1);
-    } else {
-      launch(bwd_dkv_kernel<__half, 0, false>, grid_kv, tq_u, tdo_u, counters);
-      launch(bwd_dq_kernel<__half, 0, false>, grid_q, tq, tdo, counters + 1);
-    }
-  }
+  auto both = [&](auto t_tag, auto fmt_tag, auto cap_tag, auto hd_tag) {  // tags: compile-time choices as types
+    using T = typename decltype(t_tag)::type;
+    constexpr uint32_t F = decltype(fmt_tag)::value;
+    constexpr bool C = decltype(cap_tag)::value;
+    constexpr int HD = decltype(hd_tag)::value;
+    launch(bwd_dkv_kernel<T, F, C, HD>, grid_kv, tq_u, tdo_u, counters);
+    launch(bwd_dq_kernel<T, F, C, HD>, grid_q, tq, tdo, counters + 1);
+  };
+  auto by_hd = [&](auto t_tag, auto fmt_tag, auto cap_tag) {
+    if (a.d <= 64) both(t_tag, fmt_tag, cap_tag, std::integral_constant<int, 64>{});
+    else both(t_tag, fmt_tag, cap_tag, std::integral_constant<int, 128>{});
+  };
+  auto by_cap = [&](auto t_tag, auto fmt_tag) {
+    if (a.softcap > 0.f) by_hd(t_tag, fmt_tag, std::true_type{});
+    else by_hd(t_tag, fmt_tag, std::false_type{});
+  };
+  if (a.dtype == FA_BF16) by_cap(TypeTag<__nv_bfloat16>{}, std::integral_constant<uint32_t, 1>{});
+  else by_cap(TypeTag<__half>{}, std::integral_constant<uint32_t, 0>{});
   if (e != cudaSuccess) { *err = std::string("tcgen05 backward launch: ") + cudaGetErrorString(e); return FA_ERR_CUDA; }
   return FA_OK;
 }

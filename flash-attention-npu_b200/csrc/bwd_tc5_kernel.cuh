@@ -184,10 +184,12 @@ __device__ __forceinline__ SeqInfo seq_info(const BwdParams& p, int bi) {
   return s;
 }
 
+// 32 columns of a row, of which the first n_cols (a multiple of 8, possibly <= 0) exist
 template <typename T>
-__device__ __forceinline__ void store_slice(T* dst, const uint32_t (&a)[32]) {
+__device__ __forceinline__ void store_slice(T* dst, const uint32_t (&a)[32], int n_cols) {
 #pragma unroll
   for (int e = 0; e < 32; e += 8) {
+    if (e >= n_cols) break;
     uint4 w;
     w.x = pack2<T>(__uint_as_float(a[e]), __uint_as_float(a[e + 1]));
     w.y = pack2<T>(__uint_as_float(a[e + 2]), __uint_as_float(a[e + 3]));
@@ -261,7 +263,8 @@ __device__ __forceinline__ ItemA item_a(const BwdParams& p, int t) {
   return w;
 }
 
-template <typename T, uint32_t AB_FMT, bool SOFTCAP>
+// HD (64 or 128): width of the tiles; a head dim below it leaves zero columns (filled in by the TMA unit) that are not stored.
+template <typename T, uint32_t AB_FMT, bool SOFTCAP, int HD>
 __global__ void __launch_bounds__(kThreads, 1)
 bwd_dkv_kernel(const __grid_constant__ BwdParams p, const __grid_constant__ CUtensorMap tm_q,
                const __grid_constant__ CUtensorMap tm_do, const __grid_constant__ CUtensorMap tm_k,
@@ -330,7 +333,7 @@ bwd_dkv_kernel(const __grid_constant__ BwdParams p, const __grid_constant__ CUte
                  (int64_t)w.hk * p.dv_head_stride;
         for (int c = lane; c < kBlk * 16; c += 32) {
           const int r = c >> 4, ch = c & 15;
-          if (w.key0 + r < sq.k_len) {
+          if (w.key0 + r < sq.k_len && ch * 8 < p.d) {
             *reinterpret_cast<uint4*>(dk0 + (int64_t)r * p.dk_row_stride + ch * 8) = make_uint4(0, 0, 0, 0);
             *reinterpret_cast<uint4*>(dv0 + (int64_t)r * p.dv_row_stride + ch * 8) = make_uint4(0, 0, 0, 0);
           }
@@ -341,11 +344,11 @@ bwd_dkv_kernel(const __grid_constant__ BwdParams p, const __grid_constant__ CUte
       if (!mbar_wait(smem_addr(&bar->kv_empty), (wi & 1) ^ 1, abort_flag, 60)) break;
       if (elect_one()) {
         const uint32_t full = smem_addr(&bar->kv_full);
-        mbar_arrive_expect_tx(full, 2 * kTileBytes);
+        mbar_arrive_expect_tx(full, 2 * (HD / 64) * kHalfBytes);
         tma_load_4d(k_smem, &tm_k, full, 0, w.hk, sq.k_row0 + w.key0, sq.bq);
-        tma_load_4d(k_smem + kHalfBytes, &tm_k, full, 64, w.hk, sq.k_row0 + w.key0, sq.bq);
+        if (HD > 64) tma_load_4d(k_smem + kHalfBytes, &tm_k, full, 64, w.hk, sq.k_row0 + w.key0, sq.bq);
         tma_load_4d(v_smem, &tm_v, full, 0, w.hk, sq.k_row0 + w.key0, sq.bq);
-        tma_load_4d(v_smem + kHalfBytes, &tm_v, full, 64, w.hk, sq.k_row0 + w.key0, sq.bq);
+        if (HD > 64) tma_load_4d(v_smem + kHalfBytes, &tm_v, full, 64, w.hk, sq.k_row0 + w.key0, sq.bq);
       }
       __syncwarp();
       for (int it = 0; it < w.iters; ++it) {
@@ -362,11 +365,11 @@ bwd_dkv_kernel(const __grid_constant__ BwdParams p, const __grid_constant__ CUte
         if (elect_one()) {
           const uint32_t full = smem_addr(&bar->qdo_full[s]);
           const uint32_t q_dst = ring + s * 2 * kUnitTile, do_dst = q_dst + kUnitTile;
-          mbar_arrive_expect_tx(full, 2 * kUnitTile);
+          mbar_arrive_expect_tx(full, 2 * (HD / 64) * kUnitHalf);
           tma_load_4d(q_dst, &tm_q, full, 0, head, sq.q_row0 + row0, sq.bq);
-          tma_load_4d(q_dst + kUnitHalf, &tm_q, full, 64, head, sq.q_row0 + row0, sq.bq);
+          if (HD > 64) tma_load_4d(q_dst + kUnitHalf, &tm_q, full, 64, head, sq.q_row0 + row0, sq.bq);
           tma_load_4d(do_dst, &tm_do, full, 0, head, sq.q_row0 + row0, sq.bq);
-          tma_load_4d(do_dst + kUnitHalf, &tm_do, full, 64, head, sq.q_row0 + row0, sq.bq);
+          if (HD > 64) tma_load_4d(do_dst + kUnitHalf, &tm_do, full, 64, head, sq.q_row0 + row0, sq.bq);
         }
         __syncwarp();
       }
@@ -380,7 +383,7 @@ bwd_dkv_kernel(const __grid_constant__ BwdParams p, const __grid_constant__ CUte
     // DV(u) reads: both come from this warp, in this order, and the tensor pipe keeps the order.
     const int r = warp - kMmaWarp;
     constexpr uint32_t idesc_st = make_idesc(AB_FMT, kBlk, kUnit, 0);  // [128 keys] x [64 rows], both operands K-major
-    constexpr uint32_t idesc_acc = make_idesc(AB_FMT, kBlk, kBlk, 1);  // [128 keys] x [128 head dim], B N-contiguous
+    constexpr uint32_t idesc_acc = make_idesc(AB_FMT, kBlk, HD, 1);    // [128 keys] x [head dim], B N-contiguous
     const uint64_t a_desc = make_smem_desc(r ? v_smem : k_smem, 16, 1024);                    // K (S^T = K Q^T) or V (dP^T = V dO^T)
     const uint64_t b_desc0 = make_smem_desc(ring + (r ? kUnitTile : 0), 16, 1024);            // Q or dO of stage 0, K-major
     const uint64_t b_nd0 = make_smem_desc(ring + (r ? 0 : kUnitTile), kUnitHalf, 1024);       // dO (dV += P^T dO) or Q (dK += dS^T Q), N-contiguous
@@ -407,7 +410,7 @@ bwd_dkv_kernel(const __grid_constant__ BwdParams p, const __grid_constant__ CUte
           const uint32_t d_tmem = tmem + 128 * b + 64 * r;
           mma_ss_c<false>(d_tmem, a_desc, b_desc, idesc_st);
 #pragma unroll
-          for (int ks = 1; ks < 8; ++ks) mma_ss_c<true>(d_tmem, a_desc + kmaj_off(ks), b_desc + unit_off(ks), idesc_st);
+          for (int ks = 1; ks < HD / 16; ++ks) mma_ss_c<true>(d_tmem, a_desc + kmaj_off(ks), b_desc + unit_off(ks), idesc_st);
           mma_commit(bar_stfull0 + 8 * b);
           if (u == iters - 1) mma_commit(bar_kvempty);  // the item's last reader of K / V
         }
@@ -520,8 +523,8 @@ bwd_dkv_kernel(const __grid_constant__ BwdParams p, const __grid_constant__ CUte
       __syncwarp();
       if (lane == 0) mbar_arrive(smem_addr(&bar->acc_free));
       if (jk < sq.k_len) {
-        store_slice<T>(dv_row, av);
-        store_slice<T>(dk_row, ak);
+        store_slice<T>(dv_row, av, p.d - 32 * q4);
+        store_slice<T>(dk_row, ak, p.d - 32 * q4);
       }
       ++wi;
       gu += w.iters;
@@ -585,7 +588,7 @@ __device__ __forceinline__ ItemB item_b(const BwdParams& p, int t) {
   return w;
 }
 
-template <typename T, uint32_t AB_FMT, bool SOFTCAP>
+template <typename T, uint32_t AB_FMT, bool SOFTCAP, int HD>
 __global__ void __launch_bounds__(kThreads, 1)
 bwd_dq_kernel(const __grid_constant__ BwdParams p, const __grid_constant__ CUtensorMap tm_q,
               const __grid_constant__ CUtensorMap tm_do, const __grid_constant__ CUtensorMap tm_k,
@@ -651,7 +654,7 @@ bwd_dq_kernel(const __grid_constant__ BwdParams p, const __grid_constant__ CUten
                  (int64_t)w.head * p.dq_head_stride;
         for (int c = lane; c < kBlk * 16; c += 32) {
           const int r = c >> 4, ch = c & 15;
-          if (w.row0 + r < sq.q_len) *reinterpret_cast<uint4*>(dq0 + (int64_t)r * p.dq_row_stride + ch * 8) = make_uint4(0, 0, 0, 0);
+          if (w.row0 + r < sq.q_len && ch * 8 < p.d) *reinterpret_cast<uint4*>(dq0 + (int64_t)r * p.dq_row_stride + ch * 8) = make_uint4(0, 0, 0, 0);
         }
         continue;
       }
@@ -666,11 +669,11 @@ bwd_dq_kernel(const __grid_constant__ BwdParams p, const __grid_constant__ CUten
       __syncwarp();
       if (elect_one()) {
         const uint32_t full = smem_addr(&bar->qdo_full);
-        mbar_arrive_expect_tx(full, 2 * kTileBytes);
+        mbar_arrive_expect_tx(full, 2 * (HD / 64) * kHalfBytes);
         tma_load_4d(q_smem, &tm_q, full, 0, w.head, sq.q_row0 + w.row0, sq.bq);
-        tma_load_4d(q_smem + kHalfBytes, &tm_q, full, 64, w.head, sq.q_row0 + w.row0, sq.bq);
+        if (HD > 64) tma_load_4d(q_smem + kHalfBytes, &tm_q, full, 64, w.head, sq.q_row0 + w.row0, sq.bq);
         tma_load_4d(do_smem, &tm_do, full, 0, w.head, sq.q_row0 + w.row0, sq.bq);
-        tma_load_4d(do_smem + kHalfBytes, &tm_do, full, 64, w.head, sq.q_row0 + w.row0, sq.bq);
+        if (HD > 64) tma_load_4d(do_smem + kHalfBytes, &tm_do, full, 64, w.head, sq.q_row0 + w.row0, sq.bq);
       }
       __syncwarp();
       // K(j) lives in slot j % 3 and is held until dQ += dS K of its block has run; V(j) in slot 3 + j % 2 until dP has
@@ -684,9 +687,9 @@ bwd_dq_kernel(const __grid_constant__ BwdParams p, const __grid_constant__ CUten
         if (!mbar_wait(smem_addr(&bar->kv_empty[slot]), par ^ 1, abort_flag, 71)) { ok = false; break; }
         if (elect_one()) {
           const uint32_t full = smem_addr(&bar->kv_full[slot]);
-          mbar_arrive_expect_tx(full, kTileBytes);
+          mbar_arrive_expect_tx(full, (HD / 64) * kHalfBytes);
           tma_load_4d(ring + slot * kTileBytes, tm, full, 0, w.hk, krow, sq.bq);
-          tma_load_4d(ring + slot * kTileBytes + kHalfBytes, tm, full, 64, w.hk, krow, sq.bq);
+          if (HD > 64) tma_load_4d(ring + slot * kTileBytes + kHalfBytes, tm, full, 64, w.hk, krow, sq.bq);
         }
         __syncwarp();
       }
@@ -722,7 +725,7 @@ bwd_dq_kernel(const __grid_constant__ BwdParams p, const __grid_constant__ CUten
           const uint64_t b_desc = ring_kd + slot * kSlotStep;
           mma_ss_c<false>(d_tmem, a_desc, b_desc, idesc_kk);
 #pragma unroll
-          for (int ks = 1; ks < 8; ++ks) mma_ss_c<true>(d_tmem, a_desc + kmaj_off(ks), b_desc + kmaj_off(ks), idesc_kk);
+          for (int ks = 1; ks < HD / 16; ++ks) mma_ss_c<true>(d_tmem, a_desc + kmaj_off(ks), b_desc + kmaj_off(ks), idesc_kk);
           mma_commit(bar_sfull);
           mma_commit(bar_empty0 + 8 * slot);
           if (r) mma_commit(bar_empty0 + 8 * slot);        // nobody else reads the V tile
@@ -735,7 +738,7 @@ bwd_dq_kernel(const __grid_constant__ BwdParams p, const __grid_constant__ CUten
     }
   } else if (warp == kMmaWarp + 2) {
     // ------------------------------------------------------------------ MMA issuer 2: dQ += dS K
-    constexpr uint32_t idesc_nn = make_idesc(AB_FMT, kBlk, kBlk, 1);
+    constexpr uint32_t idesc_nn = make_idesc(AB_FMT, kBlk, HD, 1);  // [128 rows] x [head dim]
     const uint64_t ring_nd = make_smem_desc(ring, kHalfBytes, 1024);
     constexpr uint64_t kSlotStep = kTileBytes >> 4;
     const uint32_t bar_full0 = smem_addr(&bar->kv_full[0]), bar_empty0 = smem_addr(&bar->kv_empty[0]);
@@ -835,7 +838,7 @@ bwd_dq_kernel(const __grid_constant__ BwdParams p, const __grid_constant__ CUten
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(smem_addr(&bar->acc_free));
-      if (i < sq.q_len) store_slice<T>(dq_row, a);
+      if (i < sq.q_len) store_slice<T>(dq_row, a, p.d - 32 * q4);
       ++wi;
       gj += w.iters;
     }
