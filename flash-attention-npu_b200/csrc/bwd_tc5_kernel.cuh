@@ -1,5 +1,5 @@
 // Attention backward on the Blackwell tensor cores (tcgen05.mma, accumulators and the P / dS operands in TMEM,
-// Q / K / V / dO tiles by TMA), head dim 128, dense and packed-varlen input.
+// Q / K / V / dO tiles by TMA), head dims up to 128, dense and packed-varlen input, optional softcap.
 //
 // Same arithmetic as bwd_kernel.cuh, which follows the reference's golden (tests/fa_small_op_golden.py:160-353) and
 // replaces its FAG kernels (csrc/arch22/flash_attn_npu_v3/fag_kernel.cpp):

@@ -305,7 +305,7 @@ def attention_backward(dout, q, k, v, out, lse, *, dq=None, dk=None, dv=None, so
                        max_seqlen_q=None, max_seqlen_k=None, kernel=0):
     """dQ, dK, dV of ``attention_forward`` (dense (b, s, h, d) or packed varlen (total, h, d) tensors) from
     the forward's ``out`` and ``lse``.  Head dim a multiple of 8, at most 256; no dropout / alibi.
-    ``kernel``: 0 automatic (tcgen05 kernels for head dim 128 without softcap), 1 the mma.sync kernel, 2 tcgen05."""
+    ``kernel``: 0 automatic (tcgen05 kernels for head dims up to 128), 1 the mma.sync kernel, 2 tcgen05."""
     lib = L.load()
     ts = (dout, q, k, v, out)
     if not all(t.is_cuda for t in ts) or not lse.is_cuda:

@@ -230,7 +230,7 @@ typedef struct fa_bwd_params {
 
 /* Bytes of device scratch fa_b200_bwd needs (fp32 dQ accumulator + rowsum(dO o O)). */
 size_t fa_b200_bwd_workspace_bytes(const fa_bwd_params* p);
-/* Three launches on `stream`.  Head dim 128 without softcap: rowsum, then two tcgen05 kernels (dK / dV per key block,
+/* Three launches on `stream`.  Head dims up to 128: rowsum, then two tcgen05 kernels (dK / dV per key block,
  * dQ per query block; no atomics, so the results are bit-reproducible).  Otherwise: a memset of the fp32 dQ accumulator,
  * rowsum, the mma.sync kernel (dQ through atomic adds), dQ conversion. */
 int fa_b200_bwd(const fa_bwd_params* p, void* workspace, size_t workspace_bytes, void* stream);
