@@ -35,7 +35,7 @@ fwd_tc5_kernel(const __grid_constant__ Tc5Params p, const __grid_constant__ CUte
   }
   const uint32_t q_smem = base;
   const uint32_t p_smem = base + 2 * kTileBytes;
-  const uint32_t kv_smem = base + 4 * kTileBytes;
+  const uint32_t kv_smem = base + Geo<HD>::kRingOff;
   Barriers* bar = reinterpret_cast<Barriers*>(smem + 4 * kTileBytes + kSlots * kTileBytes);
 
   // The warp index and the TMEM base are broadcast from lane 0 so that the compiler knows they are
@@ -85,7 +85,7 @@ fwd_tc5_kernel(const __grid_constant__ Tc5Params p, const __grid_constant__ CUte
   // scores of a row plus working set, the other roles need far fewer.
   if (warp < 8) {
     asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;\n" ::"n"(kRegsSoftmax));
-    softmax_loop<T, SOFTCAP>(p, bar, tmem, p_smem, warp >> 2, warp & 3, lane);
+    softmax_loop<T, SOFTCAP, Geo<HD>::kRows>(p, bar, tmem, p_smem, warp >> 2, warp & 3, lane);
   } else if (warp < 12) {
     asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;\n" ::"n"(kRegsCorr));
     correction_loop<T, HD>(p, bar, tmem, warp & 3, lane);
@@ -172,9 +172,9 @@ static int32_t* status_word() {
 bool tc5_eligible(const fa_fwd_params& a, bool is_causal, bool is_local, int wl_on_device) {
   (void)is_causal;
   (void)is_local;
-  // any head dim up to 128 that keeps rows 16-byte aligned: the tiles are 64 or 128 columns wide and the TMA unit
-  // fills the columns beyond the head dim with zeros
-  if (a.d < 8 || a.d > 128 || a.d % 8 != 0 || a.seqlen_q < 128) return false;
+  // any head dim up to 256 that keeps rows 16-byte aligned: the tiles are 64, 128 or 256 columns wide and the TMA
+  // unit fills the columns beyond the head dim with zeros
+  if (a.d < 8 || a.d > 256 || a.d % 8 != 0 || a.seqlen_q < 128) return false;
   // varlen: both sides packed, and the number of k / v rows known (TMA bound)
   if ((a.cu_seqlens_q != nullptr) != (a.cu_seqlens_k != nullptr)) return false;
   if (a.cu_seqlens_k && a.total_k <= 0) return false;
@@ -202,7 +202,8 @@ bool tc5_eligible(const fa_fwd_params& a, bool is_causal, bool is_local, int wl_
 }
 
 void tc5_fill_plan(const fa_fwd_params& a, fa_fwd_plan* pl) {
-  const int m_tiles = (a.seqlen_q + tc5::kTileM - 1) / tc5::kTileM;
+  const int tile_rows = a.d > 128 ? tc5::kBlockM : tc5::kTileM;  // Geo<HD>::kRows
+  const int m_tiles = (a.seqlen_q + tile_rows - 1) / tile_rows;
   const long long total = (long long)m_tiles * a.b * a.h;
   int num_sm = a.num_sm;
   if (num_sm <= 0) {
@@ -213,7 +214,7 @@ void tc5_fill_plan(const fa_fwd_params& a, fa_fwd_plan* pl) {
   pl->kernel = FA_KERNEL_TCGEN05;
   pl->config = 0;
   pl->pack_gqa = 0;
-  pl->block_m = tc5::kTileM;
+  pl->block_m = tile_rows;
   pl->block_n = tc5::kBlockN;
   pl->m_blocks = m_tiles;
   pl->num_splits = 1;
@@ -300,7 +301,8 @@ int tc5_launch(const fa_fwd_params& a, const fa_fwd_plan& pl, cudaStream_t st, s
   };
   auto pick_hd = [&](auto fix_tag, auto cap_tag) {
     if (a.d <= 64) pick(fix_tag, cap_tag, std::integral_constant<int, 64>{});
-    else pick(fix_tag, cap_tag, std::integral_constant<int, 128>{});
+    else if (a.d <= 128) pick(fix_tag, cap_tag, std::integral_constant<int, 128>{});
+    else pick(fix_tag, cap_tag, std::integral_constant<int, 256>{});
   };
   if (p.fix_tail) {
     if (cap) pick_hd(std::true_type{}, std::true_type{});

@@ -54,6 +54,22 @@ constexpr int kBarBytes = 3072;  // barriers, per-row rescale factors and 1 / l
 constexpr int kSmemBytes = 4 * kTileBytes + kSlots * kTileBytes + kBarBytes;
 static_assert(kSmemBytes <= 232448, "more than the 227 KiB a CTA can have");
 
+// Geometry by tile width HD (64, 128 or 256 columns; the head dim is at most HD).  Up to 128 a CTA tile is two
+// 128-row sub-tiles and a K / V tile fills one 32 KiB ring slot (its first half only for 64).  For 256 the 256 fp32
+// columns of O leave TMEM room for one sub-tile only: the CTA tile is 128 rows, Q takes both Q slots (64 KiB), the
+// second P slot joins the ring, and the ring is two slots of 64 KiB.
+template <int HD>
+struct Geo {
+  static_assert(HD == 64 || HD == 128 || HD == 256, "tile widths");
+  static constexpr int kHalves = HD / 64;                                      // 64-column halves of a Q / K / V tile
+  static constexpr bool kWide = HD > 128;
+  static constexpr int kRows = kWide ? kBlockM : kTileM;                       // query rows of a CTA tile
+  static constexpr int kSlotBytes = kWide ? 2 * kTileBytes : kTileBytes;
+  static constexpr int kRing = kWide ? 2 : kSlots;
+  static constexpr int kRingOff = kWide ? 3 * kTileBytes : 4 * kTileBytes;     // Q0 Q1 | P0 [P1] | ring
+  static_assert(kRingOff + kRing * kSlotBytes + kBarBytes <= kSmemBytes, "shared memory layout");
+};
+
 struct Tc5Params {
   fa_fwd_params a;
   int32_t is_causal, is_local, wl, wr;
@@ -85,6 +101,7 @@ struct TileInfo {
 // on, so the K / V prefixes a chunk re-reads tile after tile come from L2 and not from HBM.  The
 // chunk length makes a chunk a whole even number of rounds of the grid (TileSched), which keeps the
 // per-CTA sums as even as one chunk over everything would.
+template <int ROWS>  // query rows of a CTA tile: 256 (two sub-tiles) or 128 (sub-tile 0 only)
 __device__ __forceinline__ void tile_info(const Tc5Params& p, int n, TileInfo& ti) {
   const int per_m = p.a.b * p.a.h;
   const int per_chunk = p.chunk_bh * p.m_tiles;
@@ -115,7 +132,7 @@ __device__ __forceinline__ void tile_info(const Tc5Params& p, int n, TileInfo& t
   ti.uhi = 0;
 #pragma unroll
   for (int t = 0; t < 2; ++t) {
-    const int r0 = mt * kTileM + t * kBlockM;
+    const int r0 = (ROWS == kBlockM && t == 1) ? 0x3fffffff : mt * ROWS + t * kBlockM;  // no second sub-tile in 128-row tiles
     ti.row0[t] = r0;
     ti.jlo[t] = ti.jhi[t] = 0;
     ti.has[t] = false;

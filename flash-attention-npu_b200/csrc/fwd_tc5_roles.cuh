@@ -12,11 +12,12 @@ namespace tc5 {
 // (Carrying the order across tile boundaries -- Q.K^T of the next tile's first block before P.V of this tile's last
 // one -- lets one sub-tile run a block ahead of the other, and then the two need four K / V tiles at a time where the
 // ring has three: measured 8 % slower on causal 4K.)
+template <int SLOTS>
 struct RingPos {
   uint32_t cnt = 0;
   __device__ __forceinline__ void next(uint32_t& slot, uint32_t& par) {
-    slot = cnt % kSlots;
-    par = (cnt / kSlots) & 1;
+    slot = cnt % SLOTS;
+    par = (cnt / SLOTS) & 1;
     ++cnt;
   }
 };
@@ -33,7 +34,8 @@ template <bool FIX, int HD>
 __device__ __forceinline__ void producer_loop(const Tc5Params& p, const CUtensorMap* tm_q, const CUtensorMap* tm_k,
                                               const CUtensorMap* tm_v, Barriers* bar, uint32_t q_smem, uint32_t kv_smem) {
   volatile int* abort_flag = &bar->abort_flag;
-  RingPos ring;
+  using G = Geo<HD>;
+  RingPos<G::kRing> ring;
   uint32_t q_cnt[2] = {0, 0};
   const bool varlen_q = p.a.cu_seqlens_q != nullptr, varlen_k = p.a.cu_seqlens_k != nullptr;
   const int lane = threadIdx.x & 31;
@@ -42,7 +44,7 @@ __device__ __forceinline__ void producer_loop(const Tc5Params& p, const CUtensor
   TileSched sched(p);
   for (int n = sched.first(); n < p.total_tiles; n = sched.next()) {
     TileInfo ti;
-    tile_info(p, n, ti);
+    tile_info<G::kRows>(p, n, ti);
     if (ti.uhi <= ti.ulo) continue;
 #pragma unroll
     for (int t = 0; t < 2; ++t) {
@@ -53,9 +55,10 @@ __device__ __forceinline__ void producer_loop(const Tc5Params& p, const CUtensor
       const int row = ti.q_row0 + ti.row0[t];
       const int bq = varlen_q ? 0 : ti.bi;
       if (elect_one()) {
-        mbar_arrive_expect_tx(full, (HD / 64) * kHalfBytes);
-        tma_load_4d_hint(q_smem + t * kTileBytes, tm_q, full, 0, ti.hh, row, bq, q_policy);
-        if (HD > 64) tma_load_4d_hint(q_smem + t * kTileBytes + kHalfBytes, tm_q, full, 64, ti.hh, row, bq, q_policy);
+        mbar_arrive_expect_tx(full, G::kHalves * kHalfBytes);
+#pragma unroll
+        for (int hf = 0; hf < G::kHalves; ++hf)
+          tma_load_4d_hint(q_smem + t * kTileBytes + hf * kHalfBytes, tm_q, full, 64 * hf, ti.hh, row, bq, q_policy);
       }
       __syncwarp();
     }
@@ -84,9 +87,10 @@ __device__ __forceinline__ void producer_loop(const Tc5Params& p, const CUtensor
       if (!mbar_wait(smem_addr(&bar->kv_empty[slot]), par ^ 1, abort_flag, 12)) return false;
       const uint32_t full = smem_addr(&bar->kv_full[slot]);
       if (elect_one()) {
-        mbar_arrive_expect_tx(full, (HD / 64) * kHalfBytes);
-        tma_load_4d(kv_smem + slot * kTileBytes, tm, full, 0, ti.hk, row, outer);
-        if (HD > 64) tma_load_4d(kv_smem + slot * kTileBytes + kHalfBytes, tm, full, 64, ti.hk, row, outer);
+        mbar_arrive_expect_tx(full, G::kHalves * kHalfBytes);
+#pragma unroll
+        for (int hf = 0; hf < G::kHalves; ++hf)
+          tma_load_4d(kv_smem + slot * G::kSlotBytes + hf * kHalfBytes, tm, full, 64 * hf, ti.hk, row, outer);
       }
       __syncwarp();
       return true;
@@ -121,7 +125,7 @@ __device__ __forceinline__ void tail_fix_loop(const Tc5Params& p, Barriers* bar,
   TileSched sched(p);
   for (int n = sched.first(); n < p.total_tiles; n = sched.next()) {
     TileInfo ti;
-    tile_info(p, n, ti);
+    tile_info<Geo<HD>::kRows>(p, n, ti);
     if (!tile_needs_tail_fix(p, ti)) continue;
     if (!mbar_wait_patient(smem_addr(&bar->fix_req), fix_cnt & 1, abort_flag, 51)) return;
     ++fix_cnt;
@@ -130,7 +134,7 @@ __device__ __forceinline__ void tail_fix_loop(const Tc5Params& p, Barriers* bar,
     // a row is 128 bytes in each 64-column half of the tile (the swizzle only permutes inside a row)
 #pragma unroll
     for (int half = 0; half < HD / 64; ++half) {
-      const uint32_t base = kv_smem + slot * kTileBytes + half * kHalfBytes;
+      const uint32_t base = kv_smem + slot * Geo<HD>::kSlotBytes + half * kHalfBytes;
       for (int off = r0 * 128 + lane * 16; off < kHalfBytes; off += 32 * 16)
         asm volatile("st.shared.v4.b32 [%0], {%1,%1,%1,%1};\n" ::"r"(base + off), "r"(0) : "memory");
     }
@@ -154,14 +158,15 @@ __device__ __forceinline__ void mma_loop(const Tc5Params& p, Barriers* bar, uint
   volatile int* abort_flag = &bar->abort_flag;
   constexpr uint32_t idesc_qk = make_idesc(AB_FMT, kBlockM, kBlockN, 0);
   constexpr uint32_t idesc_pv = make_idesc(AB_FMT, kBlockM, HD, 1);
-  RingPos ring;
+  using G = Geo<HD>;
+  RingPos<G::kRing> ring;
   uint32_t q_cnt = 0, qk_cnt = 0, p_cnt = 0, ofree_cnt = 0, oready_cnt = 0;
   // Descriptor bases are built once; inside the loops a descriptor is base + a small constant.
   const uint64_t q_desc = make_smem_desc(q_smem + t * kTileBytes, 16, 1024);
   const uint64_t p_desc = make_smem_desc(p_smem + t * kTileBytes, 16, 1024);
   const uint64_t k_desc0 = make_smem_desc(kv_smem, 16, 1024);          // K-major operand (K)
   const uint64_t v_desc0 = make_smem_desc(kv_smem, kHalfBytes, 1024);  // N-contiguous operand (V)
-  constexpr uint64_t kSlotStep = kTileBytes >> 4;
+  constexpr uint64_t kSlotStep = G::kSlotBytes >> 4;
   // K-major operands: 16 columns per k-step = 32 bytes inside the 128-byte swizzle span
   auto k_off = [](int ks) { return (uint64_t)(((ks >> 2) * kHalfBytes + (ks & 3) * 32) >> 4); };
   const uint32_t s_tmem = tmem + t * 128, o_tmem = tmem + 256 + t * 128;
@@ -190,7 +195,7 @@ __device__ __forceinline__ void mma_loop(const Tc5Params& p, Barriers* bar, uint
   TileSched sched(p);
   for (int n = sched.first(); n < p.total_tiles; n = sched.next()) {
     TileInfo ti;
-    tile_info(p, n, ti);
+    tile_info<G::kRows>(p, n, ti);
     if (ti.uhi <= ti.ulo) continue;
     if (ti.has[t]) {
       if (!mbar_wait(smem_addr(&bar->q_full[t]), q_cnt & 1, abort_flag, 13)) return;

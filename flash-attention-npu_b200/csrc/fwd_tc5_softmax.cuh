@@ -102,7 +102,7 @@ __device__ __forceinline__ void store_p_chunk(uint32_t p_row, uint32_t p_xor, in
   }
 }
 
-template <typename T, bool SOFTCAP>
+template <typename T, bool SOFTCAP, int ROWS>
 __device__ __forceinline__ void softmax_loop(const Tc5Params& p, Barriers* bar, uint32_t tmem, uint32_t p_smem, int t,
                                              int warp_in_wg, int lane) {
   volatile int* abort_flag = &bar->abort_flag;
@@ -123,7 +123,7 @@ __device__ __forceinline__ void softmax_loop(const Tc5Params& p, Barriers* bar, 
   TileSched sched(p);
   for (int n = sched.first(); n < p.total_tiles; n = sched.next()) {
     TileInfo ti;
-    tile_info(p, n, ti);
+    tile_info<ROWS>(p, n, ti);
     if (ti.row0[t] >= ti.q_len) continue;
     const int i = ti.row0[t] + row;
     if (!ti.has[t]) {  // no visible key for the whole sub-tile: O = 0, LSE = +inf
@@ -255,9 +255,9 @@ __device__ __forceinline__ void rescale_o(uint32_t o_tmem, float f) {
     }
     tmem_st32(o_tmem + half * 64, a);
     tmem_st32(o_tmem + half * 64 + 32, b);
-    if (half == 0 && HD > 64) {
-      tmem_ld32(o_tmem + 64, a);
-      tmem_ld32(o_tmem + 96, b);
+    if (half + 1 < HD / 64) {
+      tmem_ld32(o_tmem + (half + 1) * 64, a);
+      tmem_ld32(o_tmem + (half + 1) * 64 + 32, b);
       tmem_wait_ld();
     }
   }
@@ -276,7 +276,7 @@ __device__ __forceinline__ void correction_loop(const Tc5Params& p, Barriers* ba
   TileSched sched(p);
   for (int n = sched.first(); n < p.total_tiles; n = sched.next()) {
     TileInfo ti;
-    tile_info(p, n, ti);
+    tile_info<Geo<HD>::kRows>(p, n, ti);
     if (ti.uhi <= ti.ulo) continue;
     for (int j = ti.ulo; j < ti.uhi; ++j) {
 #pragma unroll
@@ -339,9 +339,9 @@ __device__ __forceinline__ void correction_loop(const Tc5Params& p, Barriers* ba
             if (half * 64 + 32 + e < d_cols) __stcs(reinterpret_cast<uint4*>(o_ptr + half * 64 + 32 + e), w);
           }
         }
-        if (half == 0 && HD > 64) {
-          tmem_ld32(o_tmem + 64, a);
-          tmem_ld32(o_tmem + 96, b);
+        if (half + 1 < HD / 64) {
+          tmem_ld32(o_tmem + (half + 1) * 64, a);
+          tmem_ld32(o_tmem + (half + 1) * 64 + 32, b);
         }
       }
       tc_fence_before();

@@ -10,7 +10,7 @@
 
 namespace fa {
 
-// True when the tcgen05 kernel covers this problem (head dim up to 128, at least 128 query rows; dense,
+// True when the tcgen05 kernel covers this problem (head dim up to 256, at least 128 query rows; dense,
 // packed varlen, or a KV cache with per-entry lengths, paged or not; no alibi).
 bool tc5_eligible(const fa_fwd_params& a, bool is_causal, bool is_local, int wl_on_device);
 // Overwrites the tile fields of the plan for the tcgen05 kernel.
