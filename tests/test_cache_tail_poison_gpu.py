@@ -76,10 +76,10 @@ def _check(q, kc, vc, kn, vn, lens, bt, idx, kernel, tag, causal=True, window=(-
 
 @pytest.mark.parametrize("append", [False, True], ids=["read", "append"])
 @pytest.mark.parametrize("layout,d", [("contiguous", 128), ("page128", 128), ("page256", 128), ("batch_idx", 128),
-                                      ("contiguous", 64), ("page128", 64)])
+                                      ("contiguous", 64), ("page128", 64), ("contiguous", 256), ("page256", 192)])
 def test_tcgen05_prefill_ignores_the_cache_tail(layout, d, append):
     """Chunked prefill (200 query tokens) against a cache: lengths that end inside a 128-key block, exactly on a
-    block boundary, inside a page, an empty entry, a full cache; head dims 128 and 64."""
+    block boundary, inside a page, an empty entry, a full cache; every tile width of the kernel."""
     g = torch.Generator().manual_seed(4100 + len(layout) + append)
     b, s_q, h, hk, s_cache = 6, 200, 8, 2, 1536
     s_new = s_q if append else 0

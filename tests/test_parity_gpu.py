@@ -71,9 +71,10 @@ def test_varlen_ragged_lengths():
         U.check_rules(out, lse, gold_out, gold_lse, tag=f"ragged causal={causal}")
 
 
-@pytest.mark.parametrize("d,softcap", [(128, 0.0), (64, 0.0), (128, 30.0), (64, 30.0)])
+@pytest.mark.parametrize("d,softcap", [(128, 0.0), (64, 0.0), (128, 30.0), (64, 30.0), (256, 0.0), (192, 30.0), (96, 0.0)])
 def test_varlen_ragged_lengths_tcgen05(d, softcap):
-    """Ragged packed sequences on the tcgen05 kernel (head dims 128 and 64, with and without softcap): tiles that run
+    """Ragged packed sequences on the tcgen05 kernel (tile widths 64, 128 and 256 columns, head dims in between, with and
+    without softcap): tiles that run
     into the next sequence, an empty sequence, queries longer than the keys (rows without a visible key), GQA, a
     sliding window."""
     from flash_b200 import lib as L
