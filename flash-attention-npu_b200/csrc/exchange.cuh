@@ -87,20 +87,24 @@ __global__ void __launch_bounds__(kCombineWarps * 32) xchg_push_kernel(const __g
     if (lane == 0)
       for (int r = 0; r < p.world; ++r) xchg_row(p.bufs[r], parity, p.world, p.rank, n_rows, c.d, row)[c.d] = lse_row;
   }
-  // The CTA that finishes last publishes the step to every rank.
+  // The CTA that finishes last publishes the step to every rank: one thread per rank, so that the release stores
+  // (each of which waits for its own round trip over NVLink) go out side by side instead of one after the other.
   __threadfence_system();
   __syncthreads();
+  __shared__ int s_last;
   if (threadIdx.x == 0) {
     const unsigned int before = atomicAdd(&hdr->done_ctas, 1u);
-    if (before + 1u == gridDim.x) {
+    s_last = (before + 1u == gridDim.x) ? 1 : 0;
+    if (s_last) {
       hdr->done_ctas = 0u;
       *reinterpret_cast<volatile unsigned int*>(&hdr->epoch) = epoch;
       __threadfence_system();
-      for (int r = 0; r < p.world; ++r) {
-        unsigned int* flag = &reinterpret_cast<XchgHeader*>(p.bufs[r])->flags[p.rank];
-        asm volatile("st.release.sys.global.u32 [%0], %1;\n" ::"l"(flag), "r"(epoch) : "memory");
-      }
     }
+  }
+  __syncthreads();
+  if (s_last && (int)threadIdx.x < p.world) {
+    unsigned int* flag = &reinterpret_cast<XchgHeader*>(p.bufs[threadIdx.x])->flags[p.rank];
+    asm volatile("st.release.sys.global.u32 [%0], %1;\n" ::"l"(flag), "r"(epoch) : "memory");
   }
 }
 
@@ -112,28 +116,24 @@ __global__ void __launch_bounds__(kCombineWarps * 32) xchg_merge_kernel(const __
   XchgHeader* hdr = reinterpret_cast<XchgHeader*>(buf);
   const unsigned int epoch = *reinterpret_cast<volatile unsigned int*>(&hdr->epoch);
   const int parity = (int)(epoch & 1u);
-  __shared__ int s_ok;
-  if (threadIdx.x == 0) {
-    int ok = 1;
+  // thread r waits for rank r's flag (all ranks side by side); every wait has the same cycle budget
+  int ok = 1;
+  if ((int)threadIdx.x < p.world) {
+    const unsigned int* flag = &hdr->flags[threadIdx.x];
     const long long t0 = clock64();
-    for (int r = 0; r < p.world && ok; ++r) {
-      const unsigned int* flag = &hdr->flags[r];
-      for (;;) {
-        unsigned int v;
-        asm volatile("ld.acquire.sys.global.u32 %0, [%1];\n" : "=r"(v) : "l"(flag) : "memory");
-        if ((int)(v - epoch) >= 0) break;
-        if (clock64() - t0 > p.timeout_cycles) {  // a rank did not deliver: give up, say so, keep the context usable
-          ok = 0;
-          if (p.status) atomicOr(p.status, kStatusExchangeTimeout);
-          break;
-        }
-        __nanosleep(200);
+    for (;;) {
+      unsigned int v;
+      asm volatile("ld.acquire.sys.global.u32 %0, [%1];\n" : "=r"(v) : "l"(flag) : "memory");
+      if ((int)(v - epoch) >= 0) break;
+      if (clock64() - t0 > p.timeout_cycles) {  // a rank did not deliver: give up, say so, keep the context usable
+        ok = 0;
+        if (p.status) atomicOr(p.status, kStatusExchangeTimeout);
+        break;
       }
+      __nanosleep(100);
     }
-    s_ok = ok;
   }
-  __syncthreads();
-  if (!s_ok) return;
+  if (!__syncthreads_and(ok)) return;
   const int lane = threadIdx.x & 31;
   const int64_t row = (int64_t)blockIdx.x * kCombineWarps + (threadIdx.x >> 5);
   const int64_t n_rows = (int64_t)c.b * c.s * c.h;
