@@ -563,6 +563,7 @@ static int run_fwd_exchange(const fa_fwd_params& a_in, void* workspace, size_t w
   int rc = make_plan(a, &P);
   if (rc != FA_OK) return rc;
   const int ns_plan = P.pl.kernel == FA_KERNEL_TCGEN05 ? 1 : P.pl.num_splits;
+  if (ns_plan > 32) return fail(FA_ERR_UNSUPPORTED, "the cross-GPU exchange merges at most 32 local splits (set num_splits)");
   const size_t need = exchange_workspace(a, ns_plan);
   if (!workspace || workspace_bytes < need) return fail(FA_ERR_WORKSPACE, "workspace missing or too small (fa_b200_fwd_exchange_workspace)");
   if ((reinterpret_cast<uintptr_t>(workspace) & 15) != 0) return fail(FA_ERR_WORKSPACE, "workspace must be 16-byte aligned");

@@ -57,32 +57,21 @@ __global__ void __launch_bounds__(kCombineWarps * 32) xchg_push_kernel(const __g
     const int bb = (int)(row / ((int64_t)c.h * c.s));
     const float* lp = c.lse_partial + bb * c.lp_batch_stride + ss * c.lp_row_stride + hh * c.lp_head_stride;
     const float* op = c.o_partial + bb * c.op_batch_stride + ss * c.op_row_stride + hh * c.op_head_stride;
-    float m = -INFINITY;
-    for (int i = lane; i < c.num_splits; i += 32) m = fmaxf(m, lp[(int64_t)i * c.lp_split_stride]);
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
-    const bool dead = (m == -INFINITY);
-    float tot = 0.f;
-    if (!dead)
-      for (int i = lane; i < c.num_splits; i += 32) tot += __expf(lp[(int64_t)i * c.lp_split_stride] - m);
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) tot += __shfl_xor_sync(0xffffffffu, tot, o);
-    const float inv = dead ? 0.f : 1.f / tot;
+    // the arithmetic of combine_kernel; more than 32 local splits do not occur with a sharded key range
+    float l_mine, w_mine, m, tot;
+    bool dead;
+    const int n = min(c.num_splits, 32);
+    merge_weights(n, lane, [&](int i) { return lp[(int64_t)i * c.lp_split_stride]; }, l_mine, w_mine, m, tot, dead);
     const float lse_row = dead ? -INFINITY : m + logf(tot);
-    for (int col = lane * 4; col < c.d; col += 128) {
-      float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-      if (!dead) {
-        for (int i = 0; i < c.num_splits; ++i) {
-          const float l = lp[(int64_t)i * c.lp_split_stride];
-          if (l == -INFINITY) continue;
-          const float w = __expf(l - m) * inv;
-          const float4 x = *reinterpret_cast<const float4*>(op + (int64_t)i * c.op_split_stride + col);
-          acc.x += w * x.x; acc.y += w * x.y; acc.z += w * x.z; acc.w += w * x.w;
-        }
-      }
-      for (int r = 0; r < p.world; ++r) {  // the same row into every rank's buffer (peer stores over NVLink)
-        *reinterpret_cast<float4*>(xchg_row(p.bufs[r], parity, p.world, p.rank, n_rows, c.d, row) + col) = acc;
-      }
+    for (int c0 = 0; c0 < c.d; c0 += 128) {
+      const int col = c0 + lane * 4;
+      const bool on = col < c.d;
+      const float4 acc = merge_columns(n, l_mine, w_mine, [&](int i) {
+        return on ? *reinterpret_cast<const float4*>(op + (int64_t)i * c.op_split_stride + col) : make_float4(0.f, 0.f, 0.f, 0.f);
+      });
+      if (on)
+        for (int r = 0; r < p.world; ++r)  // the same row into every rank's buffer (peer stores over NVLink)
+          *reinterpret_cast<float4*>(xchg_row(p.bufs[r], parity, p.world, p.rank, n_rows, c.d, row) + col) = acc;
     }
     if (lane == 0)
       for (int r = 0; r < p.world; ++r) xchg_row(p.bufs[r], parity, p.world, p.rank, n_rows, c.d, row)[c.d] = lse_row;
@@ -141,27 +130,19 @@ __global__ void __launch_bounds__(kCombineWarps * 32) xchg_merge_kernel(const __
   const int hh = (int)(row % c.h);
   const int ss = (int)((row / c.h) % c.s);
   const int bb = (int)(row / ((int64_t)c.h * c.s));
-  float m = -INFINITY;
-  for (int r = 0; r < p.world; ++r) m = fmaxf(m, __ldcg(xchg_row(buf, parity, p.world, r, n_rows, c.d, row) + c.d));
-  const bool dead = (m == -INFINITY);
-  float tot = 0.f;
-  if (!dead)
-    for (int r = 0; r < p.world; ++r) tot += __expf(__ldcg(xchg_row(buf, parity, p.world, r, n_rows, c.d, row) + c.d) - m);
-  const float inv = dead ? 0.f : 1.f / tot;
+  float l_mine, w_mine, m, tot;
+  bool dead;
+  merge_weights(p.world, lane, [&](int r) { return __ldcg(xchg_row(buf, parity, p.world, r, n_rows, c.d, row) + c.d); }, l_mine,
+                w_mine, m, tot, dead);
   OutT* out = reinterpret_cast<OutT*>(c.o) + bb * c.o_batch_stride + ss * c.o_row_stride + hh * c.o_head_stride;
-  for (int col = lane * 4; col < c.d; col += 128) {
-    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-    if (!dead) {
-      for (int r = 0; r < p.world; ++r) {
-        const float* src = xchg_row(buf, parity, p.world, r, n_rows, c.d, row);
-        const float l = __ldcg(src + c.d);
-        if (l == -INFINITY) continue;
-        const float w = __expf(l - m) * inv;
-        const float4 x = __ldcg(reinterpret_cast<const float4*>(src + col));
-        acc.x += w * x.x; acc.y += w * x.y; acc.z += w * x.z; acc.w += w * x.w;
-      }
-    }
-    store4<OutT>(out + col, acc);
+  for (int c0 = 0; c0 < c.d; c0 += 128) {
+    const int col = c0 + lane * 4;
+    const bool on = col < c.d;
+    const float4 acc = merge_columns(p.world, l_mine, w_mine, [&](int r) {
+      return on ? __ldcg(reinterpret_cast<const float4*>(xchg_row(buf, parity, p.world, r, n_rows, c.d, row) + col))
+                : make_float4(0.f, 0.f, 0.f, 0.f);
+    });
+    if (on) store4<OutT>(out + col, acc);
   }
   if (c.lse && lane == 0)
     c.lse[bb * c.lse_batch_stride + ss * c.lse_row_stride + hh * c.lse_head_stride] = dead ? INFINITY : m + logf(tot);
