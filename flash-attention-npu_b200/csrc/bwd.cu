@@ -30,11 +30,18 @@ static cudaError_t launch_bwd(const BwdParams& p, int n_kblocks, cudaStream_t st
 
 extern "C" {
 
+// First part of the workspace: the fp32 dQ accumulator of the mma.sync kernel, or the two work-item counters of the
+// tcgen05 kernels (which write dQ directly).
+static size_t bwd_accum_bytes(const fa_bwd_params* a, int64_t rows) {
+  if (a->kernel != 1 && fa::bwd_tc5_eligible(*a)) return 16;
+  const int d_pad = a->d <= 64 ? 64 : (a->d <= 128 ? 128 : 256);
+  return fa::align16((size_t)rows * a->h * d_pad * sizeof(float));
+}
+
 size_t fa_b200_bwd_workspace_bytes(const fa_bwd_params* a) {
   if (!a) return 0;
-  const int d_pad = a->d <= 64 ? 64 : (a->d <= 128 ? 128 : 256);
   const int64_t rows = a->cu_seqlens_q ? a->total_q : (int64_t)a->b * a->seqlen_q;
-  return fa::align16((size_t)rows * a->h * d_pad * sizeof(float)) + fa::align16((size_t)rows * a->h * sizeof(float));
+  return bwd_accum_bytes(a, rows) + fa::align16((size_t)rows * a->h * sizeof(float));
 }
 
 int fa_b200_bwd(const fa_bwd_params* a, void* workspace, size_t workspace_bytes, void* stream) {
@@ -99,7 +106,7 @@ int fa_b200_bwd(const fa_bwd_params* a, void* workspace, size_t workspace_bytes,
   p.softmax_scale = a->softmax_scale;
   p.scale_log2 = a->softmax_scale * kLog2e;
   p.softcap = a->softcap;
-  const size_t acc_bytes = align16((size_t)rows * a->h * p.d_pad * sizeof(float));
+  const size_t acc_bytes = bwd_accum_bytes(a, rows);
   p.dq_accum = reinterpret_cast<float*>(workspace);
   p.delta = reinterpret_cast<float*>(reinterpret_cast<char*>(workspace) + acc_bytes);
 

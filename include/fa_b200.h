@@ -228,7 +228,8 @@ typedef struct fa_bwd_params {
   int32_t kernel;  /* 0 automatic; 1 force the mma.sync kernel; 2 force the tcgen05 kernels (FA_ERR_UNSUPPORTED if they do not cover the problem) */
 } fa_bwd_params;
 
-/* Bytes of device scratch fa_b200_bwd needs (fp32 dQ accumulator + rowsum(dO o O)). */
+/* Bytes of device scratch fa_b200_bwd needs: rowsum(dO o O), plus the fp32 dQ accumulator where the mma.sync kernel runs
+ * (the tcgen05 kernels need 16 bytes instead). */
 size_t fa_b200_bwd_workspace_bytes(const fa_bwd_params* p);
 /* Three launches on `stream`.  Head dims up to 128: rowsum, then two tcgen05 kernels (dK / dV per key block,
  * dQ per query block; no atomics, so the results are bit-reproducible).  Otherwise: a memset of the fp32 dQ accumulator,
