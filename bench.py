@@ -643,6 +643,29 @@ def measure(key, args, steps, warmup, dev, rank, world, local_rank, peaks, barri
     return entry
 
 
+def bind_to_gpu_numa_node(local_rank):
+    """Multi-process runs: keep this process (and so the pinned host buffers it allocates, first touch) on the CPUs of
+    the NUMA node its GPU hangs off, as a deployment would.  Without it all ranks' host buffers tend to land on one
+    node and the end-to-end copies of all GPUs cross the same socket link.  Returns a short description, or None when
+    the topology cannot be read (then nothing is changed)."""
+    try:
+        pr = torch.cuda.get_device_properties(local_rank)
+        bdf = f"{pr.pci_domain_id:04x}:{pr.pci_bus_id:02x}:{pr.pci_device_id:02x}.0"
+        base = f"/sys/bus/pci/devices/{bdf}"
+        node = int(open(base + "/numa_node").read().strip())
+        cpus = set()
+        for part in open(base + "/local_cpulist").read().strip().split(","):
+            lo, _, hi = part.partition("-")
+            cpus.update(range(int(lo), int(hi or lo) + 1))
+        cpus &= os.sched_getaffinity(0)
+        if node < 0 or not cpus:
+            return None
+        os.sched_setaffinity(0, cpus)
+        return f"numa node {node}, {len(cpus)} cpus"
+    except Exception:  # no sysfs, no permission, an unknown layout: run unbound
+        return None
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -674,7 +697,9 @@ def main():
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
     import torch.distributed as dist
+    host_binding = None
     if world > 1:
+        host_binding = bind_to_gpu_numa_node(local_rank)  # (a single process keeps all cores: it also times the CPU baseline)
         dist.init_process_group("nccl", device_id=dev)
 
     def barrier():
@@ -703,6 +728,8 @@ def main():
         if rank == 0:
             line["workloads"] = extra
     if rank == 0:
+        if world > 1:
+            line["config"]["host_binding"] = host_binding or "none (topology not readable)"
         print(json.dumps(line))
         sys.stdout.flush()
     if world > 1:
