@@ -6,8 +6,8 @@
 //   P = exp(S scale - LSE)   dP = dO V^T   dS = P o (dP - D) scale   dV = P^T dO   dK = dS^T Q   dQ = dS K
 // with P and dS rounded to the input dtype before the second matrix products and fp32 accumulation.
 //
-// Two persistent kernels (one CTA per SM, work items dealt out heavy first), no atomics (the results do not depend on
-// any order of arrival):
+// Two persistent kernels (one CTA per SM; work items drawn from a global counter, a head's blocks neighbours in the
+// order, its heavy blocks first), no atomics (the results do not depend on any order of arrival):
 //   bwd_dkv_kernel  one CTA per 128 keys of a (batch entry, kv head).  K and V stay in shared memory, the query
 //                   rows that see the keys (of every query head of the group) stream through a ring, 64 at a time.
 //                   It computes the TRANSPOSED products S^T = K Q^T and dP^T = V dO^T, so that a TMEM lane is a key:
@@ -20,12 +20,11 @@
 //                   from).  S and dP are free as soon as they are in registers, so the products of the next block
 //                   run under this block's exponentials.  TMEM: S | dP | dQ | dS.
 // The elementwise work has no row reduction (LSE and D are inputs), so it is split by columns over 16 warps: a
-// thread owns one TMEM lane and 32 of the 128 columns.
-// Warps 0-15 elementwise + epilogue; warps 16-18 issue the MMAs (one elected lane each), each its own share: one
-// issuing thread next to busy warps gets a tcgen05.mma out only every ~130 cycles, half the rate the tensor pipe
-// takes them at, so the products of a block are spread over two (dK / dV: the S^T / dV chain and the dP^T / dK chain,
-// each chain's TMEM hazards stay inside one in-order issuer) or three (dQ: S, dP, dQ) warps on different
-// schedulers; warp 19 is the TMA producer.
+// thread owns one TMEM lane and 32 columns (of a block's 128 in the dQ kernel, of a unit's 64 in the dK / dV kernel,
+// where warps 0-7 and 8-15 take alternate units).
+// Warps 0-15 elementwise + epilogue; warps 16-18 issue the MMAs (one elected lane each), each its own chain of
+// products: S^T then dV, and dP^T then dK (each chain's TMEM hazards stay inside one in-order issuer), or S, dP and
+// dQ (spreading the issue over warps did not change the speed by itself); warp 19 is the TMA producer.
 // A CTA walks over its work items without tearing anything down: barrier phases and ring positions run on, the next
 // item's tiles are requested as soon as the current item's last product has read the old ones, and the epilogue hands
 // the accumulators back (acc_free) as soon as they are in registers, so its global stores lie under the next item's
