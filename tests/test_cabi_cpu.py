@@ -216,3 +216,41 @@ def test_plan_prefill_against_a_cache_goes_to_the_tcgen05_kernel():
     assert rc == 0 and pl.kernel == L.KERNEL_TCGEN05
     rc, pl = _plan(_params(**dict(kw, alibi_slopes=256)))
     assert rc == 0 and pl.kernel == L.KERNEL_MMA
+
+
+def _bwd_params(**kw):
+    p = L.BwdParams()
+    for name in ("q", "k", "v", "o", "dout", "lse", "dq", "dk", "dv"):
+        setattr(p, name, 256)
+    p.b, p.seqlen_q, p.seqlen_k, p.h, p.h_k, p.d, p.total_q = 2, 512, 512, 8, 2, 128, 1024
+    for t, heads in (("q", 8), ("k", 2), ("v", 2), ("o", 8), ("do", 8), ("dq", 8), ("dk", 2), ("dv", 2)):
+        setattr(p, f"{t}_batch_stride", 512 * heads * 128)
+        setattr(p, f"{t}_row_stride", heads * 128)
+        setattr(p, f"{t}_head_stride", 128)
+    p.lse_batch_stride, p.lse_head_stride = 8 * 512, 512
+    p.dtype, p.softmax_scale = L.FA_BF16, 0.088
+    p.window_left = p.window_right = -1
+    for k, v in kw.items():
+        setattr(p, k, v)
+    return p
+
+
+def test_backward_workspace_and_kernel_choice():
+    """The tcgen05 backward (head dims up to 128; packed input only with the number of k / v rows) needs the rowsum
+    and 16 bytes of counters; the mma.sync kernel needs its fp32 dQ accumulator as well.  A forced kernel that does not
+    cover the problem is refused before anything is launched (the pointers here are never dereferenced)."""
+    lib = L.load()
+    rows, h = 2 * 512, 8
+    delta = rows * h * 4
+    assert lib.fa_b200_bwd_workspace_bytes(C.byref(_bwd_params())) == 16 + delta
+    assert lib.fa_b200_bwd_workspace_bytes(C.byref(_bwd_params(softcap=30.0, d=64))) == 16 + delta
+    assert lib.fa_b200_bwd_workspace_bytes(C.byref(_bwd_params(kernel=1))) == rows * h * 128 * 4 + delta
+    assert lib.fa_b200_bwd_workspace_bytes(C.byref(_bwd_params(d=256))) == rows * h * 256 * 4 + delta
+    packed = dict(cu_seqlens_q=256, cu_seqlens_k=256, lse_batch_stride=0, lse_head_stride=1024)
+    assert lib.fa_b200_bwd_workspace_bytes(C.byref(_bwd_params(total_k=1024, **packed))) == 16 + delta
+    assert lib.fa_b200_bwd_workspace_bytes(C.byref(_bwd_params(total_k=0, **packed))) == rows * h * 128 * 4 + delta
+    for kw, msg in ((dict(kernel=2, d=256), "tcgen05 backward covers"), (dict(kernel=5), "kernel must be"),
+                    (dict(h_k=3), "must divide"), (dict(d=100), "multiple of 8")):
+        p = _bwd_params(**kw)
+        rc = lib.fa_b200_bwd(C.byref(p), 4096, 1 << 40, None)
+        assert rc != 0 and msg in lib.fa_b200_last_error().decode(), (kw, lib.fa_b200_last_error())
