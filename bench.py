@@ -539,6 +539,9 @@ def measure(key, args, steps, warmup, dev, rank, world, local_rank, peaks, barri
     stream = torch.cuda.current_stream()
     ev = [torch.cuda.Event(enable_timing=True) for _ in range(steps + 1)]
     barrier()
+    # one more untimed step, so that the first timed one does not start on a GPU the barrier has just left idle (with
+    # few timed steps a single slow first step on one rank is what the max over ranks reports)
+    wl.step()
     launches0 = _L.load().fa_b200_launch_count() + getattr(wl, "replayed_launches", 0)
     ev[0].record(stream)
     for i in range(steps):
