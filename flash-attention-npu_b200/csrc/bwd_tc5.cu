@@ -47,7 +47,7 @@ int bwd_tc5_launch(const BwdParams& p, const fa_bwd_params& a, cudaStream_t st, 
   const long long items_kv = (long long)((a.seqlen_k + kBlk - 1) / kBlk) * a.h_k * a.b;
   const long long items_q = (long long)((a.seqlen_q + kBlk - 1) / kBlk) * a.h * a.b;
   const dim3 grid_kv((unsigned)std::min<long long>(items_kv, num_sm)), grid_q((unsigned)std::min<long long>(items_q, num_sm));
-  // the two item counters: the first words of the fp32 dQ accumulator, which these kernels do not use
+  // the two work-item counters: the first 16 bytes of the workspace (where the mma.sync kernel has its fp32 dQ accumulator)
   int32_t* counters = reinterpret_cast<int32_t*>(p.dq_accum);
   cudaError_t e = cudaMemsetAsync(counters, 0, 2 * sizeof(int32_t), st);
   auto launch = [&](auto kern, dim3 grid, const CUtensorMap& mq, const CUtensorMap& mdo, int32_t* counter) {
