@@ -254,3 +254,29 @@ def test_backward_workspace_and_kernel_choice():
         p = _bwd_params(**kw)
         rc = lib.fa_b200_bwd(C.byref(p), 4096, 1 << 40, None)
         assert rc != 0 and msg in lib.fa_b200_last_error().decode(), (kw, lib.fa_b200_last_error())
+
+
+def test_plan_tcgen05_prefill_covers_head_dims_up_to_256_and_softcap():
+    """Dense prefill with at least 128 query rows goes to the tcgen05 kernel for every head dim up to 256 that is a
+    multiple of 8, with or without softcap; above 128 the CTA tile is 128 rows (one sub-tile), otherwise 256.  Alibi and
+    fewer than 128 query rows stay on the general kernel."""
+    def dense(d, sq=1024, **kw):
+        h, hk = 8, 2
+        return _params(b=2, seqlen_q=sq, seqlen_k=1024, h=h, h_k=hk, d=d, total_q=2 * sq, causal=1,
+                       q_batch_stride=sq * h * d, q_row_stride=h * d, q_head_stride=d,
+                       k_batch_stride=1024 * hk * d, k_row_stride=hk * d, k_head_stride=d,
+                       v_batch_stride=1024 * hk * d, v_row_stride=hk * d, v_head_stride=d,
+                       o_batch_stride=sq * h * d, o_row_stride=h * d, o_head_stride=d,
+                       lse_batch_stride=h * sq, lse_head_stride=sq, **kw)
+    for d, rows in ((8, 256), (40, 256), (64, 256), (96, 256), (128, 256), (136, 128), (192, 128), (256, 128)):
+        rc, pl = _plan(dense(d))
+        assert rc == 0 and pl.kernel == L.KERNEL_TCGEN05 and pl.block_m == rows and pl.block_n == 128, (d, pl.kernel, pl.block_m)
+        assert pl.m_blocks == -(-1024 // rows) and pl.num_splits == 1 and pl.workspace_bytes == 0
+        rc, pl = _plan(dense(d, softcap=30.0))
+        assert rc == 0 and pl.kernel == L.KERNEL_TCGEN05
+    rc, pl = _plan(dense(128, alibi_slopes=256))
+    assert rc == 0 and pl.kernel == L.KERNEL_MMA
+    rc, pl = _plan(dense(128, sq=100))
+    assert rc == 0 and pl.kernel == L.KERNEL_MMA
+    rc, pl = _plan(dense(128, kernel=L.KERNEL_TCGEN05, sq=100))
+    assert rc != 0  # forced, but the problem is not covered
